@@ -1,0 +1,132 @@
+// Engine state shared by the executor's translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <functional>
+#include <map>
+#include <string>
+#include <vector>
+#include "gehtp_cuda.h"
+#include "launchers.h"
+#include "launchers_w4.h"
+
+namespace gehtp {
+
+constexpr uint32_t kMaxTemps = WT_EXEC_MAX_TEMPS;
+constexpr uint32_t kNoOff = 0xFFFFFFFFu;
+
+struct KvGeom {
+    bool ready = false;
+    uint32_t slot_bytes = 0, nslots = 0;
+    uint32_t* posmap = nullptr;  // device, nslots entries
+};
+
+// One runlist op after planning: resolved device pointers baked into `launch`.
+struct PlanOp {
+    int rc = 0;                 // non-zero: the op fails when reached, with `err`
+    std::string err;
+    std::function<void(cudaStream_t)> launch;
+    uint32_t engine = WT_ENG_SCALAR;
+    uint32_t out_id[2] = {kNoOff, kNoOff};   // temps written, for last-bytes tracking
+    uint32_t out_bytes[2] = {0, 0};
+    int kv_append_state = -1;   // AUTO append: host counter check / bump
+    int kv_gather_state = -1;   // AUTO gather: host counter check
+    uint32_t w4_m = 0;          // M of a W4A16 matmul (reported through engine_m)
+    // fusion: when `fused` is set on op i, it replaces ops [i, i + span)
+    std::function<void(cudaStream_t)> fused;
+    uint32_t span = 0;
+    uint32_t stat = 0;          // index into the stats struct, 0 = none
+};
+
+struct W4Packed {
+    uint32_t* packed = nullptr;   // device, K*N/2 bytes, strip-major layout
+    const uint16_t* scales = nullptr;  // device, [K/64][N], inside the uploaded slot
+    uint32_t K = 0, N = 0;
+};
+
+struct Engine {
+    bool dev_ok = false;
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    std::string last_error;
+
+    // identity of the planned blob
+    const wt_blob* blob = nullptr;
+    const uint8_t* blob_wbase = nullptr;
+    uint32_t blob_nops = 0, blob_nslots = 0;
+    bool planned = false;
+
+    uint8_t* d_weights = nullptr;
+    size_t weights_bytes = 0;
+    std::map<uint32_t, uint8_t*> d_ext;        // EXT_IN / EXT_WGT slots: own buffers
+    std::map<uint64_t, W4Packed> w4;            // key = slot | K<<16 ... see executor.cu
+
+    uint8_t* d_arena = nullptr;
+    size_t arena_bytes = 0;
+    uint8_t* temp_dev[kMaxTemps];
+    uint32_t temp_cap[kMaxTemps];
+    uint32_t temp_last[kMaxTemps];
+
+    // TEMPOFF table / wt_exec_pool_init
+    bool have_static = false;
+    uint32_t static_cap = 0, vtcm_cap = 0;
+    size_t vtcm_base = 0;               // arena offset of the on-chip-resident region
+    uint32_t static_off[kMaxTemps], vtcm_off[kMaxTemps];
+    bool user_pool = false;
+    uint32_t user_total = 0, user_static = 0;
+    std::vector<uint32_t> user_off;
+
+    // persistent states
+    bool states_loaded = false;
+    uint32_t n_states = 0;
+    uint8_t* st_buf[WT_MAX_STATES];
+    uint32_t st_bytes[WT_MAX_STATES];
+    uint32_t st_count[WT_MAX_STATES];   // host mirror of the AUTO position counters
+    uint32_t* d_st_count = nullptr;     // device, WT_MAX_STATES entries
+    KvGeom kv[WT_MAX_STATES];
+
+    unsigned int* d_status = nullptr;   // first failing op (1-based) raised by a kernel
+    unsigned int* h_status = nullptr;   // pinned
+
+    std::vector<PlanOp> plan;
+    uint32_t fused_ops = 0;
+    uint32_t demoted_temps = 0;
+
+    // I/O staging
+    uint8_t* h_in = nullptr;  size_t h_in_cap = 0;    // pinned
+    uint8_t* h_out = nullptr; size_t h_out_cap = 0;   // pinned
+    std::map<uint32_t, std::pair<uint8_t*, size_t>> mirrors;  // wt_exec_temp host views
+    const uint8_t* ext_in = nullptr;
+    const uint8_t* ext_in_dev = nullptr;
+    const uint8_t* ext_wgt = nullptr;
+
+    // CUDA graph of a whole run
+    cudaGraphExec_t graph = nullptr;
+    uint32_t graph_out_temp = kNoOff;
+    bool graph_has_in = false, graph_has_out = false;
+    uint32_t warm_runs = 0;
+    unsigned long long graph_launches = 0;  // kernels inside the captured graph
+
+    // options
+    int opt_fuse = 1, opt_graph = 1, trace_on = 0;
+    const char* hook_spec = nullptr;
+    wt_op_ts* ts_buf = nullptr;
+    uint32_t ts_cap = 0;
+    wt_exec_stats st{};
+
+    // tensor parallel
+    int tp_rank = 0, tp_world = 1;
+    void* nccl_comm = nullptr;
+};
+
+extern Engine g;
+
+// executor.cu
+bool ensure_device(char* err, size_t errn);
+// plan.cu
+int build_plan(const wt_blob* b, char* err, size_t errn);
+void drop_plan(bool keep_states);
+// fuse.cu
+void fuse_plan(const wt_blob* b);
+
+}  // namespace gehtp

@@ -1,0 +1,493 @@
+// The wt_exec_* C API on CUDA: device set-up, the run loop over a planned op
+// list, host<->device I/O staging, per-op timing / hooks / traces, whole-run
+// CUDA graphs. Mirrors the calling contract of the reference engine
+// (kernels/src/runtime/oplist_exec.c:2499-2602; kernels/include/oplist_exec.h).
+#include <fcntl.h>
+#include <unistd.h>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include "engine.h"
+
+namespace gehtp {
+
+Engine g;
+
+static int64_t now_us() {
+    return std::chrono::duration_cast<std::chrono::microseconds>(
+               std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+static void set_err(char* err, size_t errn, const char* msg) {
+    g.last_error = msg;
+    if (err && errn) std::snprintf(err, errn, "%s", msg);
+}
+
+bool ensure_device(char* err, size_t errn) {
+    if (g.dev_ok) { cudaSetDevice(g.device); return true; }
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); set_err(err, errn, "no CUDA device"); return false; }
+    int dev = g.device;
+    if (dev < 0) { const char* e = std::getenv("GEHTP_CUDA_DEVICE"); dev = e ? std::atoi(e) : 0; }
+    if (dev >= n || cudaSetDevice(dev) != cudaSuccess) { set_err(err, errn, "no CUDA device"); return false; }
+    g.device = dev;
+    if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess) { set_err(err, errn, "no CUDA device"); return false; }
+    cudaMalloc(&g.d_st_count, WT_MAX_STATES * sizeof(uint32_t));
+    cudaMemset(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t));
+    cudaMalloc(&g.d_status, sizeof(unsigned int));
+    cudaMemset(g.d_status, 0, sizeof(unsigned int));
+    cudaMallocHost(&g.h_status, sizeof(unsigned int));
+    *g.h_status = 0;
+    if (const char* e = std::getenv("GEHTP_CUDA_FUSE")) g.opt_fuse = std::atoi(e);
+    if (const char* e = std::getenv("GEHTP_CUDA_GRAPH")) g.opt_graph = std::atoi(e);
+    for (uint32_t i = 0; i < kMaxTemps; i++) { g.temp_dev[i] = nullptr; g.temp_cap[i] = 0; g.temp_last[i] = 0; g.static_off[i] = kNoOff; g.vtcm_off[i] = kNoOff; }
+    g.dev_ok = true;
+    return true;
+}
+
+static void grow_pinned(uint8_t*& p, size_t& cap, size_t need) {
+    if (need <= cap) return;
+    if (p) cudaFreeHost(p);
+    cap = (need + 4095) / 4096 * 4096;
+    if (cudaMallocHost(&p, cap) != cudaSuccess) { p = nullptr; cap = 0; }
+}
+
+// "opidx:temp,opidx:temp" dump after op `ii` of the current range
+// (exec_hook_dump, oplist_exec.c:117-166).
+static void hook_dump(uint32_t ii) {
+    static const char* env_hook = nullptr;
+    static bool env_tried = false;
+    const char* hook = g.hook_spec;
+    if (!hook) {
+        if (!env_tried) { env_hook = std::getenv("GEHTP_HOOK"); env_tried = true; }
+        hook = env_hook;
+    }
+    if (!hook || !hook[0]) return;
+    const char* tok = hook;
+    while (*tok) {
+        const char* comma = std::strchr(tok, ',');
+        size_t len = comma ? (size_t)(comma - tok) : std::strlen(tok);
+        std::string item(tok, len);
+        size_t col = item.rfind(':');
+        if (col != std::string::npos) {
+            uint32_t hi = (uint32_t)std::strtoul(item.substr(0, col).c_str(), nullptr, 0);
+            uint32_t ht = (uint32_t)std::strtoul(item.substr(col + 1).c_str(), nullptr, 0);
+            if (hi == ii && ht < kMaxTemps && g.temp_cap[ht]) {
+                uint32_t nbytes = g.temp_last[ht];
+                std::vector<uint8_t> host(nbytes);
+                cudaStreamSynchronize(g.stream);
+                cudaMemcpy(host.data(), g.temp_dev[ht], nbytes, cudaMemcpyDeviceToHost);
+                char fn[128];
+                std::snprintf(fn, sizeof fn, "/tmp/hook_%u_%u.f16.raw", hi, ht);
+                int fd = open(fn, O_WRONLY | O_CREAT | O_TRUNC, 0666);
+                if (fd >= 0) {
+                    size_t off = 0;
+                    while (off < nbytes) {
+                        ssize_t w = write(fd, host.data() + off, nbytes - off);
+                        if (w <= 0) break;
+                        off += (size_t)w;
+                    }
+                    close(fd);
+                }
+            }
+        }
+        if (!comma) break;
+        tok = comma + 1;
+    }
+}
+
+static FILE* g_trace_fp = nullptr;
+static void trace_line(const char* fmt, unsigned a, unsigned b, int c, long long d) {
+    if (!g_trace_fp) {
+        const char* fn = std::getenv("GEHTP_TRACE_FILE");
+        g_trace_fp = std::fopen(fn ? fn : "/tmp/gehtp_optrace.txt", "a");
+    }
+    if (g_trace_fp) { std::fprintf(g_trace_fp, fmt, a, b, c, d); std::fflush(g_trace_fp); }
+}
+
+static bool hooks_active() {
+    if (g.hook_spec) return g.hook_spec[0] != 0;
+    const char* e = std::getenv("GEHTP_HOOK");
+    return e && e[0];
+}
+
+static void bump_stat(uint32_t stat) {
+    uint32_t* f = &g.st.ops;
+    if (stat) f[stat - 1]++;
+    if (stat == 6) g.st.pin_skipped++;  // there is no on-chip weight cache to fill
+}
+
+static int ensure_plan(const wt_blob* b, char* err, size_t errn) {
+    if (g.planned && (g.blob != b || g.blob_wbase != b->weight_base || g.blob_nops != b->n_ops ||
+                      g.blob_nslots != b->n_slots))
+        drop_plan(true);
+    if (g.planned) return 0;
+    int rc = build_plan(b, err, errn);
+    if (rc != 0) { drop_plan(true); if (err) g.last_error = err; }
+    return rc;
+}
+
+// Host-side part of an op that the device cannot check before it is queued:
+// the AUTO position counters of the KV states (oplist_exec.c:2166-2173, 2198-2207).
+static int host_precheck(const PlanOp& p, char* err, size_t errn) {
+    char m[160];
+    if (p.kv_append_state >= 0) {
+        uint32_t si = (uint32_t)p.kv_append_state;
+        if (g.st_count[si] >= g.kv[si].nslots) {
+            std::snprintf(m, sizeof m, "kv append state %u count=%u >= nslots=%u (context too long)", si, g.st_count[si], g.kv[si].nslots);
+            set_err(err, errn, m);
+            return -1;
+        }
+        g.st_count[si]++;
+    }
+    if (p.kv_gather_state >= 0) {
+        uint32_t si = (uint32_t)p.kv_gather_state;
+        if (g.st_count[si] == 0u || g.st_count[si] > g.kv[si].nslots) {
+            std::snprintf(m, sizeof m, "kv gather state %u count=%u bad (append first?)", si, g.st_count[si]);
+            set_err(err, errn, m);
+            return -1;
+        }
+    }
+    return 0;
+}
+
+static void note_outputs(const PlanOp& p) {
+    for (int k = 0; k < 2; k++) {
+        uint32_t id = p.out_id[k];
+        if (id == kNoOff) continue;
+        g.temp_last[id] = p.out_bytes[k];
+        if (g.temp_cap[id] < p.out_bytes[k]) g.temp_cap[id] = p.out_bytes[k];
+    }
+}
+
+// Queues ops [first, first+count) on the engine stream. Returns 0 or the
+// 1-based index of the op that failed before launch.
+static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sync, uint32_t* engine_m,
+                       int64_t* op_us, char* err, size_t errn) {
+    const int64_t t_run0 = now_us();
+    const bool hooks = hooks_active();
+    for (uint32_t ii = 0; ii < count;) {
+        const uint32_t i = first + ii;
+        PlanOp& p = g.plan[i];
+        uint32_t span = 1;
+        const bool use_fused = fuse && p.fused && p.span >= 1 && ii + p.span <= count;
+        if (use_fused) span = p.span;
+        const int64_t t0 = now_us();
+        int rc = 0;
+        if (g.trace_on) trace_line("pre%u code=%u fused=%d pool=%lld\n", ii, g.blob->ops[i].opcode, use_fused ? 1 : 0, (long long)g.arena_bytes);
+        for (uint32_t k = 0; k < span && !rc; k++) {
+            PlanOp& q = g.plan[i + k];
+            if (q.rc) { set_err(err, errn, q.err.c_str()); rc = -1; break; }
+            if (host_precheck(q, err, errn)) { rc = -1; break; }
+            if (q.w4_m) *engine_m = q.w4_m;
+            bump_stat(q.stat);
+            g.st.ops++;
+            note_outputs(q);
+            if (!use_fused && q.launch) q.launch(g.stream);
+        }
+        if (!rc && use_fused) p.fused(g.stream);
+        if (!rc && (per_op_sync || hooks)) {
+            cudaError_t ce = cudaStreamSynchronize(g.stream);
+            if (ce != cudaSuccess) { set_err(err, errn, cudaGetErrorString(ce)); rc = -1; }
+        }
+        if (!rc && hooks) for (uint32_t k = 0; k < span; k++) hook_dump(ii + k);
+        const int64_t t1 = now_us();
+        for (uint32_t k = 0; k < span; k++) {
+            if (op_us) op_us[ii + k] = k == 0 ? t1 - t0 : 0;
+            if (g.ts_buf && i + k < g.ts_cap) {
+                wt_op_ts& ts = g.ts_buf[i + k];
+                ts.start_us = (uint32_t)(t0 - t_run0);
+                ts.dur_us = k == 0 ? (uint32_t)(t1 - t0) : 0;
+                ts.dma_us = 0; ts.dma_bytes = 0;
+                ts.engine = g.plan[i + k].engine;
+            }
+        }
+        if (g.trace_on) trace_line("op%u code=%u rc=%d us=%lld\n", ii, g.blob->ops[i].opcode, rc, (long long)(t1 - t0));
+        if (rc) return (int)i + 1;
+        ii += span;
+    }
+    return 0;
+}
+
+// Ends a run: waits for the stream and turns a device-raised status into the
+// reference's error return.
+static int finish_run(char* err, size_t errn) {
+    cudaMemcpyAsync(g.h_status, g.d_status, sizeof(unsigned int), cudaMemcpyDeviceToHost, g.stream);
+    cudaError_t ce = cudaStreamSynchronize(g.stream);
+    if (ce != cudaSuccess) { set_err(err, errn, cudaGetErrorString(ce)); return -1; }
+    if (*g.h_status) {
+        unsigned int code = *g.h_status;
+        *g.h_status = 0;
+        cudaMemsetAsync(g.d_status, 0, sizeof(unsigned int), g.stream);
+        char m[96];
+        std::snprintf(m, sizeof m, "kv gather miss (state bug) at op %u", code - 1);
+        set_err(err, errn, m);
+        return (int)code;
+    }
+    return 0;
+}
+
+static void stage_inputs(const wt_blob* b, const void* in_host, const void* in_dev) {
+    for (auto& kv : g.d_ext) {
+        const wt_slot& sl = b->slots[kv.first];
+        if (sl.addr != WT_SLOT_EXT_IN) continue;
+        if (in_host) {
+            grow_pinned(g.h_in, g.h_in_cap, sl.len);
+            std::memcpy(g.h_in, in_host, sl.len);
+            cudaMemcpyAsync(kv.second, g.h_in, sl.len, cudaMemcpyHostToDevice, g.stream);
+        } else if (in_dev) {
+            cudaMemcpyAsync(kv.second, in_dev, sl.len, cudaMemcpyDeviceToDevice, g.stream);
+        }
+    }
+}
+
+static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void* in_host,
+                    const void* in_dev, void* out_host, void* out_dev, uint32_t out_temp, bool sync_end,
+                    uint32_t* engine_m, int64_t* op_us, char* err, size_t errn) {
+    uint32_t dummy_m = 0;
+    if (!engine_m) engine_m = &dummy_m;
+    *engine_m = 0;
+    if (!b) { set_err(err, errn, "null blob"); return -1; }
+    if (!ensure_device(err, errn)) return -1;
+    if ((uint64_t)first + count > b->n_ops) { set_err(err, errn, "range oob"); return -1; }
+    if (ensure_plan(b, err, errn) != 0) return -1;
+
+    const bool timing = op_us || g.ts_buf;
+    const bool whole = first == 0 && count == b->n_ops;
+    const bool has_in = in_host || in_dev;
+    const bool eager_only = timing || hooks_active() || g.trace_on || !g.opt_graph || !whole || in_dev || out_dev;
+
+    int rc = 0;
+    if (!eager_only && g.graph && g.graph_out_temp == out_temp && g.graph_has_in == has_in &&
+        g.graph_has_out == (out_host != nullptr)) {
+        // replay: host bookkeeping first, then one launch
+        for (uint32_t i = 0; i < b->n_ops; i++) {
+            PlanOp& q = g.plan[i];
+            if (q.rc) { set_err(err, errn, q.err.c_str()); return (int)i + 1; }
+            if (host_precheck(q, err, errn)) return (int)i + 1;
+            if (q.w4_m) *engine_m = q.w4_m;
+            bump_stat(q.stat);
+            g.st.ops++;
+            note_outputs(q);
+        }
+        if (in_host) {
+            for (auto& kv : g.d_ext)
+                if (b->slots[kv.first].addr == WT_SLOT_EXT_IN) std::memcpy(g.h_in, in_host, b->slots[kv.first].len);
+        }
+        cudaGraphLaunch(g.graph, g.stream);
+        g_launches += g.graph_launches;
+        rc = finish_run(err, errn);
+        if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
+        return rc;
+    }
+
+    // a run that could be graphed later is captured on its second eager pass
+    const bool capture = !eager_only && !g.graph && g.warm_runs >= 1;
+    uint32_t out_bytes_planned = 0;
+    if (capture) {
+        if (in_host)
+            for (auto& kv : g.d_ext)
+                if (b->slots[kv.first].addr == WT_SLOT_EXT_IN) grow_pinned(g.h_in, g.h_in_cap, b->slots[kv.first].len);
+        if (out_host && out_temp < kMaxTemps) {
+            // the size the output temp has after a whole run is known from the previous run
+            out_bytes_planned = g.temp_last[out_temp];
+            grow_pinned(g.h_out, g.h_out_cap, out_bytes_planned ? out_bytes_planned : 4);
+        }
+        if (cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            g.opt_graph = 0;
+            return run_impl(b, first, count, in_host, in_dev, out_host, out_dev, out_temp, sync_end, engine_m, op_us, err, errn);
+        }
+    }
+    const unsigned long long launches0 = g_launches;
+    if (has_in) stage_inputs(b, in_host, in_dev);
+    rc = queue_range(first, count, g.opt_fuse != 0, timing, engine_m, op_us, err, errn);
+    if (capture) {
+        if (rc == 0 && out_host && out_temp < kMaxTemps && g.temp_cap[out_temp])
+            cudaMemcpyAsync(g.h_out, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToHost, g.stream);
+        cudaGraph_t graph = nullptr;
+        cudaError_t ce = cudaStreamEndCapture(g.stream, &graph);
+        if (rc != 0 || ce != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            g.opt_graph = 0;  // this blob cannot be graphed; stay eager
+            if (rc != 0) return rc;
+            // host counters were advanced while capturing: undo, then run eagerly
+            for (uint32_t i = 0; i < b->n_ops; i++)
+                if (g.plan[i].kv_append_state >= 0) g.st_count[g.plan[i].kv_append_state]--;
+            return run_impl(b, first, count, in_host, in_dev, out_host, out_dev, out_temp, sync_end, engine_m, op_us, err, errn);
+        }
+        ce = cudaGraphInstantiate(&g.graph, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ce != cudaSuccess) {
+            g.graph = nullptr; g.opt_graph = 0; cudaGetLastError();
+            for (uint32_t i = 0; i < b->n_ops; i++)
+                if (g.plan[i].kv_append_state >= 0) g.st_count[g.plan[i].kv_append_state]--;
+            return run_impl(b, first, count, in_host, in_dev, out_host, out_dev, out_temp, sync_end, engine_m, op_us, err, errn);
+        }
+        g.graph_launches = g_launches - launches0;
+        g.graph_out_temp = out_temp; g.graph_has_in = has_in; g.graph_has_out = out_host != nullptr;
+        cudaGraphLaunch(g.graph, g.stream);
+        rc = finish_run(err, errn);
+        if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
+        return rc;
+    }
+    if (rc != 0) { cudaStreamSynchronize(g.stream); return rc; }
+    if (whole) g.warm_runs++;
+    if (out_dev && out_temp < kMaxTemps && g.temp_cap[out_temp])
+        cudaMemcpyAsync(out_dev, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToDevice, g.stream);
+    if (out_host && out_temp < kMaxTemps && g.temp_cap[out_temp]) {
+        grow_pinned(g.h_out, g.h_out_cap, g.temp_last[out_temp]);
+        cudaMemcpyAsync(g.h_out, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToHost, g.stream);
+    }
+    if (!sync_end) return 0;
+    rc = finish_run(err, errn);
+    if (rc == 0 && out_host && out_temp < kMaxTemps && g.temp_cap[out_temp])
+        std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
+    return rc;
+}
+
+}  // namespace gehtp
+
+using namespace gehtp;
+
+extern "C" {
+
+int wt_exec_run_range(const struct wt_blob* b, uint32_t first, uint32_t count, uint32_t* engine_m,
+                      int64_t* op_us, char* err, size_t errn) {
+    return run_impl(b, first, count, g.ext_in, nullptr, nullptr, nullptr, kNoOff, true, engine_m, op_us, err, errn);
+}
+
+int wt_exec_run(const struct wt_blob* b, uint32_t* engine_m, int64_t* op_us, char* err, size_t errn) {
+    std::memset(&g.st, 0, sizeof g.st);
+    if (!b) { set_err(err, errn, "null blob"); return -1; }
+    return run_impl(b, 0, b->n_ops, g.ext_in, nullptr, nullptr, nullptr, kNoOff, true, engine_m, op_us, err, errn);
+}
+
+int wt_exec_run_io(const struct wt_blob* b, const void* in_ptr, void* out_ptr, uint32_t out_temp,
+                   uint32_t* engine_m, int64_t* op_us, char* err, size_t errn) {
+    std::memset(&g.st, 0, sizeof g.st);
+    if (!b) { set_err(err, errn, "null blob"); return -1; }
+    return run_impl(b, 0, b->n_ops, in_ptr, nullptr, out_ptr, nullptr, out_temp, true, engine_m, op_us, err, errn);
+}
+
+int gehtp_cuda_run_dev(const struct wt_blob* b, const void* in_dev, void* out_dev, uint32_t out_temp,
+                       char* err, size_t errn) {
+    std::memset(&g.st, 0, sizeof g.st);
+    if (!b) { set_err(err, errn, "null blob"); return -1; }
+    return run_impl(b, 0, b->n_ops, nullptr, in_dev, nullptr, out_dev, out_temp, false, nullptr, nullptr, err, errn);
+}
+
+uint8_t* wt_exec_temp(uint32_t id) {
+    if (!g.dev_ok || id >= kMaxTemps || !g.temp_cap[id] || !g.temp_dev[id]) return nullptr;
+    auto& m = g.mirrors[id];
+    size_t need = g.temp_cap[id];
+    if (m.second < need) {
+        if (m.first) cudaFreeHost(m.first);
+        m.first = nullptr;
+        if (cudaMallocHost(&m.first, need) != cudaSuccess) { m.second = 0; return nullptr; }
+        m.second = need;
+    }
+    cudaSetDevice(g.device);
+    cudaStreamSynchronize(g.stream);
+    if (cudaMemcpy(m.first, g.temp_dev[id], need, cudaMemcpyDeviceToHost) != cudaSuccess) return nullptr;
+    return m.first;
+}
+
+uint32_t wt_exec_temp_bytes(uint32_t id) { return id < kMaxTemps ? g.temp_cap[id] : 0; }
+uint32_t wt_exec_temp_last_bytes(uint32_t id) { return id < kMaxTemps ? g.temp_last[id] : 0; }
+
+void wt_exec_shutdown(void) {
+    std::memset(&g.st, 0, sizeof g.st);
+    if (!g.dev_ok) return;
+    cudaSetDevice(g.device);
+    cudaStreamSynchronize(g.stream);
+    drop_plan(true);
+    g.user_pool = false;
+    g.user_off.clear();
+}
+
+void wt_exec_state_reset(void) {
+    if (!g.dev_ok) return;
+    cudaSetDevice(g.device);
+    for (uint32_t i = 0; i < g.n_states; i++) {
+        cudaMemsetAsync(g.st_buf[i], 0, g.st_bytes[i], g.stream);
+        g.st_count[i] = 0;
+        if (g.kv[i].ready) cudaMemsetAsync(g.kv[i].posmap, 0xFF, (size_t)g.kv[i].nslots * 4, g.stream);
+    }
+    cudaMemsetAsync(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t), g.stream);
+    cudaStreamSynchronize(g.stream);
+}
+
+void wt_exec_pool_init(uint8_t* base, uint32_t total_cap, uint32_t static_cap, const uint32_t* offsets) {
+    if (base) {
+        g.user_pool = true;
+        g.user_total = total_cap;
+        g.user_static = static_cap;
+    } else if (!offsets) {
+        g.user_pool = false;
+    }
+    g.user_off.clear();
+    if (offsets) g.user_off.assign(offsets, offsets + kMaxTemps);
+    if (g.planned) drop_plan(true);
+}
+
+void wt_exec_get_stats(struct wt_exec_stats* st) { if (st) *st = g.st; }
+void wt_exec_set_ext_weights(const void* wgt_ptr) { g.ext_wgt = (const uint8_t*)wgt_ptr; }
+void wt_exec_set_ts(struct wt_op_ts* buf, uint32_t cap) { g.ts_buf = buf; g.ts_cap = buf ? cap : 0; }
+void wt_exec_set_trace(int on) { g.trace_on = on ? 1 : 0; }
+void wt_exec_set_hook(const char* spec) { g.hook_spec = spec; }
+
+// One JSON line per slot, then per op, then a summary line.
+void wt_w3_report(const char* blob_name, const uint8_t* buf, size_t size, const struct wt_blob* w,
+                  void (*emit)(const char* line, void* ud), void* ud) {
+    if (!emit || !w) return;
+    (void)buf;
+    char line[512];
+    std::snprintf(line, sizeof line, "{\"blob\":\"%s\",\"bytes\":%zu,\"ver\":%u,\"n_slots\":%u,\"n_ops\":%u,\"weight_off\":%u}",
+                  blob_name ? blob_name : "", size, (unsigned)w->ver, w->n_slots, w->n_ops, w->weight_off);
+    emit(line, ud);
+    for (uint32_t i = 0; i < w->n_slots; i++) {
+        const wt_slot& s = w->slots[i];
+        std::snprintf(line, sizeof line, "{\"slot\":%u,\"len\":%u,\"count\":%u,\"offset\":%llu,\"addr\":%u}", i, s.len,
+                      s.count, (unsigned long long)s.offset, s.addr);
+        emit(line, ud);
+    }
+    for (uint32_t i = 0; i < w->n_ops; i++) {
+        const wt_op& op = w->ops[i];
+        int n = std::snprintf(line, sizeof line, "{\"op\":%u,\"opcode\":%u,\"args\":[", i, (unsigned)op.opcode);
+        for (uint16_t a2 = 0; a2 < op.n_args && n < (int)sizeof line - 16; a2++)
+            n += std::snprintf(line + n, sizeof line - n, a2 ? ",%u" : "%u", op.args[a2]);
+        std::snprintf(line + n, sizeof line - n, "]}");
+        emit(line, ud);
+    }
+}
+
+// ---- CUDA-side configuration ----
+int gehtp_cuda_set_device(int ordinal) {
+    if (g.dev_ok && g.device != ordinal) return -1;
+    g.device = ordinal;
+    return ensure_device(nullptr, 0) ? 0 : -1;
+}
+void gehtp_cuda_set_fusion(int on) {
+    if (g.opt_fuse != (on ? 1 : 0) && g.planned) drop_plan(true);
+    g.opt_fuse = on ? 1 : 0;
+}
+void gehtp_cuda_set_graph(int on) {
+    g.opt_graph = on ? 1 : 0;
+    if (!on && g.graph) { cudaGraphExecDestroy(g.graph); g.graph = nullptr; }
+}
+uint64_t gehtp_cuda_launch_count(void) { return g_launches; }
+uint32_t gehtp_cuda_fused_ops(void) { return g.fused_ops; }
+void* gehtp_cuda_stream(void) { return ensure_device(nullptr, 0) ? (void*)g.stream : nullptr; }
+void* gehtp_cuda_temp_dev(uint32_t id) { return (id < kMaxTemps && g.temp_cap[id]) ? g.temp_dev[id] : nullptr; }
+int gehtp_cuda_sync(void) {
+    if (!g.dev_ok) return -1;
+    cudaSetDevice(g.device);
+    return (int)cudaStreamSynchronize(g.stream);
+}
+const char* gehtp_cuda_last_error(void) { return g.last_error.c_str(); }
+size_t gehtp_w4a16_slot_bytes(uint32_t K, uint32_t N) { return (size_t)K * N / 2 + (size_t)2 * (K / GEHTP_W4_GROUP) * N; }
+
+}  // extern "C"

@@ -1,0 +1,31 @@
+// Fused decode attention over the KV ring (ops_attn_decode.cu).
+#pragma once
+#include "launchers.h"
+
+namespace gehtp {
+
+struct AttnDecodeArgs {
+    const uint16_t* q;         // [kv_heads_total * rep][hd], rotary already applied
+    const uint16_t* ring;      // KV ring of kvcache.h layout
+    const uint32_t* counter;   // device position counter (AUTO) or NULL
+    uint32_t n_kv;             // positions to attend when counter == NULL
+    const uint16_t* mask;      // additive fp16 mask per position, or NULL
+    uint32_t mask_seq_stride;  // elements between the masks of two sequences (0 = shared)
+    uint32_t kvh_per_seq;      // KV heads of one sequence (batch folds into the head dim)
+    float scale;               // score * scale, or score / scale when scale_div
+    int scale_div;
+    uint32_t rep;              // query heads per KV head (<= 16)
+    uint32_t kv_heads;         // KV heads per ring slot (= kv_heads_total)
+    uint32_t nslots;
+    uint32_t nsplit;           // context slices = gridDim.y
+    float* part_o;             // scratch [kv_heads_total][nsplit][rep][hd]
+    float* part_ml;            // scratch [kv_heads_total][nsplit][rep][2]
+};
+
+uint32_t attn_decode_pick_splits(uint32_t kv_heads_total, uint32_t max_positions);
+size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_t hd, uint32_t nsplit);
+// false: shape not handled (rep > 16 or head_dim not 64/128); nothing launched
+bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out,
+                   uint32_t kv_heads_total);
+
+}  // namespace gehtp

@@ -1,0 +1,46 @@
+// W4A16 launchers and the epilogue descriptor shared by the W4A16 kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include "launchers.h"
+
+namespace gehtp {
+
+// What happens to an fp32 accumulator on its way to memory.
+//   mode 0: y = f16(acc)
+//   mode 1: y = f16( f16(acc) + res )          (matmul followed by a residual ADD op;
+//           both fp16 roundings of the two-op form are kept)
+struct W4Epilogue {
+    int mode = 0;
+    const uint16_t* res = nullptr;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void w4_store(const W4Epilogue& ep, uint16_t* y, uint32_t m, uint32_t n,
+                                         uint32_t N, float acc) {
+    const size_t o = (size_t)m * N + n;
+    uint16_t h = __half_as_ushort(__float2half_rn(acc));
+    if (acc != acc) h = (uint16_t)(((__float_as_uint(acc) >> 16) & 0x8000u) | 0x7c00u);
+    if (ep.mode == 1) {
+        float s = __fadd_rn(__half2float(__ushort_as_half(h)),
+                            __half2float(__ushort_as_half(ep.res[o])));
+        h = __half_as_ushort(__float2half_rn(s));
+        if (s != s) h = (uint16_t)(((__float_as_uint(s) >> 16) & 0x8000u) | 0x7c00u);
+    }
+    y[o] = h;
+}
+#endif
+
+// nib: slot nibbles [K][N/2]; packed: K*N/2 bytes in the strip-major layout.
+void k_w4_repack(cudaStream_t st, const uint8_t* nib, uint32_t* packed, uint32_t K, uint32_t N);
+void k_w4_unpack_i8(cudaStream_t st, const uint32_t* packed, int8_t* out, uint32_t K, uint32_t N);
+// Streaming form, any M (intended for M <= 16; larger M re-reads the weights
+// from L2 once per 16 rows).
+void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
+                    uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep);
+// tcgen05 / TMEM form for M >= 128 (w4a16_gemm_sm100.cu). Returns false when
+// the shape is outside what it handles (the caller then uses the skinny form).
+bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,
+                        const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
+                        const W4Epilogue& ep);
+
+}  // namespace gehtp

@@ -1,0 +1,210 @@
+// Gated-delta-net ops: depthwise causal conv1d (whole sequence and one-token
+// step) and the chunked gated delta rule. Reference: exec_conv1d_ssm
+// (kernels/src/runtime/oplist_exec.c:1349-1376), conv1d_step_f16 and
+// delta_chunk_f16 / solve_tri_f16 (kernels/src/hvx/gdn_kern.c:14-38, 54-167;
+// formulas in kernels/include/gdn_sm.h:5-12).
+// Compiled with --fmad=false: the reference multiplies, rounds, then adds, and
+// each sum below runs in the reference's order so that results differ from it
+// only through expf.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace gehtp {
+
+// y[t,c] = sum_j w[j,c] * x[t-(k-1)+j, c]; input rows beyond seq-k+1 and
+// before 0 count as zero; no activation.
+__global__ void conv1d_ssm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
+                                  uint16_t* __restrict__ y, uint32_t seq, uint32_t C, uint32_t k) {
+    const int32_t in_rows = (seq >= k) ? (int32_t)(seq - k + 1) : 0;
+    const size_t total = (size_t)seq * C;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (size_t)gridDim.x * blockDim.x) {
+        uint32_t t = (uint32_t)(e / C), c = (uint32_t)(e % C);
+        float acc = 0.0f;
+        for (uint32_t j = 0; j < k; j++) {
+            int32_t src = (int32_t)t - (int32_t)(k - 1) + (int32_t)j;
+            if (src < 0 || src >= in_rows) continue;
+            acc += h2f(x[(size_t)src * C + c]) * h2f(w[(size_t)j * C + c]);
+        }
+        y[e] = f2h(acc);
+    }
+}
+
+void k_conv1d_ssm(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_t* y, uint32_t seq,
+                  uint32_t C, uint32_t k) {
+    size_t total = (size_t)seq * C;
+    if (!total) return;
+    size_t g = (total + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    conv1d_ssm_kernel<<<(unsigned)g, 256, 0, st>>>(x, w, y, seq, C, k);
+    g_launches++;
+}
+
+// One token: s = sum_{i<dc-1} w[i,c]*win[i,c] + w[dc-1,c]*x[c]; y = silu(s);
+// then the fp32 window shifts by one and takes x.
+__global__ void conv1d_step_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
+                                   uint16_t* __restrict__ y, float* __restrict__ win, uint32_t C,
+                                   uint32_t dc) {
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float xf = h2f(x[c]);
+    float s = 0.0f;
+    for (uint32_t i = 0; i + 1 < dc; i++) s += h2f(w[(size_t)i * C + c]) * win[(size_t)i * C + c];
+    s += h2f(w[(size_t)(dc - 1) * C + c]) * xf;
+    y[c] = f2h(s / (1.0f + expf(-s)));
+    for (uint32_t i = 0; i + 2 < dc; i++) win[(size_t)i * C + c] = win[(size_t)(i + 1) * C + c];
+    win[(size_t)(dc - 2) * C + c] = xf;
+}
+
+void k_conv1d_step(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_t* y, float* win,
+                   uint32_t C, uint32_t dc) {
+    conv1d_step_kernel<<<(C + 127) / 128, 128, 0, st>>>(x, w, y, win, C, dc);
+    g_launches++;
+}
+
+// Chunked gated delta rule, one CTA per head, c <= 64 tokens, state S[D][D]
+// fp32 updated in place. Shared memory: kf, qf, bm (v then b), u [c][D] fp32;
+// S [D][D] fp32 when D <= 128; L and T [c][c] fp16, later reused as QK fp32.
+template <bool S_SMEM>
+__global__ void __launch_bounds__(256)
+delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                   const uint16_t* __restrict__ q, const uint16_t* __restrict__ beta,
+                   const uint16_t* __restrict__ g, uint16_t* __restrict__ y, float* __restrict__ Sg,
+                   int c, int ntok, int D, int q_raw) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int h = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
+    float* kf = (float*)smem;
+    float* qf = kf + (size_t)c * D;
+    float* bm = qf + (size_t)c * D;
+    float* u = bm + (size_t)c * D;
+    float* G = u + (size_t)c * D;      // [64]
+    float* bj = G + 64;                // [64]
+    uint16_t* Lh = (uint16_t*)(bj + 64);  // [c][c]
+    uint16_t* T = Lh + 64 * 64;           // [c][c]
+    float* QK = (float*)Lh;               // [c][c] fp32, after T is dead
+    float* S = S_SMEM ? (float*)(T + 64 * 64) : Sg + (size_t)h * D * D;
+    float* Sglob = Sg + (size_t)h * D * D;
+
+    const uint16_t* kh = k + (size_t)h * ntok * D;
+    const uint16_t* vh = v + (size_t)h * ntok * D;
+    const uint16_t* qh = q + (size_t)h * ntok * D;
+    const uint16_t* bh = beta + (size_t)h * ntok;
+    const uint16_t* gh = g + (size_t)h * ntok;
+    uint16_t* yh = y + (size_t)h * ntok * D;
+    const float scale = q_raw ? 1.0f : 1.0f / sqrtf((float)D);
+
+    if (tid == 0) {
+        float acc = 0.0f;
+        for (int t = 0; t < c; t++) { acc += h2f(gh[t]); G[t] = acc; }
+    }
+    for (int t = tid; t < c; t += NT) bj[t] = h2f(bh[t]);
+    for (int e = tid; e < c * D; e += NT) {
+        kf[e] = h2f(kh[e]);
+        bm[e] = h2f(vh[e]);
+        qf[e] = h2f(qh[e]) * scale;
+    }
+    if (S_SMEM)
+        for (int e = tid; e < D * D; e += NT) S[e] = Sglob[e];
+    __syncthreads();
+
+    // L[j][i] = exp(G_j - G_i) * (k_j . k_i) * beta_j for i < j, else 0 (fp16)
+    for (int e = tid; e < c * c; e += NT) {
+        int j = e / c, i = e % c;
+        uint16_t r = 0;
+        if (i < j) {
+            float s = 0.0f;
+            for (int n = 0; n < D; n++) s += kf[j * D + n] * kf[i * D + n];
+            r = f2h(expf(G[j] - G[i]) * s * bj[j]);
+        }
+        Lh[j * c + i] = r;
+    }
+    __syncthreads();
+    // T = (I + L)^-1 by rows; each row needs the rows above it
+    for (int r = 0; r < c; r++) {
+        for (int j = tid; j < c; j += NT) {
+            uint16_t out = 0;
+            if (j <= r) {
+                float s = (r == j) ? 1.0f : 0.0f;
+                for (int i = j; i < r; i++) s -= h2f(Lh[r * c + i]) * h2f(T[i * c + j]);
+                out = f2h(s);
+            }
+            T[r * c + j] = out;
+        }
+        __syncthreads();
+    }
+    // b_j = beta_j (v_j - e^{G_j} S0 k_j), in place over v
+    for (int e = tid; e < c * D; e += NT) {
+        int j = e / D, m = e % D;
+        float sk = 0.0f;
+        for (int n = 0; n < D; n++) sk += S[m * D + n] * kf[j * D + n];
+        bm[e] = bj[j] * (bm[e] - expf(G[j]) * sk);
+    }
+    __syncthreads();
+    // u = T b
+    for (int e = tid; e < c * D; e += NT) {
+        int j = e / D, m = e % D;
+        float acc = 0.0f;
+        for (int i = 0; i <= j; i++) {
+            float tij = h2f(T[j * c + i]);
+            if (tij == 0.0f) continue;
+            acc += tij * bm[i * D + m];
+        }
+        u[e] = acc;
+    }
+    __syncthreads();
+    // QK[t][i] = exp(G_t - G_i) (q_t . k_i), i <= t (T and L are dead now)
+    for (int e = tid; e < c * c; e += NT) {
+        int t = e / c, i = e % c;
+        float qk = 0.0f;
+        if (i <= t) {
+            for (int n = 0; n < D; n++) qk += qf[t * D + n] * kf[i * D + n];
+            qk *= expf(G[t] - G[i]);
+        }
+        QK[e] = qk;
+    }
+    __syncthreads();
+    // y_t = e^{G_t} (S0 q_t) + sum_{i<=t} QK[t][i] u_i
+    for (int e = tid; e < c * D; e += NT) {
+        int t = e / D, m = e % D;
+        float s = 0.0f;
+        for (int n = 0; n < D; n++) s += S[m * D + n] * qf[t * D + n];
+        float acc = expf(G[t]) * s;
+        for (int i = 0; i <= t; i++) {
+            float qk = QK[t * c + i];
+            if (qk == 0.0f) continue;
+            acc += qk * u[i * D + m];
+        }
+        yh[e] = f2h(acc);
+    }
+    __syncthreads();
+    // S' = e^{G_c} S0 + sum_i e^{G_c - G_i} u_i k_i^T
+    const float eC = expf(G[c - 1]);
+    for (int e = tid; e < D * D; e += NT) {
+        int m = e / D, n = e % D;
+        float sv = S[e] * eC;
+        for (int i = 0; i < c; i++) {
+            float wu = expf(G[c - 1] - G[i]) * u[i * D + m];
+            if (wu == 0.0f) continue;
+            sv += wu * kf[i * D + n];
+        }
+        Sglob[e] = sv;
+    }
+}
+
+void k_delta_chunk(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_t* q,
+                   const uint16_t* beta, const uint16_t* g, uint16_t* y, float* S, uint32_t c,
+                   uint32_t ntok, uint32_t H, uint32_t D, uint32_t q_raw) {
+    size_t base = (size_t)4 * c * D * 4 + 128 * 4 + 2 * 64 * 64 * 2;
+    bool s_smem = base + (size_t)D * D * 4 <= 227 * 1024;
+    size_t smem = base + (s_smem ? (size_t)D * D * 4 : 0);
+    if (s_smem) {
+        cudaFuncSetAttribute(delta_chunk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        delta_chunk_kernel<true><<<H, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
+    } else {
+        cudaFuncSetAttribute(delta_chunk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        delta_chunk_kernel<false><<<H, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
+    }
+    g_launches++;
+}
+
+}  // namespace gehtp

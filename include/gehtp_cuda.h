@@ -1,0 +1,196 @@
+/* libgehtp_cuda.so — CUDA (sm_100a) executor for WTOP runlists.
+ *
+ * The wt_exec_* entry points below are the ones the GEHTP runners bind
+ * (kernels/include/oplist_exec.h:31-114 in the reference), with the same
+ * argument meaning, return codes and lifetime rules. The op list, the slot
+ * table and the TEMPOFF / STATE tables are consumed as they are; temps live in
+ * one device arena, slots are uploaded once, states stay resident across runs.
+ *
+ * Return convention of the run calls: 0 = every op succeeded; >0 = 1-based
+ * index of the op that failed; -1 = range / TEMPOFF / STATE table error.
+ * `err` (may be NULL) receives a short reason. One engine per process, one
+ * caller thread (the reference has the same rule).
+ *
+ * The library never computes on the CPU: without a usable CUDA device every
+ * run call fails with "no CUDA device".
+ */
+#ifndef GEHTP_B200_GEHTP_CUDA_H
+#define GEHTP_B200_GEHTP_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include "wtop_format.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- engine */
+
+/* oplist_exec.h:31 — run every op of `b`. */
+int wt_exec_run(const struct wt_blob* b, uint32_t* engine_m,
+                int64_t* op_us, char* err, size_t errn);
+
+/* oplist_exec.h:66 — run ops [first, first+count). Running the list in
+ * pieces leaves the same bytes in every temp as one whole run. */
+int wt_exec_run_range(const struct wt_blob* b, uint32_t first, uint32_t count,
+                      uint32_t* engine_m, int64_t* op_us, char* err, size_t errn);
+
+/* oplist_exec.h:75 — as wt_exec_run, with the EXT_IN slot read from host
+ * memory `in_ptr` and temp `out_temp` copied to host memory `out_ptr` after
+ * the run (its last written size). Either pointer may be NULL. */
+int wt_exec_run_io(const struct wt_blob* b, const void* in_ptr, void* out_ptr,
+                   uint32_t out_temp, uint32_t* engine_m, int64_t* op_us,
+                   char* err, size_t errn);
+
+/* oplist_exec.h:35-38 — host view of a temp. The pointer is a pinned host
+ * mirror refreshed from the device by this call; it stays valid until
+ * wt_exec_shutdown() or the next wt_exec_temp() of the same id. */
+uint8_t* wt_exec_temp(uint32_t id);
+uint32_t wt_exec_temp_bytes(uint32_t id);
+uint32_t wt_exec_temp_last_bytes(uint32_t id);
+
+/* oplist_exec.h:43 — drops the plan, the temp arena and uploaded slots.
+ * Persistent states survive (decode semantics); call on PASS and FAIL paths. */
+void wt_exec_shutdown(void);
+
+/* oplist_exec.h:48 — zero every persistent state and its position counter. */
+void wt_exec_state_reset(void);
+
+/* oplist_exec.h:56 — static temp pool supplied by the caller. On the GPU the
+ * pool memory itself is device memory owned by the engine, so `base` is only
+ * tested for NULL; `offsets[id]` (0xFFFFFFFF = not in table) and the two
+ * capacities are honoured. NULL/NULL restores the default. */
+void wt_exec_pool_init(uint8_t* base, uint32_t total_cap, uint32_t static_cap,
+                       const uint32_t* offsets);
+
+/* oplist_exec.h:62-68 */
+struct wt_exec_stats {
+    uint32_t ops, nop, matmul, rmsnorm, silu, pin, pin_skipped;
+    uint32_t im2col, conv2d, add, spill, fill, transpose;
+};
+void wt_exec_get_stats(struct wt_exec_stats* st);
+
+/* oplist_exec.h:81 — base of the external weight file image (host memory)
+ * for slots marked WT_SLOT_EXT_WGT. Borrowed for the life of the process. */
+void wt_exec_set_ext_weights(const void* wgt_ptr);
+
+/* oplist_exec.h:87-95 — per-op timestamps. Tensor-core ops report
+ * WT_ENG_HMX, other GPU kernels WT_ENG_HVX, host-only bookkeeping ops
+ * WT_ENG_SCALAR. Registering a buffer (or passing op_us) makes the engine
+ * synchronise after every op; without either, ops are queued back to back. */
+enum wt_engine { WT_ENG_SCALAR = 0, WT_ENG_HVX = 1, WT_ENG_HMX = 2 };
+struct wt_op_ts {
+    uint32_t start_us, dur_us, dma_us, dma_bytes, engine;
+};
+void wt_exec_set_ts(struct wt_op_ts* buf, uint32_t cap);
+
+/* oplist_exec.h:101 — per-op trace lines (to $GEHTP_TRACE_FILE or
+ * /tmp/gehtp_optrace.txt). Off by default here. */
+void wt_exec_set_trace(int on);
+
+/* oplist_exec.h:108 — "opidx:temp,opidx:temp": after op `opidx` of a range
+ * succeeds, temp `temp` is written to /tmp/hook_<idx>_<temp>.f16.raw.
+ * Falls back to $GEHTP_HOOK when never set. */
+void wt_exec_set_hook(const char* spec);
+
+/* oplist_exec.h:112 — one JSON line per slot and op through `emit`. */
+void wt_w3_report(const char* blob_name, const uint8_t* buf, size_t size,
+                  const struct wt_blob* w,
+                  void (*emit)(const char* line, void* ud), void* ud);
+
+/* ------------------------------------------------ CUDA-side configuration
+ * None of these has a counterpart in the reference; they select how the same
+ * op list is run on GPUs. */
+
+/* Device ordinal used by the engine (default: $GEHTP_CUDA_DEVICE or 0).
+ * Call before the first run. Returns 0, or -1 with no such device. */
+int gehtp_cuda_set_device(int ordinal);
+
+/* 1 = recognise op chains at plan time and run each as one kernel (attention
+ * over the KV ring, rotary embedding, SwiGLU, norm+matmul prologues).
+ * 0 = one kernel per op (every temp materialised; used for op-by-op parity).
+ * Default 1, or $GEHTP_CUDA_FUSE. */
+void gehtp_cuda_set_fusion(int on);
+
+/* 1 = after a first eager run of a blob, replay whole runs as one CUDA graph.
+ * Default 1, or $GEHTP_CUDA_GRAPH. Timing (op_us / set_ts), hooks and traces
+ * force eager execution for that run. */
+void gehtp_cuda_set_graph(int on);
+
+/* Tensor parallelism inside one node: this process is `rank` of `world`.
+ * `nccl_unique_id` is the 128-byte id made by rank 0 and sent to the others by
+ * the caller (the engine does no rendezvous of its own). Column- and
+ * row-parallel matmuls are found from the op list's dataflow. Returns 0 or -1. */
+int gehtp_cuda_tp_init(int rank, int world, const void* nccl_unique_id, size_t id_bytes);
+int gehtp_cuda_tp_unique_id(void* out_id, size_t id_bytes);
+void gehtp_cuda_tp_shutdown(void);
+/* Ops whose first output is a partial sum over the ranks (the outputs of
+ * row-parallel projections): the engine all-reduces it in place right after
+ * the op. Indices come from the blob's sideband manifest. */
+int gehtp_cuda_tp_allreduce_after(const uint32_t* op_idx, uint32_t n);
+
+/* Kernels launched by the engine since the process started. */
+uint64_t gehtp_cuda_launch_count(void);
+/* Number of ops of the current plan replaced by fused launches. */
+uint32_t gehtp_cuda_fused_ops(void);
+/* Device pointer / stream the engine uses (so a host that owns device memory,
+ * e.g. a bench, can time on the right stream). */
+void* gehtp_cuda_stream(void);
+void* gehtp_cuda_temp_dev(uint32_t id);
+/* Wait for every queued op. Returns 0 or the CUDA error code. */
+int gehtp_cuda_sync(void);
+const char* gehtp_cuda_last_error(void);
+
+/* Device-resident I/O for hosts that keep buffers on the GPU: like
+ * wt_exec_run_io but `in_dev` / `out_dev` are device pointers and nothing is
+ * synchronised before return. */
+int gehtp_cuda_run_dev(const struct wt_blob* b, const void* in_dev, void* out_dev,
+                       uint32_t out_temp, char* err, size_t errn);
+
+/* ------------------------------------------------------- W4A16 group-64
+ * Weight slot form accepted by opcode 1 on this executor (the reference's
+ * opcode 1 is an HMX-specific integer contract found by slot size,
+ * oplist_exec.c:438-529; it selects W4A16 when the weight slot holds K*N/2
+ * bytes, wtop_ops/op_matmul.cpp:40-44):
+ *
+ *   slot = nibbles[K][N/2] then scales[K/64][N], len = K*N/2 + 2*(K/64)*N
+ *   byte[k][j] = q[k][2j] | q[k][2j+1] << 4      (low nibble = even column;
+ *                nibble order of kernels/host/vendor/weight_pack.cc:114)
+ *   w[k][n] = fp16( (q[k][n] - 8) * scale[k/64][n] ),  y = fp16( sum_k a*w ) with
+ *   fp32 accumulation. K % 64 == 0, N % 16 == 0.
+ *
+ * Op args: [a_ref, w_ref, out_temp, M, K, N]; a_ref / w_ref decode like every
+ * other ref. A weight slot of exactly K*N/2 bytes (the legacy side-band form)
+ * is rejected with "legacy W4A16 slot form unsupported on CUDA". */
+#define GEHTP_W4_GROUP 64u
+size_t gehtp_w4a16_slot_bytes(uint32_t K, uint32_t N);
+
+/* Host-pointer kernel entry points: each copies its operands to the device,
+ * runs the same kernel the engine uses, and copies the result back. For
+ * tests and small tools; 0 on success, -1 otherwise (see gehtp_cuda_last_error).
+ *
+ * gehtp_w4a16_matmul: `w_slot` in the slot form above. `path`: 0 = engine's
+ * choice by M, 1 = streaming GEMV (mma.sync), 2 = tcgen05 GEMM. */
+int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y_f16,
+                       uint32_t M, uint32_t K, uint32_t N, int path);
+/* Integer q-8 of every weight, read back out of the device-side packed
+ * layout: out_i8[k*N + n]. Proves the repack is lossless. */
+int gehtp_w4a16_unpack(const uint8_t* w_slot, int8_t* out_i8, uint32_t K, uint32_t N);
+/* y = x / sqrt(mean(x^2) + 1e-6) * gamma (+ beta); rows x width (opcode 25,
+ * oplist_exec.c:1817-1872). beta may be NULL. */
+int gehtp_rmsnorm(const uint16_t* x, const uint16_t* gamma, const uint16_t* beta,
+                  uint16_t* y, uint32_t rows, uint32_t width);
+/* Decode attention straight off a KV ring (layout of kvcache.h:19-47:
+ * slot = [K face kv_heads*hd][V face kv_heads*hd], position p in slot
+ * p % nslots): out[h] = softmax(q[h]·K^T * scale + mask) · V for n_kv
+ * positions; head h reads KV head h / (n_heads/kv_heads). mask (n_kv f16,
+ * additive) may be NULL. */
+int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t* mask,
+                      uint16_t* out, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
+                      uint32_t n_kv, uint32_t nslots, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
