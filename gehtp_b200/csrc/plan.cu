@@ -704,10 +704,10 @@ int load_tempoff(const wt_blob* b, char* err, size_t errn) {
 }
 
 // STATE table: [n] n x {bytes}; buffers are zeroed once and live until the
-// process ends (wt_exec_load_states, oplist_exec.c:2071-2102). A state may be
-// up to 4 GiB - 1 here (the reference stops at 1 GiB).
+// process ends or a blob with a different table is run
+// (wt_exec_load_states, oplist_exec.c:2071-2102). A state may be up to
+// 4 GiB - 1 here (the reference stops at 1 GiB).
 int load_states(const wt_blob* b, char* err, size_t errn) {
-    if (g.states_loaded) return 0;
     for (uint32_t s = 0; s < b->n_slots; s++) {
         if (b->slots[s].addr != WT_SLOT_STATE) continue;
         const uint8_t* p = b->weight_base + b->slots[s].offset;
@@ -718,18 +718,31 @@ int load_states(const wt_blob* b, char* err, size_t errn) {
             std::snprintf(err, errn, "state slot table bad (n=%u len=%u)", n, len);
             return -1;
         }
+        // Same table as the states already resident: keep them (decode semantics).
+        // A different table means a different model: the old states are released.
+        bool same = g.states_loaded && g.n_states == n;
+        for (uint32_t i = 0; same && i < n; i++) same = g.st_bytes[i] == wt_rd_u32(p + 4 + (size_t)i * 4);
+        if (same) return 0;
+        for (uint32_t i = 0; i < g.n_states; i++) {
+            cudaFree(g.st_buf[i]); g.st_buf[i] = nullptr;
+            if (g.kv[i].posmap) cudaFree(g.kv[i].posmap);
+            g.kv[i] = KvGeom();
+        }
+        g.n_states = 0;
+        cudaMemsetAsync(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t), g.stream);
         for (uint32_t i = 0; i < n; i++) {
             uint32_t bytes = wt_rd_u32(p + 4 + (size_t)i * 4);
             if (bytes == 0) { std::snprintf(err, errn, "state %u bytes bad %u", i, bytes); return -1; }
             if (cudaMalloc(&g.st_buf[i], bytes) != cudaSuccess) {
+                cudaGetLastError();
                 std::snprintf(err, errn, "state %u alloc %u", i, bytes);
                 return -1;
             }
             cudaMemsetAsync(g.st_buf[i], 0, bytes, g.stream);
             g.st_bytes[i] = bytes;
             g.st_count[i] = 0;
+            g.n_states = i + 1;
         }
-        g.n_states = n;
         break;
     }
     g.states_loaded = true;
