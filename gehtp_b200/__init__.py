@@ -22,7 +22,7 @@ def lib():
                 "libgehtp_cuda.so is not built (run `python -m gehtp_b200.build`); "
                 "this package has no CPU fallback")
         from .wtop import bind
-        _lib = bind(ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL))
+        _lib = bind(ctypes.CDLL(LIB_PATH))
     return _lib
 
 
