@@ -36,6 +36,7 @@ struct PlanOp {
     std::function<void(cudaStream_t)> fused;
     uint32_t span = 0;
     uint32_t stat = 0;          // index into the stats struct, 0 = none
+    bool uses_internal = false; // touches a temp that has no memory in a fused plan
 };
 
 struct W4Packed {
@@ -104,11 +105,19 @@ struct Engine {
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_out_temp = kNoOff;
     bool graph_has_in = false, graph_has_out = false;
+    const void* graph_in_dev = nullptr;
+    void* graph_out_dev = nullptr;
     uint32_t warm_runs = 0;
     unsigned long long graph_launches = 0;  // kernels inside the captured graph
 
+    // per-unit CUDA event profiling (gehtp_cuda_run_profiled)
+    struct ProfEvent { uint32_t op; cudaEvent_t e0, e1; };
+    float* prof_ms = nullptr;
+    std::vector<ProfEvent> prof_events;
+
     // options
     int opt_fuse = 1, opt_graph = 1, trace_on = 0;
+    bool force_unfused = false;   // a run needed an op that the fused plan gave no memory
     const char* hook_spec = nullptr;
     wt_op_ts* ts_buf = nullptr;
     uint32_t ts_cap = 0;
@@ -127,6 +136,8 @@ bool ensure_device(char* err, size_t errn);
 int build_plan(const wt_blob* b, char* err, size_t errn);
 void drop_plan(bool keep_states);
 // fuse.cu
-void fuse_plan(const wt_blob* b);
+void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal);
+void fuse_materialize(const wt_blob* b);
+void fuse_release();
 
 }  // namespace gehtp

@@ -120,8 +120,10 @@ static void bump_stat(uint32_t stat) {
 
 static int ensure_plan(const wt_blob* b, char* err, size_t errn) {
     if (g.planned && (g.blob != b || g.blob_wbase != b->weight_base || g.blob_nops != b->n_ops ||
-                      g.blob_nslots != b->n_slots))
+                      g.blob_nslots != b->n_slots)) {
         drop_plan(true);
+        g.force_unfused = false;
+    }
     if (g.planned) return 0;
     int rc = build_plan(b, err, errn);
     if (rc != 0) { drop_plan(true); if (err) g.last_error = err; }
@@ -161,12 +163,16 @@ static void note_outputs(const PlanOp& p) {
     }
 }
 
+constexpr int kNeedUnfused = -1000;
+
 // Queues ops [first, first+count) on the engine stream. Returns 0 or the
 // 1-based index of the op that failed before launch.
 static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sync, uint32_t* engine_m,
                        int64_t* op_us, char* err, size_t errn) {
     const int64_t t_run0 = now_us();
     const bool hooks = hooks_active();
+    std::vector<PlanOp*> pending;
+    if (hooks) fuse = false;   // dumps need every intermediate temp
     for (uint32_t ii = 0; ii < count;) {
         const uint32_t i = first + ii;
         PlanOp& p = g.plan[i];
@@ -175,18 +181,34 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
         if (use_fused) span = p.span;
         const int64_t t0 = now_us();
         int rc = 0;
+        uint32_t fail = i;
         if (g.trace_on) trace_line("pre%u code=%u fused=%d pool=%lld\n", ii, g.blob->ops[i].opcode, use_fused ? 1 : 0, (long long)g.arena_bytes);
         for (uint32_t k = 0; k < span && !rc; k++) {
             PlanOp& q = g.plan[i + k];
-            if (q.rc) { set_err(err, errn, q.err.c_str()); rc = -1; break; }
-            if (host_precheck(q, err, errn)) { rc = -1; break; }
+            if (!use_fused && q.uses_internal) return kNeedUnfused;
+            if (q.rc) { set_err(err, errn, q.err.c_str()); rc = -1; fail = i + k; break; }
+            if (host_precheck(q, err, errn)) { rc = -1; fail = i + k; break; }
             if (q.w4_m) *engine_m = q.w4_m;
             bump_stat(q.stat);
             g.st.ops++;
             note_outputs(q);
-            if (!use_fused && q.launch) q.launch(g.stream);
+            pending.push_back(&q);
         }
-        if (!rc && use_fused) p.fused(g.stream);
+        {
+            cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+            if (g.prof_ms && !rc) {
+                cudaEventCreate(&ev0); cudaEventCreate(&ev1);
+                g.prof_events.push_back({i, ev0, ev1});
+                cudaEventRecord(ev0, g.stream);
+            }
+            if (!rc) {
+                if (use_fused) p.fused(g.stream);
+                else for (PlanOp* q : pending) if (q->launch) q->launch(g.stream);
+            }
+            if (ev1) cudaEventRecord(ev1, g.stream);
+            pending.clear();
+        }
+
         if (!rc && (per_op_sync || hooks)) {
             cudaError_t ce = cudaStreamSynchronize(g.stream);
             if (ce != cudaSuccess) { set_err(err, errn, cudaGetErrorString(ce)); rc = -1; }
@@ -204,7 +226,7 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
             }
         }
         if (g.trace_on) trace_line("op%u code=%u rc=%d us=%lld\n", ii, g.blob->ops[i].opcode, rc, (long long)(t1 - t0));
-        if (rc) return (int)i + 1;
+        if (rc) return (int)fail + 1;
         ii += span;
     }
     return 0;
@@ -256,11 +278,16 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
     const bool timing = op_us || g.ts_buf;
     const bool whole = first == 0 && count == b->n_ops;
     const bool has_in = in_host || in_dev;
-    const bool eager_only = timing || hooks_active() || g.trace_on || !g.opt_graph || !whole || in_dev || out_dev;
+    const bool eager_only = timing || hooks_active() || g.trace_on || !g.opt_graph || !whole || g.prof_ms;
 
     int rc = 0;
-    if (!eager_only && g.graph && g.graph_out_temp == out_temp && g.graph_has_in == has_in &&
-        g.graph_has_out == (out_host != nullptr)) {
+    if (!eager_only && g.graph && (g.graph_out_temp != out_temp || g.graph_has_in != has_in ||
+                                   g.graph_has_out != (out_host != nullptr) || g.graph_in_dev != in_dev ||
+                                   g.graph_out_dev != out_dev)) {
+        cudaGraphExecDestroy(g.graph);   // same blob, different I/O binding: capture again
+        g.graph = nullptr;
+    }
+    if (!eager_only && g.graph) {
         // replay: host bookkeeping first, then one launch
         for (uint32_t i = 0; i < b->n_ops; i++) {
             PlanOp& q = g.plan[i];
@@ -277,6 +304,7 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
         }
         cudaGraphLaunch(g.graph, g.stream);
         g_launches += g.graph_launches;
+        if (!sync_end) return 0;
         rc = finish_run(err, errn);
         if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
         return rc;
@@ -303,9 +331,41 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
     const unsigned long long launches0 = g_launches;
     if (has_in) stage_inputs(b, in_host, in_dev);
     rc = queue_range(first, count, g.opt_fuse != 0, timing, engine_m, op_us, err, errn);
+    if (rc == kNeedUnfused) {
+        // an op inside a fused chain has to run on its own: plan again with every temp in memory
+        if (capture) { cudaGraph_t gr = nullptr; cudaStreamEndCapture(g.stream, &gr); if (gr) cudaGraphDestroy(gr); cudaGetLastError(); }
+        cudaStreamSynchronize(g.stream);
+        g.force_unfused = true;
+        auto old_ext = std::move(g.d_ext);   // injected inputs and temps written so far outlive the re-plan
+        g.d_ext.clear();
+        uint8_t* old_arena = g.d_arena;
+        g.d_arena = nullptr;
+        std::vector<uint8_t*> old_dev(g.temp_dev, g.temp_dev + kMaxTemps);
+        std::vector<uint32_t> old_cap(g.temp_cap, g.temp_cap + kMaxTemps), old_last(g.temp_last, g.temp_last + kMaxTemps);
+        drop_plan(true);
+        int prc = ensure_plan(b, err, errn);
+        for (uint32_t t = 0; prc == 0 && t < kMaxTemps; t++) {
+            if (!old_cap[t] || !old_dev[t] || !g.temp_dev[t]) continue;
+            cudaMemcpyAsync(g.temp_dev[t], old_dev[t], old_cap[t], cudaMemcpyDeviceToDevice, g.stream);
+            g.temp_cap[t] = old_cap[t];
+            g.temp_last[t] = old_last[t];
+        }
+        for (auto& kv : old_ext) {
+            auto it = g.d_ext.find(kv.first);
+            if (prc == 0 && it != g.d_ext.end())
+                cudaMemcpyAsync(it->second, kv.second, b->slots[kv.first].len, cudaMemcpyDeviceToDevice, g.stream);
+        }
+        cudaStreamSynchronize(g.stream);
+        for (auto& kv : old_ext) cudaFree(kv.second);
+        if (old_arena) cudaFree(old_arena);
+        if (prc != 0) return -1;
+        return run_impl(b, first, count, in_host, in_dev, out_host, out_dev, out_temp, sync_end, engine_m, op_us, err, errn);
+    }
     if (capture) {
         if (rc == 0 && out_host && out_temp < kMaxTemps && g.temp_cap[out_temp])
             cudaMemcpyAsync(g.h_out, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToHost, g.stream);
+        if (rc == 0 && out_dev && out_temp < kMaxTemps && g.temp_cap[out_temp])
+            cudaMemcpyAsync(out_dev, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToDevice, g.stream);
         cudaGraph_t graph = nullptr;
         cudaError_t ce = cudaStreamEndCapture(g.stream, &graph);
         if (rc != 0 || ce != cudaSuccess || !graph) {
@@ -328,7 +388,9 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
         }
         g.graph_launches = g_launches - launches0;
         g.graph_out_temp = out_temp; g.graph_has_in = has_in; g.graph_has_out = out_host != nullptr;
+        g.graph_in_dev = in_dev; g.graph_out_dev = out_dev;
         cudaGraphLaunch(g.graph, g.stream);
+        if (!sync_end) return 0;
         rc = finish_run(err, errn);
         if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
         return rc;
@@ -404,6 +466,7 @@ void wt_exec_shutdown(void) {
     cudaSetDevice(g.device);
     cudaStreamSynchronize(g.stream);
     drop_plan(true);
+    g.force_unfused = false;
     g.user_pool = false;
     g.user_off.clear();
 }
@@ -471,8 +534,9 @@ int gehtp_cuda_set_device(int ordinal) {
     return ensure_device(nullptr, 0) ? 0 : -1;
 }
 void gehtp_cuda_set_fusion(int on) {
-    if (g.opt_fuse != (on ? 1 : 0) && g.planned) drop_plan(true);
+    if ((g.opt_fuse != (on ? 1 : 0) || g.force_unfused) && g.planned) drop_plan(true);
     g.opt_fuse = on ? 1 : 0;
+    g.force_unfused = false;
 }
 void gehtp_cuda_set_graph(int on) {
     g.opt_graph = on ? 1 : 0;
@@ -488,6 +552,77 @@ int gehtp_cuda_sync(void) {
     return (int)cudaStreamSynchronize(g.stream);
 }
 const char* gehtp_cuda_last_error(void) { return g.last_error.c_str(); }
+// Eager run with a CUDA event pair around every launch unit; op_ms[i] gets the
+// device time of the unit that starts at op i (0 for ops inside a fused unit).
+int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_t out_temp, float* op_ms,
+                            uint32_t cap, char* err, size_t errn) {
+    std::memset(&g.st, 0, sizeof g.st);
+    if (!b || !op_ms) { set_err(err, errn, "null argument"); return -1; }
+    for (uint32_t i = 0; i < cap; i++) op_ms[i] = 0.0f;
+    g.prof_ms = op_ms;
+    g.prof_events.clear();
+    int rc = run_impl(b, 0, b->n_ops, in_ptr, nullptr, nullptr, nullptr, out_temp, true, nullptr, nullptr, err, errn);
+    g.prof_ms = nullptr;
+    for (auto& e : g.prof_events) {
+        float ms = 0.0f;
+        if (rc == 0 && e.op < cap && cudaEventElapsedTime(&ms, e.e0, e.e1) == cudaSuccess) op_ms[e.op] = ms;
+        cudaEventDestroy(e.e0); cudaEventDestroy(e.e1);
+    }
+    g.prof_events.clear();
+    return rc;
+}
+
+// Loads `bytes` of a persistent state from host or device memory and, for a KV
+// state, marks positions [0, n_positions) as resident (ring slot p holds
+// position p) and sets the state's position counter to n_positions.
+int gehtp_cuda_state_load(const struct wt_blob* b, uint32_t idx, const void* src, size_t bytes, int src_is_device,
+                          uint32_t kv_elems, uint32_t n_positions, char* err, size_t errn) {
+    if (!ensure_device(err, errn)) return -1;
+    if (b && ensure_plan(b, err, errn) != 0) return -1;
+    if (idx >= g.n_states || bytes > g.st_bytes[idx]) { set_err(err, errn, "state load: bad index or size"); return -1; }
+    if (src && bytes)
+        cudaMemcpyAsync(g.st_buf[idx], src, bytes, src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, g.stream);
+    if (kv_elems) {
+        KvGeom& k = g.kv[idx];
+        if (!k.ready) {
+            uint32_t slot_bytes = kv_elems * 4u;
+            if (slot_bytes < 256u || (slot_bytes & 127u) || g.st_bytes[idx] % slot_bytes) { set_err(err, errn, "state load: kv geometry bad"); return -1; }
+            k.slot_bytes = slot_bytes; k.nslots = g.st_bytes[idx] / slot_bytes;
+            if (cudaMalloc(&k.posmap, (size_t)k.nslots * 4) != cudaSuccess) { set_err(err, errn, "kv posmap alloc"); return -1; }
+            k.ready = true;
+        }
+        if (n_positions > k.nslots) { set_err(err, errn, "state load: more positions than ring slots"); return -1; }
+        std::vector<uint32_t> pm(k.nslots, 0xFFFFFFFFu);
+        for (uint32_t p = 0; p < n_positions; p++) pm[p] = p;
+        cudaMemcpyAsync(k.posmap, pm.data(), (size_t)k.nslots * 4, cudaMemcpyHostToDevice, g.stream);
+        cudaMemcpyAsync(g.d_st_count + idx, &n_positions, 4, cudaMemcpyHostToDevice, g.stream);
+        g.st_count[idx] = n_positions;
+        cudaStreamSynchronize(g.stream);
+    }
+    cudaError_t ce = cudaStreamSynchronize(g.stream);
+    if (ce != cudaSuccess) { set_err(err, errn, cudaGetErrorString(ce)); return -1; }
+    return 0;
+}
+
+// Sets the position counter of a KV state (positions at or past it stay in the
+// ring but are no longer attended; the next append overwrites them).
+int gehtp_cuda_state_set_count(uint32_t idx, uint32_t n_positions) {
+    if (!g.dev_ok || idx >= g.n_states || !g.kv[idx].ready || n_positions > g.kv[idx].nslots) return -1;
+    cudaSetDevice(g.device);
+    cudaMemcpyAsync(g.d_st_count + idx, &n_positions, 4, cudaMemcpyHostToDevice, g.stream);
+    cudaStreamSynchronize(g.stream);
+    g.st_count[idx] = n_positions;
+    return 0;
+}
+
+// Copies a persistent state to host memory (bytes <= its size).
+int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes) {
+    if (!g.dev_ok || idx >= g.n_states || bytes > g.st_bytes[idx]) return -1;
+    cudaSetDevice(g.device);
+    cudaStreamSynchronize(g.stream);
+    return cudaMemcpy(dst, g.st_buf[idx], bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+
 size_t gehtp_w4a16_slot_bytes(uint32_t K, uint32_t N) { return (size_t)K * N / 2 + (size_t)2 * (K / GEHTP_W4_GROUP) * N; }
 
 }  // extern "C"

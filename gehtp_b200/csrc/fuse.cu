@@ -1,5 +1,411 @@
-// Plan-time fusion of op chains into single launches (filled in below).
+// Plan-time fusion: recognises op chains of the runlist and replaces each by
+// one or two launches. Three chains are handled, all in the shape the
+// reference's emitter decomposes ONNX graphs into (one op per node):
+//
+//   attention step   SPLIT x3, rotary on q and k (mul / slice / slice / neg /
+//                    concat / mul / add, twice), KV_APPEND (AUTO position),
+//                    KV_GATHER K^T and V, batched MATMUL_F16 scores, BINARY
+//                    scale by a broadcast constant, ADD mask, SOFTMAX, batched
+//                    MATMUL_F16 with V           -> rope+append kernel, split-KV
+//                                                   attention kernel, merge kernel
+//   SwiGLU           W4A16 gate, UNARY sigmoid, BINARY mul, W4A16 up, BINARY mul
+//                                                -> one pass over both matrices
+//   residual + norm  ADD followed by RMSNORM2 of its result -> one kernel
+//
+// A chain is fused only when every intermediate temp is consumed inside the
+// chain and the chain's ops are contiguous in the list. Temps that exist only
+// inside fused chains get no arena memory; running such an op on its own
+// (run_range pieces, dump hooks) makes the engine rebuild the plan unfused.
+#include <algorithm>
+#include <cstring>
 #include "engine.h"
+#include "launchers_attn.h"
+
 namespace gehtp {
-void fuse_plan(const wt_blob* b) { (void)b; }
+
+namespace {
+
+struct Graph {
+    const wt_blob* b;
+    std::vector<std::vector<uint32_t>> users;   // op -> ops reading one of its outputs
+    std::vector<int> producer_of_arg[WT_MAX_ARGS];  // [arg][op] -> producing op or -1
+};
+
+// argument positions that read a tensor, per opcode
+int input_args(const wt_op& op, int out[8]) {
+    int n = 0;
+    auto add = [&](int i) { out[n++] = i; };
+    switch (op.opcode) {
+    case OP_MATMUL_W4A16: case OP_ADD_F16: case OP_GATHER_F16: case OP_KV_APPEND_F16:
+    case OP_MATMUL_F16: case OP_MATMUL_F16_SPLIT: case OP_CONV1D_SSM_STEP_F16:
+        add(0); add(1); break;
+    case OP_BINARY_F16: add(0); add(1); if (op.args[4] == 8) add(2); break;
+    case OP_SCATTER_ND_F16: add(0); add(1); add(2); break;
+    case OP_DELTA_CHUNK_F16: for (int i = 0; i < 5; i++) add(i); break;
+    case OP_CONCAT_F16: for (uint32_t i = 0; i < op.args[10] && i < 4; i++) add((int)i); break;
+    case OP_SILU_F16: case OP_UNARY_F16: case OP_SOFTMAX_F16: case OP_STRIDED_SLICE_F16: case OP_SPLIT_F16:
+    case OP_REDUCE_F16: case OP_CUMSUM_F32: case OP_CONV1D_SSM_F16: case OP_ARGMAX_F16: case OP_RMSNORM2_F16:
+    case OP_BROADCAST_F16: case OP_TRANSPOSE_GEN_F16: case OP_PAD_F16: case OP_TRANSPOSE_F16: case OP_IM2COL:
+    case OP_CONV2D_F16: case OP_SPILL: case OP_DMA:
+        add(0); break;
+    default: break;
+    }
+    return n;
 }
+
+bool is_temp_ref(uint32_t a) { return (a & 0xC000u) == 0 && a < kMaxTemps; }
+
+void build_graph(const wt_blob* b, const std::vector<PlanOp>& meas, Graph& G) {
+    G.b = b;
+    G.users.assign(b->n_ops, {});
+    for (auto& v : G.producer_of_arg) v.assign(b->n_ops, -1);
+    std::vector<int> cur(kMaxTemps, -1);
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        const wt_op& op = b->ops[i];
+        int ia[8];
+        int n = input_args(op, ia);
+        for (int k = 0; k < n; k++) {
+            uint32_t a = op.args[ia[k]];
+            if (!is_temp_ref(a) || cur[a] < 0) continue;
+            G.producer_of_arg[ia[k]][i] = cur[a];
+            G.users[cur[a]].push_back(i);
+        }
+        for (int k = 0; k < 2; k++)
+            if (meas[i].out_id[k] != kNoOff) cur[meas[i].out_id[k]] = (int)i;
+    }
+}
+
+struct Rope {
+    bool ok = false;
+    int src_op = -1;          // producer of x
+    uint32_t x, cos_b, sin_b, rows, hd, out_op;
+    std::vector<uint32_t> ops;
+};
+
+// out = ADD(xc, xs); xc = MUL(x, cos); xs = MUL(CONCAT(NEG(SLICE(x, h:)), SLICE(x, :h)), sin)
+Rope match_rope(const Graph& G, int add_op) {
+    Rope r;
+    const wt_blob* b = G.b;
+    if (add_op < 0 || b->ops[add_op].opcode != OP_ADD_F16) return r;
+    int xc = G.producer_of_arg[0][add_op], xs = G.producer_of_arg[1][add_op];
+    if (xc < 0 || xs < 0) return r;
+    auto is_mul = [&](int i) { return b->ops[i].opcode == OP_BINARY_F16 && b->ops[i].args[4] == 2; };
+    if (!is_mul(xc) || !is_mul(xs)) return r;
+    int cat = G.producer_of_arg[0][xs];
+    if (cat < 0 || b->ops[cat].opcode != OP_CONCAT_F16) return r;
+    const wt_op& c = b->ops[cat];
+    if (c.args[10] != 2 || c.args[12] != c.args[13]) return r;
+    uint32_t h = c.args[12], hd = 2 * h;
+    int neg = G.producer_of_arg[0][cat], x1 = G.producer_of_arg[1][cat];
+    if (neg < 0 || x1 < 0 || b->ops[neg].opcode != OP_UNARY_F16 || b->ops[neg].args[3] != 0) return r;
+    int x2 = G.producer_of_arg[0][neg];
+    if (x2 < 0 || b->ops[x1].opcode != OP_STRIDED_SLICE_F16 || b->ops[x2].opcode != OP_STRIDED_SLICE_F16) return r;
+    const wt_op &s1 = b->ops[x1], &s2 = b->ops[x2], &m = b->ops[xc];
+    uint32_t x = m.args[0];
+    if (s1.args[0] != x || s2.args[0] != x) return r;
+    uint32_t n = b->ops[add_op].args[3];
+    if (n % hd) return r;
+    uint32_t rows = n / hd;
+    // rank-2 slices [rows, hd] -> columns [0,h) and [h,hd), unit strides
+    auto slice_ok = [&](const wt_op& s, uint32_t c0, uint32_t c1) {
+        return s.args[3] == 2 && s.args[4] == 0 && s.args[5] == c0 && s.args[7] == rows && s.args[8] == c1 &&
+               s.args[10] <= 1 && s.args[11] <= 1 && s.args[13] == rows && s.args[14] == hd && s.args[2] == rows * h;
+    };
+    if (!slice_ok(s1, 0, h) || !slice_ok(s2, h, hd)) return r;
+    if (m.args[3] != n || b->ops[xs].args[3] != n || c.args[11] != n || b->ops[neg].args[2] != rows * h) return r;
+    r.ok = true;
+    r.x = x; r.cos_b = m.args[1]; r.sin_b = b->ops[xs].args[1]; r.rows = rows; r.hd = hd; r.out_op = (uint32_t)add_op;
+    r.src_op = G.producer_of_arg[0][xc];
+    r.ops = {(uint32_t)xc, (uint32_t)x1, (uint32_t)x2, (uint32_t)neg, (uint32_t)cat, (uint32_t)xs, (uint32_t)add_op};
+    return r;
+}
+
+struct Span {
+    int kind;                // 0 attention, 1 swiglu, 2 add+norm
+    uint32_t first, count;
+    std::vector<uint32_t> ops;
+    // attention
+    uint32_t qkv, cos_q, sin_q, cos_k, sin_k, q_out, mask, ctx, state, B, nh, kvh, hd, nslots, pos;
+    float scale; int scale_div;
+    // swiglu
+    uint32_t a_ref, wg, wu, y, M, K, N;
+    // add+norm
+    uint32_t add_a, add_b, sum_t, gamma_s, beta_s, norm_y, n;
+};
+
+bool contiguous(std::vector<uint32_t>& ops, uint32_t& first) {
+    std::sort(ops.begin(), ops.end());
+    ops.erase(std::unique(ops.begin(), ops.end()), ops.end());
+    first = ops.front();
+    return ops.back() - ops.front() + 1 == ops.size();
+}
+
+// every op of the span except `outs` is read only by ops of the span
+bool closed(const Graph& G, const std::vector<uint32_t>& ops, std::initializer_list<uint32_t> outs) {
+    for (uint32_t o : ops) {
+        if (std::find(outs.begin(), outs.end(), o) != outs.end()) continue;
+        for (uint32_t u : G.users[o])
+            if (!std::binary_search(ops.begin(), ops.end(), u)) return false;
+    }
+    return true;
+}
+
+bool const_scalar(const Graph& G, int bc_op, float& v) {
+    const wt_blob* b = G.b;
+    if (bc_op < 0 || b->ops[bc_op].opcode != OP_BROADCAST_F16) return false;
+    uint32_t src = b->ops[bc_op].args[0];
+    if (!(src & 0x8000u) || b->ops[bc_op].args[3] != 1) return false;
+    const wt_slot& s = b->slots[src & 0x7FFFu];
+    if (s.addr != 0 || s.len < 2) return false;
+    uint16_t h;
+    std::memcpy(&h, b->weight_base + s.offset, 2);
+    // fp16 -> fp32 on the host
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 31u, m = h & 1023u, bits;
+    if (e == 0) {
+        if (!m) bits = sign;
+        else { int sh = 0; while (!(m & 1024u)) { m <<= 1; sh++; } bits = sign | ((uint32_t)(113 - sh) << 23) | ((m & 1023u) << 13); }
+    } else if (e == 31u) bits = sign | 0x7f800000u | (m << 13);
+    else bits = sign | ((e + 112u) << 23) | (m << 13);
+    std::memcpy(&v, &bits, 4);
+    return true;
+}
+
+bool match_attention(const Graph& G, uint32_t ia, Span& sp) {
+    const wt_blob* b = G.b;
+    const wt_op& ap = b->ops[ia];
+    if (ap.opcode != OP_KV_APPEND_F16 || ap.args[3] != WT_KV_POS_AUTO) return false;
+    uint32_t state = ap.args[2];
+    Rope rk = match_rope(G, G.producer_of_arg[0][ia]);
+    int vsplit = G.producer_of_arg[1][ia];
+    if (!rk.ok || vsplit < 0 || rk.src_op < 0) return false;
+    const wt_op &ks = b->ops[rk.src_op], &vs = b->ops[vsplit];
+    if (ks.opcode != OP_SPLIT_F16 || vs.opcode != OP_SPLIT_F16 || ks.args[0] != vs.args[0]) return false;
+    if (ks.args[10] != 3 || ks.args[15] != 1 || vs.args[15] != 2 || vs.args[10] != 3) return false;
+    uint32_t s0 = ks.args[11], s1 = ks.args[12], s2 = ks.args[13], hd = rk.hd;
+    if (s1 != s2 || s0 % hd || s1 % hd || vs.args[11] != s0 || vs.args[12] != s1 || vs.args[13] != s2) return false;
+    uint32_t nh = s0 / hd, kvh = s1 / hd;
+    if (!kvh || nh % kvh || rk.rows % kvh) return false;
+    uint32_t B = rk.rows / kvh;
+    // ops after the append, in list order
+    uint32_t j = ia + 1;
+    uint32_t kT = 0, vv = 0;
+    std::vector<uint32_t> ops;
+    while (j < b->n_ops && b->ops[j].opcode == OP_KV_GATHER_F16 && b->ops[j].args[0] == state) {
+        const wt_op& gop = b->ops[j];
+        if (gop.args[3] != WT_KV_POS_AUTO || gop.args[4] != B * nh || gop.args[5] != B * kvh || gop.args[6] != hd) return false;
+        if (gop.args[1]) kT = gop.args[1];
+        if (gop.args[2]) vv = gop.args[2];
+        ops.push_back(j++);
+    }
+    if (!kT || !vv || j + 5 > b->n_ops) return false;
+    const wt_op &sc = b->ops[j], &bi = b->ops[j + 1], &ad = b->ops[j + 2], &sm = b->ops[j + 3], &pv = b->ops[j + 4];
+    if (sc.opcode != OP_MATMUL_F16 || bi.opcode != OP_BINARY_F16 || ad.opcode != OP_ADD_F16 ||
+        sm.opcode != OP_SOFTMAX_F16 || pv.opcode != OP_MATMUL_F16) return false;
+    uint32_t H = B * nh, nslots = sc.args[5];
+    if (sc.args[1] != kT || sc.args[3] != 1 || sc.args[4] != hd || (sc.args[6] & 7u) != 4u || (sc.args[6] >> 16) != H) return false;
+    if (bi.args[0] != sc.args[2] || (bi.args[4] != 2 && bi.args[4] != 3) || bi.args[3] != H * nslots) return false;
+    if (ad.args[0] != bi.args[2] || ad.args[3] != H * nslots) return false;
+    if (sm.args[0] != ad.args[2] || sm.args[2] != H || sm.args[3] != nslots) return false;
+    if (pv.args[0] != sm.args[1] || pv.args[1] != vv || pv.args[3] != 1 || pv.args[4] != nslots || pv.args[5] != hd ||
+        (pv.args[6] & 7u) != 4u || (pv.args[6] >> 16) != H) return false;
+    float scale;
+    if (!const_scalar(G, G.producer_of_arg[1][j + 1], scale)) return false;
+    // q: rotary over SPLIT index 0 of the same qkv
+    Rope rq = match_rope(G, G.producer_of_arg[0][j]);
+    if (!rq.ok || rq.hd != hd || rq.rows != H || rq.src_op < 0) return false;
+    const wt_op& qs = b->ops[rq.src_op];
+    if (qs.opcode != OP_SPLIT_F16 || qs.args[0] != ks.args[0] || qs.args[15] != 0 || qs.args[10] != 3 || qs.args[11] != s0) return false;
+    // the ring must be the one the geometry implies
+    uint32_t si = state & 0x1FFFu;
+    if ((state & 0xE000u) != WT_REF_STATE_FLAG || si >= g.n_states || !g.kv[si].ready || g.kv[si].nslots != nslots ||
+        g.kv[si].slot_bytes != B * kvh * hd * 4u) return false;
+    if (nh / kvh > 16 || (hd != 128 && hd != 64)) return false;
+    // mask operand: a temp or slot of H*nslots elements laid out [H][nslots]
+    for (uint32_t o : rq.ops) ops.push_back(o);
+    for (uint32_t o : rk.ops) ops.push_back(o);
+    ops.push_back((uint32_t)rq.src_op); ops.push_back((uint32_t)rk.src_op); ops.push_back((uint32_t)vsplit);
+    ops.push_back(ia);
+    for (uint32_t k = 0; k < 5; k++) ops.push_back(j + k);
+    uint32_t first;
+    if (!contiguous(ops, first)) return false;
+    if (!closed(G, ops, {j + 4})) return false;
+    sp.kind = 0; sp.first = first; sp.count = (uint32_t)ops.size(); sp.ops = ops;
+    sp.qkv = ks.args[0]; sp.cos_q = rq.cos_b; sp.sin_q = rq.sin_b; sp.cos_k = rk.cos_b; sp.sin_k = rk.sin_b;
+    sp.q_out = b->ops[rq.out_op].args[2]; sp.mask = ad.args[1]; sp.ctx = pv.args[2]; sp.state = si;
+    sp.B = B; sp.nh = nh; sp.kvh = kvh; sp.hd = hd; sp.nslots = nslots; sp.pos = ap.args[3];
+    sp.scale = scale; sp.scale_div = bi.args[4] == 3;
+    return true;
+}
+
+bool match_swiglu(const Graph& G, uint32_t ip, Span& sp) {
+    const wt_blob* b = G.b;
+    const wt_op& pr = b->ops[ip];
+    if (pr.opcode != OP_BINARY_F16 || pr.args[4] != 2) return false;
+    int act = G.producer_of_arg[0][ip], up = G.producer_of_arg[1][ip];
+    if (act < 0 || up < 0 || b->ops[act].opcode != OP_BINARY_F16 || b->ops[act].args[4] != 2 || b->ops[up].opcode != OP_MATMUL_W4A16) return false;
+    int gate = G.producer_of_arg[0][act], sig = G.producer_of_arg[1][act];
+    if (gate < 0 || sig < 0 || b->ops[gate].opcode != OP_MATMUL_W4A16 || b->ops[sig].opcode != OP_UNARY_F16 || b->ops[sig].args[3] != 8) return false;
+    if (G.producer_of_arg[0][sig] != gate) return false;
+    const wt_op &gt = b->ops[gate], &u = b->ops[up];
+    if (gt.args[0] != u.args[0] || gt.args[3] != u.args[3] || gt.args[4] != u.args[4] || gt.args[5] != u.args[5]) return false;
+    uint32_t M = gt.args[3], n = M * gt.args[5];
+    if (M > 16 || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
+    std::vector<uint32_t> ops = {(uint32_t)gate, (uint32_t)sig, (uint32_t)act, (uint32_t)up, ip};
+    uint32_t first;
+    if (!contiguous(ops, first) || !closed(G, ops, {ip})) return false;
+    sp.kind = 1; sp.first = first; sp.count = 5; sp.ops = ops;
+    sp.a_ref = gt.args[0]; sp.wg = gt.args[1]; sp.wu = u.args[1]; sp.y = pr.args[2];
+    sp.M = M; sp.K = gt.args[4]; sp.N = gt.args[5];
+    return true;
+}
+
+bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
+    const wt_blob* b = G.b;
+    if (i + 1 >= b->n_ops) return false;
+    const wt_op &ad = b->ops[i], &nm = b->ops[i + 1];
+    if (ad.opcode != OP_ADD_F16 || nm.opcode != OP_RMSNORM2_F16) return false;
+    if (nm.args[0] != ad.args[2] || nm.args[4] != ad.args[3] || !is_temp_ref(ad.args[2])) return false;
+    sp.kind = 2; sp.first = i; sp.count = 2; sp.ops = {i, i + 1};
+    sp.add_a = ad.args[0]; sp.add_b = ad.args[1]; sp.sum_t = ad.args[2];
+    sp.gamma_s = nm.args[1] & 0x7FFFu; sp.beta_s = nm.args[2] & 0x7FFFu; sp.norm_y = nm.args[3]; sp.n = ad.args[3];
+    return true;
+}
+
+std::vector<Span> g_spans;
+float* g_attn_scratch = nullptr;
+
+const uint8_t* resolve(const wt_blob* b, uint32_t arg) {
+    if (arg & 0x8000u) {
+        uint32_t s = arg & 0x7FFFu;
+        if (s >= b->n_slots) return nullptr;
+        auto it = g.d_ext.find(s);
+        if (it != g.d_ext.end()) return it->second;
+        return g.d_weights + b->slots[s].offset;
+    }
+    if (!is_temp_ref(arg)) return nullptr;
+    return g.temp_dev[arg];
+}
+
+}  // namespace
+
+// Finds the chains. `internal[t]` is set for temp ids written only inside
+// fused chains (and not among a chain's outputs): they need no memory.
+void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal) {
+    g_spans.clear();
+    internal.assign(kMaxTemps, 0);
+    Graph G;
+    build_graph(b, meas, G);
+    std::vector<uint8_t> taken(b->n_ops, 0);
+    auto claim = [&](Span& sp) {
+        for (uint32_t o : sp.ops) if (taken[o] || meas[o].rc) return false;
+        for (uint32_t o : sp.ops) taken[o] = 1;
+        g_spans.push_back(sp);
+        return true;
+    };
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        Span sp{};
+        if (b->ops[i].opcode == OP_KV_APPEND_F16 && match_attention(G, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        Span sp{};
+        if (!taken[i] && b->ops[i].opcode == OP_BINARY_F16 && match_swiglu(G, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i + 1 < b->n_ops; i++) {
+        Span sp{};
+        if (!taken[i] && !taken[i + 1] && match_add_norm(G, i, sp)) claim(sp);
+    }
+    // temps written only by interior ops of chains
+    std::vector<int> writes_in(kMaxTemps, 0), writes_out(kMaxTemps, 0);
+    std::vector<uint8_t> interior(b->n_ops, 0);
+    for (const Span& sp : g_spans) {
+        if (sp.kind == 2) continue;
+        for (uint32_t o : sp.ops) interior[o] = 1;
+        interior[sp.ops.back()] = 0;                       // the chain's result
+        if (sp.kind == 0)                                   // the rotated q is kept as the attention kernel's input
+            for (uint32_t o : sp.ops)
+                if (meas[o].out_id[0] == sp.q_out) interior[o] = 0;
+    }
+    for (uint32_t i = 0; i < b->n_ops; i++)
+        for (int k = 0; k < 2; k++) {
+            uint32_t id = meas[i].out_id[k];
+            if (id == kNoOff) continue;
+            (interior[i] ? writes_in : writes_out)[id]++;
+        }
+    for (uint32_t t = 0; t < kMaxTemps; t++) internal[t] = writes_in[t] > 0 && writes_out[t] == 0;
+}
+
+// Bakes the fused launches into the plan (after addresses are known).
+void fuse_materialize(const wt_blob* b) {
+    size_t scratch_floats = 0;
+    for (const Span& sp : g_spans)
+        if (sp.kind == 0) {
+            uint32_t ns = attn_decode_pick_splits(sp.B * sp.kvh, sp.nslots);
+            size_t f = attn_decode_scratch_floats(sp.B * sp.kvh, sp.nh / sp.kvh, sp.hd, ns);
+            if (f > scratch_floats) scratch_floats = f;
+        }
+    if (scratch_floats) {
+        if (cudaMalloc(&g_attn_scratch, scratch_floats * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return; }
+    }
+    g.fused_ops = 0;
+    for (const Span& sp : g_spans) {
+        PlanOp& head = g.plan[sp.first];
+        if (sp.kind == 0) {
+            const uint16_t* qkv = (const uint16_t*)resolve(b, sp.qkv);
+            const uint16_t *cq = (const uint16_t*)resolve(b, sp.cos_q), *sq = (const uint16_t*)resolve(b, sp.sin_q);
+            const uint16_t *ck = (const uint16_t*)resolve(b, sp.cos_k), *sk = (const uint16_t*)resolve(b, sp.sin_k);
+            uint16_t* q_out = (uint16_t*)resolve(b, sp.q_out);
+            const uint16_t* mask = (const uint16_t*)resolve(b, sp.mask);
+            uint16_t* ctx = (uint16_t*)resolve(b, sp.ctx);
+            if (!qkv || !cq || !sq || !ck || !sk || !q_out || !mask || !ctx) continue;
+            uint32_t si = sp.state;
+            uint16_t* ring = (uint16_t*)g.st_buf[si];
+            uint32_t* posmap = g.kv[si].posmap;
+            uint32_t* ctr = g.d_st_count + si;
+            uint32_t B = sp.B, nh = sp.nh, kvh = sp.kvh, hd = sp.hd, nslots = sp.nslots, pos = sp.pos;
+            AttnDecodeArgs a{};
+            a.q = q_out; a.ring = ring; a.counter = ctr; a.n_kv = 0; a.n_kv_add = 1; a.bump_counter = ctr;
+            a.mask = mask; a.mask_seq_stride = nh * nslots; a.kvh_per_seq = kvh;
+            a.scale = sp.scale; a.scale_div = sp.scale_div; a.rep = nh / kvh; a.kv_heads = B * kvh; a.nslots = nslots;
+            a.nsplit = attn_decode_pick_splits(B * kvh, nslots);
+            a.part_o = g_attn_scratch;
+            a.part_ml = g_attn_scratch + (size_t)B * kvh * a.nsplit * a.rep * hd;
+            head.fused = [=](cudaStream_t st) {
+                k_rope_kv_append(st, qkv, cq, sq, ck, sk, q_out, ring, posmap, ctr, B, nh, kvh, hd, nslots, pos);
+                k_attn_decode(st, a, hd, ctx, B * kvh);
+            };
+        } else if (sp.kind == 1) {
+            const uint16_t* act = (const uint16_t*)resolve(b, sp.a_ref);
+            uint16_t* y = (uint16_t*)resolve(b, sp.y);
+            auto find = [&](uint32_t wref) -> const W4Packed* {
+                uint64_t key = (uint64_t)(wref & 0x7FFFu) | ((uint64_t)sp.K << 16) | ((uint64_t)sp.N << 40);
+                auto it = g.w4.find(key);
+                return it == g.w4.end() ? nullptr : &it->second;
+            };
+            const W4Packed *wg = find(sp.wg), *wu = find(sp.wu);
+            if (!act || !y || !wg || !wu) continue;
+            const uint32_t *pg = wg->packed, *pu = wu->packed;
+            const uint16_t *sg = wg->scales, *su = wu->scales;
+            uint32_t M = sp.M, K = sp.K, N = sp.N;
+            head.fused = [=](cudaStream_t st) { k_w4a16_skinny_swiglu(st, act, pg, sg, pu, su, y, M, K, N); };
+        } else {
+            const uint16_t *aa = (const uint16_t*)resolve(b, sp.add_a), *ab = (const uint16_t*)resolve(b, sp.add_b);
+            uint16_t *sum = (uint16_t*)resolve(b, sp.sum_t), *y = (uint16_t*)resolve(b, sp.norm_y);
+            const uint16_t* gam = (const uint16_t*)resolve(b, 0x8000u | sp.gamma_s);
+            const uint16_t* bet = (const uint16_t*)resolve(b, 0x8000u | sp.beta_s);
+            if (!aa || !ab || !sum || !y || !gam) continue;
+            uint32_t rw = b->slots[sp.gamma_s].len / 2u;
+            if (!rw || sp.n % rw) continue;
+            uint32_t rows = sp.n / rw;
+            head.fused = [=](cudaStream_t st) { k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw); };
+        }
+        head.span = sp.count;
+        g.fused_ops += sp.count;
+    }
+}
+
+void fuse_release() {
+    if (g_attn_scratch) { cudaFree(g_attn_scratch); g_attn_scratch = nullptr; }
+    g_spans.clear();
+}
+
+}  // namespace gehtp

@@ -37,6 +37,10 @@ void k_w4_unpack_i8(cudaStream_t st, const uint32_t* packed, int8_t* out, uint32
 // from L2 once per 16 rows).
 void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
                     uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep);
+// Gate and up projections with the SwiGLU product in the epilogue (one pass over both matrices).
+void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* pg, const uint16_t* sg,
+                           const uint32_t* pu, const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K,
+                           uint32_t N);
 // tcgen05 / TMEM form for M >= 128 (w4a16_gemm_sm100.cu). Returns false when
 // the shape is outside what it handles (the caller then uses the skinny form).
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,

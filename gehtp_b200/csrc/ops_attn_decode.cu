@@ -81,7 +81,7 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t rep = A.rep;
-    const uint32_t n_kv = A.counter ? *A.counter : A.n_kv;
+    const uint32_t n_kv = A.counter ? *A.counter + A.n_kv_add : A.n_kv;
     uint32_t per = (n_kv + A.nsplit - 1) / A.nsplit;
     per = (per + TILE - 1) / TILE * TILE;
     const uint32_t p_begin = split * per;
@@ -258,7 +258,8 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
 
 // out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}, slices in order.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit) {
+                                         uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit,
+                                         uint32_t* bump_counter) {
     const uint32_t h = blockIdx.x;           // query head, = kvh * rep + r
     const uint32_t kvh = h / rep, r = h % rep;
     float mt = -INFINITY;
@@ -274,6 +275,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
         }
         out[(size_t)h * hd + d] = f2h(lt > 0.0f ? acc / lt : 0.0f);
     }
+    // every reader of the counter (the split kernel) has finished: stream order
+    if (bump_counter && blockIdx.x == 0 && threadIdx.x == 0) *bump_counter += 1;
 }
 
 }  // namespace
@@ -307,7 +310,7 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
         if (!attr) { cudaFuncSetAttribute(attn_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
         attn_decode_split_kernel<64><<<grid, NWARP * 32, smem, st>>>(a);
     }
-    attn_decode_merge_kernel<<<kv_heads_total * a.rep, hd < 128 ? 64 : 128, 0, st>>>(a.part_o, a.part_ml, out, a.rep, hd, a.nsplit);
+    attn_decode_merge_kernel<<<kv_heads_total * a.rep, hd < 128 ? 64 : 128, 0, st>>>(a.part_o, a.part_ml, out, a.rep, hd, a.nsplit, a.bump_counter);
     g_launches += 2;
     return true;
 }

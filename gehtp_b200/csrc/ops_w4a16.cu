@@ -129,12 +129,25 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 slo, __half2 sh
     a[3] = *(uint32_t*)&h3;
 }
 
-template <int MT, int UNROLL>
+// SwiGLU on two accumulators with the op chain's roundings: gate -> fp16,
+// sigmoid -> fp16, gate*sigmoid -> fp16, up -> fp16, product -> fp16
+// (UNARY subtype 8 and two BINARY mul ops of the reference executor).
+__device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
+    float gt = h2f(f2h(gate_acc));
+    float sg = h2f(f2h(1.0f / (1.0f + expf(-gt))));
+    float act = h2f(f2h(__fmul_rn(gt, sg)));
+    float up = h2f(f2h(up_acc));
+    return f2h(__fmul_rn(act, up));
+}
+
+template <int MT, int UNROLL, bool DUAL>
 __global__ void __launch_bounds__(512)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
-                    const uint16_t* __restrict__ sc, uint16_t* __restrict__ y, uint32_t M,
+                    const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
+                    const uint16_t* __restrict__ sc2, uint16_t* __restrict__ y, uint32_t M,
                     uint32_t K, uint32_t N, uint32_t kgw, W4Epilogue ep) {
-    extern __shared__ float red[];  // [nwarps][MT*4][32]
+    extern __shared__ float red[];  // [nwarps][NACC][32]
+    constexpr int NACC = MT * 4 * (DUAL ? 2 : 1);
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t nb = blockIdx.x, NB = N / 16, KG = K / 64;
@@ -143,37 +156,54 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
     uint32_t kg0 = warp * kgw, kg1 = kg0 + kgw;
     if (kg1 > KG) kg1 = KG;
 
-    float acc[MT][4];
+    float acc[MT][4], acc2[DUAL ? MT : 1][4];
 #pragma unroll
     for (int i = 0; i < MT; i++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) acc[i][c] = 0.0f;
+        for (int c = 0; c < 4; c++) { acc[i][c] = 0.0f; if (DUAL) acc2[i][c] = 0.0f; }
 
     const uint4* wbase = wp + (size_t)nb * 32 + lane;
+    const uint4* wbase2 = DUAL ? wp2 + (size_t)nb * 32 + lane : nullptr;
     for (uint32_t kg = kg0; kg < kg1; kg += UNROLL) {
-        uint4 wq[UNROLL];
-        uint16_t s0[UNROLL], s1[UNROLL];
+        uint4 wq[UNROLL], wq2[DUAL ? UNROLL : 1];
+        uint16_t s0[UNROLL], s1[UNROLL], t0[DUAL ? UNROLL : 1], t1[DUAL ? UNROLL : 1];
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             if (kg + u < kg1) {
                 wq[u] = __ldcs(wbase + (size_t)(kg + u) * NB * 32);  // streamed once: evict first
                 s0[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo);
                 s1[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo + 8);
+                if (DUAL) {
+                    wq2[u] = __ldcs(wbase2 + (size_t)(kg + u) * NB * 32);
+                    t0[u] = __ldg(sc2 + (size_t)(kg + u) * N + n_lo);
+                    t1[u] = __ldg(sc2 + (size_t)(kg + u) * N + n_lo + 8);
+                }
             } else {
                 wq[u] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
                 s0[u] = 0; s1[u] = 0;
+                if (DUAL) { wq2[u] = wq[u]; t0[u] = 0; t1[u] = 0; }
             }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             if (kg + u >= kg1) break;
-            const __half2 slo = __half2half2(__ushort_as_half(s0[u]));
-            const __half2 shi = __half2half2(__ushort_as_half(s1[u]));
-            uint32_t af[4][4];
-            dequant_word(wq[u].x, slo, shi, af[0]);
-            dequant_word(wq[u].y, slo, shi, af[1]);
-            dequant_word(wq[u].z, slo, shi, af[2]);
-            dequant_word(wq[u].w, slo, shi, af[3]);
+            uint32_t af[4][4], af2[DUAL ? 4 : 1][4];
+            {
+                const __half2 slo = __half2half2(__ushort_as_half(s0[u]));
+                const __half2 shi = __half2half2(__ushort_as_half(s1[u]));
+                dequant_word(wq[u].x, slo, shi, af[0]);
+                dequant_word(wq[u].y, slo, shi, af[1]);
+                dequant_word(wq[u].z, slo, shi, af[2]);
+                dequant_word(wq[u].w, slo, shi, af[3]);
+            }
+            if (DUAL) {
+                const __half2 slo = __half2half2(__ushort_as_half(t0[u]));
+                const __half2 shi = __half2half2(__ushort_as_half(t1[u]));
+                dequant_word(wq2[u].x, slo, shi, af2[0]);
+                dequant_word(wq2[u].y, slo, shi, af2[1]);
+                dequant_word(wq2[u].z, slo, shi, af2[2]);
+                dequant_word(wq2[u].w, slo, shi, af2[3]);
+            }
 #pragma unroll
             for (int i = 0; i < MT; i++) {
                 const uint32_t m = m0 + i * 8 + g;
@@ -187,6 +217,12 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
                 mma16816(acc[i], af[1], b0.z, b0.w);
                 mma16816(acc[i], af[2], b1.x, b1.y);
                 mma16816(acc[i], af[3], b1.z, b1.w);
+                if (DUAL) {
+                    mma16816(acc2[i], af2[0], b0.x, b0.y);
+                    mma16816(acc2[i], af2[1], b0.z, b0.w);
+                    mma16816(acc2[i], af2[2], b1.x, b1.y);
+                    mma16816(acc2[i], af2[3], b1.z, b1.w);
+                }
             }
         }
     }
@@ -194,36 +230,65 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
 #pragma unroll
     for (int i = 0; i < MT; i++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) red[(warp * MT * 4 + i * 4 + c) * 32 + lane] = acc[i][c];
+        for (int c = 0; c < 4; c++) {
+            red[(warp * NACC + i * 4 + c) * 32 + lane] = acc[i][c];
+            if (DUAL) red[(warp * NACC + MT * 4 + i * 4 + c) * 32 + lane] = acc2[i][c];
+        }
     __syncthreads();
     for (uint32_t idx = threadIdx.x; idx < MT * 4 * 32; idx += blockDim.x) {
-        float s = 0.0f;
-        for (uint32_t w = 0; w < nwarps; w++) s += red[w * MT * 4 * 32 + idx];
+        float s = 0.0f, s2 = 0.0f;
+        for (uint32_t w = 0; w < nwarps; w++) {
+            s += red[w * NACC * 32 + idx];
+            if (DUAL) s2 += red[w * NACC * 32 + MT * 4 * 32 + idx];
+        }
         const uint32_t ln = idx & 31, c = (idx >> 5) & 3, i = idx >> 7;
         const uint32_t gg = ln >> 2, tt = ln & 3;
         const uint32_t n = nb * 16 + gg + ((c & 2) ? 8 : 0);
         const uint32_t m = m0 + i * 8 + tt * 2 + (c & 1);
-        if (m < M) w4_store(ep, y, m, n, N, s);
+        if (m < M) {
+            if (DUAL) y[(size_t)m * N + n] = swiglu_chain(s, s2);
+            else w4_store(ep, y, m, n, N, s);
+        }
     }
+}
+
+static uint32_t skinny_kgw(uint32_t KG) {
+    uint32_t kgw = 8;
+    while ((KG + kgw - 1) / kgw > 16) kgw += 8;
+    return kgw;
 }
 
 void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
                     uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep) {
     if (!M || !N || !K) return;
-    const uint32_t KG = K / 64;
-    uint32_t kgw = 8;
-    while ((KG + kgw - 1) / kgw > 16) kgw += 8;
-    uint32_t nwarps = (KG + kgw - 1) / kgw;
+    const uint32_t KG = K / 64, kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
     if (M <= 8) {
         dim3 grid(N / 16, 1);
         size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
-        w4a16_skinny_kernel<1, 8><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, y, M,
-                                                                 K, N, kgw, ep);
+        w4a16_skinny_kernel<1, 8, false><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, nullptr, nullptr, y, M, K, N, kgw, ep);
     } else {
         dim3 grid(N / 16, (M + 15) / 16);
         size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        w4a16_skinny_kernel<2, 4><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, y, M,
-                                                                 K, N, kgw, ep);
+        w4a16_skinny_kernel<2, 4, false><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, nullptr, nullptr, y, M, K, N, kgw, ep);
+    }
+    g_launches++;
+}
+
+// y = swiglu(a.Wg, a.Wu): two weight matrices of the same shape in one pass.
+void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* pg, const uint16_t* sg,
+                           const uint32_t* pu, const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K,
+                           uint32_t N) {
+    if (!M || !N || !K) return;
+    const uint32_t KG = K / 64, kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    W4Epilogue ep;
+    if (M <= 8) {
+        dim3 grid(N / 16, 1);
+        size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
+        w4a16_skinny_kernel<1, 4, true><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+    } else {
+        dim3 grid(N / 16, (M + 15) / 16);
+        size_t smem = (size_t)nwarps * 16 * 32 * sizeof(float);
+        w4a16_skinny_kernel<2, 2, true><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
     }
     g_launches++;
 }

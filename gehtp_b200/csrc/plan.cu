@@ -36,6 +36,8 @@ struct Planner {
     // building walk inputs
     uint8_t* addr[kMaxTemps];
     bool in_static[kMaxTemps], in_vtcm[kMaxTemps];
+    bool internal[kMaxTemps];   // exists only inside fused chains: no memory
+    PlanOp* cur = nullptr;
 
     uint8_t* dummy() const { return (uint8_t*)(uintptr_t)256; }
 
@@ -68,6 +70,7 @@ struct Planner {
         t = arg;
         if (t >= kMaxTemps || !written[t]) return nullptr;
         touch(t);
+        if (build && internal[t]) { if (cur) cur->uses_internal = true; return dummy(); }
         return build ? addr[t] : dummy();
     }
     void touch(uint32_t t) {
@@ -97,6 +100,7 @@ struct Planner {
             live[id].push_back({opi, opi});
             return dummy();
         }
+        if (internal[id]) { p.uses_internal = true; return dummy(); }
         return addr[id];
     }
 };
@@ -796,9 +800,14 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     };
     reset_walk(false);
     std::memset(P.maxb, 0, sizeof P.maxb);
-    {
-        std::vector<PlanOp> tmp(b->n_ops);
-        for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; plan_op(P, b->ops[i], tmp[i]); }
+    std::memset(P.internal, 0, sizeof P.internal);
+    std::vector<PlanOp> meas(b->n_ops);
+    for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; P.cur = &meas[i]; plan_op(P, b->ops[i], meas[i]); }
+    const bool fusing = g.opt_fuse && !g.force_unfused;
+    if (fusing) {
+        std::vector<uint8_t> internal;
+        fuse_analyze(b, meas, internal);
+        for (uint32_t i = 0; i < kMaxTemps; i++) P.internal[i] = internal[i] != 0;
     }
 
     // static-pool entries that would overwrite each other while both are live
@@ -827,6 +836,7 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     std::vector<size_t> toff(kMaxTemps, 0);
     for (uint32_t i = 0; i < kMaxTemps; i++) {
         if (!P.maxb[i] || P.in_static[i] || g.vtcm_off[i] != kNoOff) continue;
+        if (P.internal[i]) { P.maxb[i] = 0; continue; }
         toff[i] = off;
         off += align_up(P.maxb[i], 256);
     }
@@ -843,12 +853,12 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     // building walk
     reset_walk(true);
     g.plan.assign(b->n_ops, PlanOp());
-    for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; plan_op(P, b->ops[i], g.plan[i]); }
+    for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; P.cur = &g.plan[i]; plan_op(P, b->ops[i], g.plan[i]); }
     // run-time temp table starts empty; addresses appear as ops execute
     for (uint32_t i = 0; i < kMaxTemps; i++) g.temp_dev[i] = P.addr[i];
 
     g.fused_ops = 0;
-    if (g.opt_fuse) fuse_plan(b);
+    if (fusing) fuse_materialize(b);
     cudaError_t ce = cudaStreamSynchronize(g.stream);
     if (ce != cudaSuccess) { std::snprintf(err, errn, "plan upload: %s", cudaGetErrorString(ce)); return -1; }
     g.blob = b; g.blob_wbase = b->weight_base; g.blob_nops = b->n_ops; g.blob_nslots = b->n_slots;
@@ -865,6 +875,7 @@ void drop_plan(bool keep_states) {
     g.d_ext.clear();
     for (auto& kv : g.w4) cudaFree(kv.second.packed);
     g.w4.clear();
+    fuse_release();
     if (g.d_arena) { cudaFree(g.d_arena); g.d_arena = nullptr; }
     g.arena_bytes = 0;
     for (uint32_t i = 0; i < kMaxTemps; i++) { g.temp_dev[i] = nullptr; g.temp_cap[i] = 0; g.temp_last[i] = 0; }

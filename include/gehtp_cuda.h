@@ -148,6 +148,26 @@ const char* gehtp_cuda_last_error(void);
 int gehtp_cuda_run_dev(const struct wt_blob* b, const void* in_dev, void* out_dev,
                        uint32_t out_temp, char* err, size_t errn);
 
+/* Eager run with a CUDA event pair (on the engine stream) around every launch
+ * unit: op_ms[i] = device milliseconds of the unit that starts at op i, 0 for
+ * ops absorbed into a fused unit. `in_ptr` is host memory as in wt_exec_run_io. */
+int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_t out_temp,
+                            float* op_ms, uint32_t cap, char* err, size_t errn);
+
+/* Persistent-state image exchange (the reference keeps states inside its
+ * engine and can only fill them by running append ops; its host golden saves
+ * and restores them through a file, compiler/src/ops/host_decode_state.cpp:14-62).
+ * load: copy `bytes` from host (or device) memory into state `idx`; with
+ * kv_elems != 0 the state is a KV ring of kv_elems K values per position, ring
+ * slots [0, n_positions) are marked as holding positions 0.. and the state's
+ * position counter becomes n_positions. `b` (may be NULL once a blob has run)
+ * makes sure the blob's state table is resident first. */
+int gehtp_cuda_state_load(const struct wt_blob* b, uint32_t idx, const void* src, size_t bytes,
+                          int src_is_device, uint32_t kv_elems, uint32_t n_positions,
+                          char* err, size_t errn);
+int gehtp_cuda_state_set_count(uint32_t idx, uint32_t n_positions);
+int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes);
+
 /* ------------------------------------------------------- W4A16 group-64
  * Weight slot form accepted by opcode 1 on this executor (the reference's
  * opcode 1 is an HMX-specific integer contract found by slot size,

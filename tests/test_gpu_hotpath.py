@@ -172,6 +172,30 @@ def test_run_range_pieces_equal_whole_run(cuda):
     cuda.wt_exec_state_reset()
 
 
+def test_fused_plan_survives_piecewise_and_hooked_runs(cuda):
+    """With fusion on, chains run as single kernels and their inner temps have
+    no memory; asking for one of those ops alone makes the engine plan again
+    unfused, and results stay the same."""
+    buf, man = build_decode_runlist(TINY, 2, 32, seed=5, quant="w4")
+    face = decode_face(man, [3, 4], 0, TINY.head_dim, TINY.rope_theta)
+    cuda.gehtp_cuda_set_fusion(1)
+    cuda.gehtp_cuda_set_graph(0)
+    cuda.wt_exec_state_reset()
+    eng = Engine(cuda, buf)
+    eng.run_io(face, man["token_temp"], None)
+    assert cuda.gehtp_cuda_fused_ops() >= TINY.layers * (25 + 5 + 2)
+    fused_logits = eng.temp(man["logits_temp"]).copy()
+    cuda.wt_exec_state_reset()
+    for i in range(man["n_ops"]):
+        eng.run_range(i, 1)
+    assert cuda.gehtp_cuda_fused_ops() == 0
+    piece_logits = eng.temp(man["logits_temp"]).copy()
+    eng.shutdown()
+    cuda.wt_exec_state_reset()
+    assert_fp16_close(fused_logits, piece_logits, "fused vs piecewise")
+    cuda.gehtp_cuda_set_graph(1)
+
+
 def test_prefill_runlist_matches_reference(cuda, ref):
     cfg = DecoderConfig(256, 2, 4, 2, 128, 512, 512, 1e6, "tiny")
     seq = 48
