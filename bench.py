@@ -1,0 +1,405 @@
+"""Decode throughput of a Qwen3-4B-shaped W4A16 decoder runlist on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (our arm)
+    python bench.py --impl reference --gpus N --steps K ...   (the reference's CPU path)
+
+One step = one decode step of the whole runlist (36 layers + lm_head) for a
+batch of sequences that all sit at a KV context of about 8192 positions.
+Rank 0 prints one JSON line. `value` is measured with the step's input face
+already in HBM; `e2e` goes through wt_exec_run_io with host buffers (host to
+device copy of the face, device to host read of the chosen tokens inside the
+timed region). With N > 1 the projections are tensor-parallel (column / row
+sharded runlists per rank, NCCL all-reduce inside the engine after the
+row-parallel ones).
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "qwen3_4b_shape_w4a16_decode_tokens_per_s"
+UNIT = "tok/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 8 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 8:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def w4_bytes(M, K, N):
+    """Algorithmic bytes of one W4A16 matmul: nibbles + scales + activations in + out."""
+    return K * N // 2 + 2 * (K // 64) * N + 2 * M * K + 2 * M * N
+
+
+def classify_units(blob, op_ms, man, n_kv):
+    """Groups the launch units of one profiled step: name -> [launches, total ms, algorithmic bytes]."""
+    from gehtp_b200.wtop import OP
+    groups = {}
+
+    def add(name, ms, nbytes):
+        g = groups.setdefault(name, [0, 0.0, 0])
+        g[0] += 1
+        g[1] += ms
+        g[2] += nbytes
+    B = man["B"]
+    i, n = 0, blob.n_ops
+    while i < n:
+        ms = op_ms[i]
+        op = blob.ops[i]
+        if ms <= 0.0:
+            i += 1
+            continue
+        if op.opcode == OP.MATMUL_W4A16:
+            M, K, N = op.args[3], op.args[4], op.args[5]
+            nb = w4_bytes(M, K, N)
+            dual = (i + 3 < n and blob.ops[i + 1].opcode == OP.UNARY and blob.ops[i + 3].opcode == OP.MATMUL_W4A16
+                    and op_ms[i + 3] <= 0.0)
+            if dual:
+                nb += K * N // 2 + 2 * (K // 64) * N
+            add("w4a16_gemv", ms, nb)
+        elif op.opcode == OP.SPLIT and i + 1 < n and op_ms[i + 1] <= 0.0:
+            kv_elems = man["kv_elems"]
+            add("attn_decode", ms, 2 * n_kv * kv_elems * 2 + 4 * man["q_elems"])
+        elif op.opcode == OP.ADD and i + 1 < n and op_ms[i + 1] <= 0.0:
+            add("add_rmsnorm", ms, 4 * op.args[3] * 2)
+        elif op.opcode == OP.RMSNORM2:
+            add("rmsnorm", ms, 2 * op.args[4] * 2)
+        else:
+            add("other", ms, 0)
+        i += 1
+    return groups
+
+
+def run_ours(args, rank, world):
+    import torch
+    import gehtp_b200
+    from gehtp_b200.runlists import QWEN3_4B, build_decode_runlist, decode_face
+    from gehtp_b200.wtop import Engine
+
+    cfg = QWEN3_4B
+    B, ctx, K, W = args.batch, args.ctx, args.steps, args.warmup
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    lib = gehtp_b200.lib()
+    assert lib.gehtp_cuda_set_device(local) == 0, "no CUDA device"
+    if world > 1:
+        init_tp(lib, rank, world)
+
+    t0 = time.time()
+    buf, man = build_decode_runlist(cfg, B, ctx, seed=1004, quant="w4", n_layers=args.layers, tp=world, rank=rank)
+    kvh, nh, hd = cfg.kv_heads // world, cfg.n_heads // world, cfg.head_dim
+    man["kv_elems"], man["q_elems"] = B * kvh * hd, B * nh * hd
+    eng = Engine(lib, buf)
+    err = ctypes.create_string_buffer(256)
+    if world > 1:
+        idx = (ctypes.c_uint32 * len(man["row_parallel_ops"]))(*man["row_parallel_ops"])
+        assert lib.gehtp_cuda_tp_allreduce_after(idx, len(man["row_parallel_ops"])) == 0
+    total_steps = W + K
+    p0 = max(ctx - total_steps, 0)
+
+    # KV rings ~ N(0,1) for positions [0, ctx), generated on the device
+    ring_elems = ctx * 2 * man["kv_elems"]
+    for li in range(man["layers"]):
+        kv = torch.randn(ring_elems, device="cuda", dtype=torch.float16)
+        rc = lib.gehtp_cuda_state_load(ctypes.byref(eng.blob), li, kv.data_ptr(), ring_elems * 2, 1, man["kv_elems"], p0, err, 256)
+        assert rc == 0, err.value
+        del kv
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+
+    rng = np.random.default_rng(4)
+    faces = [decode_face(man, rng.integers(0, cfg.vocab, B), p0 + s, hd, cfg.rope_theta) for s in range(total_steps)]
+    out_host = np.zeros(2 * B, np.uint16)
+    stream = torch.cuda.ExternalStream(lib.gehtp_cuda_stream())
+    tok_temp = man["token_temp"]
+
+    def reset_positions():
+        for li in range(man["layers"]):
+            assert lib.gehtp_cuda_state_set_count(li, p0) == 0
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn):
+        """W warm-up steps, then exactly K steps between two CUDA events on the engine stream; max over ranks."""
+        reset_positions()
+        for s in range(W):
+            step_fn(s)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+        for s in range(W, W + K):
+            step_fn(s)
+        with torch.cuda.stream(stream):
+            e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # first runs: plan build, weight upload and repack, graph capture
+    reset_positions()
+    for s in range(2):
+        eng.run_io(faces[s], tok_temp, out_host)
+
+    # ---- e2e: host face in, tokens out, through wt_exec_run_io
+    def step_e2e(s):
+        eng.run_io(faces[s], tok_temp, out_host)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = lib.gehtp_cuda_launch_count()
+    e2e_ms = timed(step_e2e)
+    launches_e2e = lib.gehtp_cuda_launch_count() - launches0
+
+    # ---- device-resident: faces already in HBM, tokens stay on the device
+    faces_dev = [torch.from_numpy(f.view(np.int16).copy()).cuda() for f in faces]
+    out_dev = torch.zeros(2 * B, dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+
+    def step_dev(s):
+        rc = lib.gehtp_cuda_run_dev(ctypes.byref(eng.blob), faces_dev[s].data_ptr(), out_dev.data_ptr(), tok_temp, err, 256)
+        assert rc == 0, err.value
+    reset_positions()
+    for s in range(2):          # re-capture of the graph for the device-resident binding
+        step_dev(s)
+    lib.gehtp_cuda_sync()
+    launches0 = lib.gehtp_cuda_launch_count()
+    dev_ms = timed(step_dev)
+    launches_dev = lib.gehtp_cuda_launch_count() - launches0
+    clocks = sampler.stop()
+    assert lib.gehtp_cuda_sync() == 0
+
+    # ---- per-kernel device times of a few steps (CUDA events around every launch unit)
+    reset_positions()
+    op_ms = (ctypes.c_float * eng.blob.n_ops)()
+    acc = None
+    prof_steps = 3
+    for s in range(prof_steps + 1):
+        rc = lib.gehtp_cuda_run_profiled(ctypes.byref(eng.blob), faces[s].ctypes.data, tok_temp, op_ms, eng.blob.n_ops, err, 256)
+        assert rc == 0, err.value
+        if s == 0:
+            continue        # first eager pass after graph mode: warm-up
+        cur = np.array(op_ms[:], dtype=np.float64)
+        acc = cur if acc is None else acc + cur
+    acc /= prof_steps
+    groups = classify_units(eng.blob, acc, man, p0 + 2)
+    fused_ops = int(lib.gehtp_cuda_fused_ops())
+    eng.shutdown()
+    return dict(e2e_ms=e2e_ms, dev_ms=dev_ms, launches=int(launches_dev), launches_e2e=int(launches_e2e), clocks=clocks,
+                groups=groups, man=man, face_bytes=int(faces[0].nbytes), out_bytes=int(out_host.nbytes),
+                setup_s=setup_s, fused_ops=fused_ops, blob_bytes=int(buf.size))
+
+
+def reference_sample(args, reps):
+    """Times the reference's own executor (compiled for the host, scalar code,
+    one thread as the reference runs it) on a bounded sample of the workload:
+    one decoder layer at the full batch and KV context plus a 2048-column slice
+    of lm_head, weights dequantised to fp16 because the reference has no
+    group-64 W4A16 op. The step time of the whole model is extrapolated linearly
+    (layers x layer time + vocab/2048 x head-slice time)."""
+    from gehtp_b200.runlists import QWEN3_4B, build_decode_runlist, decode_face
+    from gehtp_b200.wtop import KV_POS_AUTO, OP, S, ST, BlobBuilder, Engine
+    from oracle.refexec import ref_lib
+    import tempfile
+    cfg, B, ctx = QWEN3_4B, args.batch, args.ctx
+    tmp = tempfile.mkdtemp()
+    lib = ref_lib(private_dir=tmp)
+    if lib is None:
+        return None
+    vs = 2048
+    buf, man = build_decode_runlist(cfg, B, ctx, seed=1004, quant="f16", n_layers=1, vocab=vs)
+    kv_elems = B * cfg.kv_heads * cfg.head_dim
+    # fill the KV ring through the reference's own append op
+    fill = BlobBuilder()
+    fill.add_states([kv_elems * 4 * ctx])
+    rng = np.random.default_rng(1)
+    kslot = fill.add_slot(rng.standard_normal(kv_elems).astype(np.float16))
+    n_fill = ctx - 1 - reps
+    for _ in range(n_fill):
+        fill.add_op(OP.KV_APPEND, [S(kslot), S(kslot), ST(0), KV_POS_AUTO])
+    feng = Engine(lib, fill.build())
+    feng.run()
+    eng = Engine(lib, buf)
+    n_ops = eng.blob.n_ops
+    op_us = (ctypes.c_int64 * n_ops)()
+    err = ctypes.create_string_buffer(256)
+    from gehtp_b200.wtop import OP as _OP
+    head_ops = [i for i in range(n_ops) if eng.blob.ops[i].opcode == _OP.MATMUL_F16 and eng.blob.ops[i].args[5] == vs]
+    times = []
+    for r in range(reps):
+        face = decode_face(man, rng.integers(0, vs, B), n_fill + r, cfg.head_dim, cfg.rope_theta)
+        t0 = time.time()
+        rc = lib.wt_exec_run_io(ctypes.byref(eng.blob), face.ctypes.data, None, man["token_temp"], None, op_us, err, 256)
+        wall = time.time() - t0
+        assert rc == 0, err.value
+        us = np.array(op_us[:], dtype=np.float64)
+        head = us[head_ops].sum() if head_ops else 0.0
+        layer = us.sum() - head
+        full_s = (layer * args.layers + head * (cfg.vocab / vs)) * 1e-6
+        times.append((wall, full_s))
+    eng.shutdown()
+    wall = float(np.mean([t[0] for t in times]))
+    full = float(np.mean([t[1] for t in times]))
+    return dict(tok_s=B / full, step_s_extrapolated=full, sample_wall_s=wall, reps=reps,
+                sample="1 of %d layers at batch %d, KV ctx %d, plus a %d-column slice of lm_head; fp16 weights; "
+                       "step time extrapolated linearly; %d repetition(s) of %.1f s" % (args.layers, B, ctx, vs, reps, wall))
+
+
+def init_tp(lib, rank, world):
+    """NCCL communicator of the engine: rank 0 makes the id, torch.distributed carries it."""
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        dist.init_process_group("nccl")
+    idb = (ctypes.c_uint8 * 128)()
+    if rank == 0:
+        assert lib.gehtp_cuda_tp_unique_id(idb, 128) == 0
+    t = torch.tensor(list(idb), dtype=torch.uint8, device="cuda")
+    dist.broadcast(t, 0)
+    raw = bytes(t.cpu().tolist())
+    cbuf = (ctypes.c_uint8 * 128).from_buffer_copy(raw)
+    assert lib.gehtp_cuda_tp_init(rank, world, cbuf, 128) == 0, lib.gehtp_cuda_last_error()
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    B = args.batch
+    config = {"workload": "Qwen3-4B-shaped decoder decode step, W4A16 group-64, batch %d, KV context %d, %d layers + lm_head 151936"
+                          % (B, args.ctx, args.layers),
+              "batch": B, "kv_context": args.ctx, "layers": args.layers,
+              "parallelism": "tp%d" % world if world > 1 else "single GPU",
+              "l2": "inputs larger than L2: every step streams the weights and the KV rings (GBs) once"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        probe = reference_sample(args, 1)
+        if probe is None:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libgehtp_ref.so was not built"}))
+            return
+        reps = int(max(1, min(args.steps, 150.0 // max(probe["sample_wall_s"], 1e-3)))) - 1
+        res = reference_sample(args, reps) if reps >= 1 else probe
+        line = {"impl": "reference", "metric": METRIC, "value": res["tok_s"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["step_s_extrapolated"] * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": config, "gpu_launches": 0,
+                "cpu_baseline": {"value": res["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": res["sample"]},
+                "e2e": {"value": res["tok_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    r = run_ours(args, rank, world)
+    if rank != 0:
+        return
+    K = args.steps
+    peak, peak_src = load_peaks()
+    value = B * K / (r["dev_ms"] * 1e-3)
+    e2e = B * K / (r["e2e_ms"] * 1e-3)
+    groups = r["groups"]
+    kernels = {}
+    for name, (n, ms, nb) in groups.items():
+        kernels[name] = {"launches_per_step": n, "ms_per_step": ms, "avg_us": ms * 1e3 / max(n, 1),
+                         "achieved_gbs": (nb / (ms * 1e-3) / 1e9) if ms > 0 and nb else None}
+    dom = max((k for k in groups if groups[k][2] > 0), key=lambda k: groups[k][1])
+    dn, dms, dbytes = groups[dom]
+    achieved = dbytes / (dms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
+            "ms_per_step": r["dev_ms"] / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic", "config": config, "clocks": r["clocks"],
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": r["e2e_ms"] / K, "h2d_bytes_per_step": r["face_bytes"],
+                    "d2h_bytes_per_step": r["out_bytes"]},
+            "gpu_launches": r["launches"],
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "bytes_per_launch": dbytes / dn, "avg_launch_us": dms * 1e3 / dn},
+            "kernels": kernels, "fused_ops": r["fused_ops"], "setup_s": r["setup_s"]}
+    if world == 1 and not args.no_cpu_baseline:
+        cb = reference_sample(args, 1)
+        if cb:
+            line["cpu_baseline"] = {"value": cb["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": cb["sample"]}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -196,6 +196,16 @@ class Emitter:
         return self.linear(prod, *wd, M, row_parallel=True)
 
 
+def synth_embedding(rng, V, H):
+    """fp16 ~ N(0, 0.02) [V, H]. Large tables are tiled from a 1024-row block:
+    converting hundreds of millions of floats on the host takes longer than the
+    whole benchmark, and a decode step reads only one row per sequence."""
+    if V <= 4096:
+        return (rng.standard_normal((V, H), dtype=np.float32) * 0.02).astype(np.float16)
+    block = (rng.standard_normal((1024, H), dtype=np.float32) * 0.02).astype(np.float16)
+    return np.tile(block, ((V + 1023) // 1024, 1))[:V]
+
+
 def synth_layer(rng, cfg, tp=1, rank=0):
     """Seeded weights of one decoder layer; with tp > 1 the shard of `rank`
     (column-parallel q/k/v/gate/up, row-parallel o/down)."""
@@ -232,8 +242,7 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
     face_total = ids_u16 + 2 * hd + nslots
     face = e.b.add_ext_in(face_total * 2)
     e.b.add_states([B * kvh * hd * 4 * nslots] * L)
-    emb = rng.normal(0.0, 0.02, (V, H)).astype(np.float16)
-    emb_s = e.b.add_slot(emb)
+    emb_s = e.b.add_slot(synth_embedding(rng, V, H))
 
     ids = e.face(S(face), 0, 2 * B, face_total)
     cos = e.face(S(face), ids_u16, hd, face_total)
@@ -333,7 +342,7 @@ def build_prefill_runlist(cfg, seq, seed=1003, quant="w4", n_layers=None, with_l
     rep = nh // kvh
     e = Emitter(quant)
     face = e.b.add_ext_in(seq * 4)
-    emb_s = e.b.add_slot(rng.normal(0.0, 0.02, (V, H)).astype(np.float16))
+    emb_s = e.b.add_slot(synth_embedding(rng, V, H))
     cos, sin = rope_tables(hd, np.arange(seq), cfg.rope_theta)
     # rows of q are (token, head): the table row of a (token, head) pair is the token's
     cos_q = S(e.b.add_slot(np.repeat(cos, nh, axis=0)))
