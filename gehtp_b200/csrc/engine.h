@@ -135,6 +135,9 @@ bool ensure_device(char* err, size_t errn);
 // plan.cu
 int build_plan(const wt_blob* b, char* err, size_t errn);
 void drop_plan(bool keep_states);
+// tp.cu
+extern std::vector<uint8_t> g_allreduce_after;   // per op: 1 = all-reduce its first output over the ranks
+int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
 // fuse.cu
 void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal);
 void fuse_materialize(const wt_blob* b);

@@ -854,6 +854,16 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     reset_walk(true);
     g.plan.assign(b->n_ops, PlanOp());
     for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; P.cur = &g.plan[i]; plan_op(P, b->ops[i], g.plan[i]); }
+    // tensor parallel: outputs named as partial sums are all-reduced right after their op
+    if (g.tp_world > 1)
+        for (uint32_t i = 0; i < b->n_ops && i < g_allreduce_after.size(); i++) {
+            PlanOp& p = g.plan[i];
+            if (!g_allreduce_after[i] || p.rc || !p.launch || p.out_id[0] == kNoOff) continue;
+            void* buf = P.addr[p.out_id[0]];
+            size_t elems = p.out_bytes[0] / 2;
+            auto inner = p.launch;
+            p.launch = [=](cudaStream_t st) { inner(st); tp_allreduce_f16(st, buf, elems); };
+        }
     // run-time temp table starts empty; addresses appear as ops execute
     for (uint32_t i = 0; i < kMaxTemps; i++) g.temp_dev[i] = P.addr[i];
 

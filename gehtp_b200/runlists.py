@@ -206,20 +206,51 @@ def synth_embedding(rng, V, H):
     return np.tile(block, ((V + 1023) // 1024, 1))[:V]
 
 
+def cols(w, c0, c1):
+    """Column slice [c0, c1) of a (nibbles, scales) weight pair (c0, c1 even)."""
+    nib, sc = w
+    return np.ascontiguousarray(nib[:, c0 // 2:c1 // 2]), np.ascontiguousarray(sc[:, c0:c1])
+
+
+def rows(w, r0, r1):
+    """Row (K) slice [r0, r1) of a weight pair; r0 and r1 are multiples of the group size 64."""
+    nib, sc = w
+    return np.ascontiguousarray(nib[r0:r1]), np.ascontiguousarray(sc[r0 // 64:r1 // 64])
+
+
+def hcat(*ws):
+    return np.concatenate([w[0] for w in ws], axis=1), np.concatenate([w[1] for w in ws], axis=1)
+
+
 def synth_layer(rng, cfg, tp=1, rank=0):
-    """Seeded weights of one decoder layer; with tp > 1 the shard of `rank`
-    (column-parallel q/k/v/gate/up, row-parallel o/down)."""
+    """Seeded weights of one decoder layer. With tp > 1 every rank draws the
+    same full matrices and keeps its shard: q/k/v heads and gate/up columns are
+    column-parallel, o and down are row-parallel (their K slices fall on
+    multiples of the scale group)."""
     H, hd = cfg.hidden, cfg.head_dim
-    nh, kvh, ffn = cfg.n_heads // tp, cfg.kv_heads // tp, cfg.ffn // tp
-    return dict(
+    NH, KVH, F = cfg.n_heads, cfg.kv_heads, cfg.ffn
+    full = dict(
         g1=rng.normal(1.0, 0.1, H).astype(np.float16),
         g2=rng.normal(1.0, 0.1, H).astype(np.float16),
-        qkv=rand_w4(rng, H, (nh + 2 * kvh) * hd),
-        o=rand_w4(rng, nh * hd, H),
-        gate=rand_w4(rng, H, ffn),
-        up=rand_w4(rng, H, ffn),
-        down=rand_w4(rng, ffn, H),
+        qkv=rand_w4(rng, H, (NH + 2 * KVH) * hd),
+        o=rand_w4(rng, NH * hd, H),
+        gate=rand_w4(rng, H, F),
+        up=rand_w4(rng, H, F),
+        down=rand_w4(rng, F, H),
     )
+    if tp == 1:
+        return full
+    nh, kvh, f = NH // tp, KVH // tp, F // tp
+    assert NH % tp == 0 and KVH % tp == 0 and F % tp == 0 and (nh * hd) % 64 == 0 and f % 64 == 0
+    q0, k0, v0 = 0, NH * hd, (NH + KVH) * hd
+    full["qkv"] = hcat(cols(full["qkv"], q0 + rank * nh * hd, q0 + (rank + 1) * nh * hd),
+                       cols(full["qkv"], k0 + rank * kvh * hd, k0 + (rank + 1) * kvh * hd),
+                       cols(full["qkv"], v0 + rank * kvh * hd, v0 + (rank + 1) * kvh * hd))
+    full["o"] = rows(full["o"], rank * nh * hd, (rank + 1) * nh * hd)
+    full["gate"] = cols(full["gate"], rank * f, (rank + 1) * f)
+    full["up"] = cols(full["up"], rank * f, (rank + 1) * f)
+    full["down"] = rows(full["down"], rank * f, (rank + 1) * f)
+    return full
 
 
 def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, with_lm_head=True,
@@ -290,7 +321,7 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
                input_slot=face, quant=quant, tp=tp, rank=rank)
     if with_lm_head:
         Vs = V // tp
-        logits = e.linear(hn, *rand_w4(rng, H, Vs), B)
+        logits = e.linear(hn, *cols(rand_w4(rng, H, V), rank * Vs, (rank + 1) * Vs), B)
         toks = []
         for bi in range(B):
             row = e.slice2(logits, B, Vs, 0, Vs) if B == 1 else e.fresh()
@@ -311,6 +342,11 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
                 nxt.append((e.concat([t for t, _ in grp], [w for _, w in grp], total), total))
             toks = nxt
         toks = [toks[0][0]]
+        if tp > 1:
+            # row maxima next to the shard-local argmax, so that ranks can be merged: [tokens int32 x B | max f16 x B]
+            mx = e.fresh()
+            e.b.add_op(OP.REDUCE, [logits, mx, B * Vs, 1, 2, B, Vs, 1, 1])
+            toks = [e.concat([toks[0], mx], [2 * B, B], 3 * B)]
         man.update(logits_temp=logits, token_temp=toks[0], vocab_shard=Vs)
     man["row_parallel_ops"] = e.row_parallel_ops
     man["n_ops"] = len(e.b.ops)
