@@ -164,7 +164,7 @@ def run_ours(args, rank, world):
     if world > 1:
         idx = (ctypes.c_uint32 * len(man["row_parallel_ops"]))(*man["row_parallel_ops"])
         assert lib.gehtp_cuda_tp_allreduce_after(idx, len(man["row_parallel_ops"])) == 0
-    total_steps = W + K
+    total_steps = max(W + K, 6)
     p0 = max(ctx - total_steps, 0)
 
     # KV rings ~ N(0,1) for positions [0, ctx), generated on the device

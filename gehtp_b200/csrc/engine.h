@@ -83,7 +83,7 @@ struct Engine {
     uint8_t* st_buf[WT_MAX_STATES];
     uint32_t st_bytes[WT_MAX_STATES];
     uint32_t st_count[WT_MAX_STATES];   // host mirror of the AUTO position counters
-    uint32_t* d_st_count = nullptr;     // device, WT_MAX_STATES entries
+    uint32_t* d_st_count = nullptr;     // device: WT_MAX_STATES counters, then WT_MAX_STATES arrival counts of the merge kernel
     KvGeom kv[WT_MAX_STATES];
 
     unsigned int* d_status = nullptr;   // first failing op (1-based) raised by a kernel

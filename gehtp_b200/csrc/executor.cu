@@ -33,8 +33,8 @@ bool ensure_device(char* err, size_t errn) {
     if (dev >= n || cudaSetDevice(dev) != cudaSuccess) { set_err(err, errn, "no CUDA device"); return false; }
     g.device = dev;
     if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess) { set_err(err, errn, "no CUDA device"); return false; }
-    cudaMalloc(&g.d_st_count, WT_MAX_STATES * sizeof(uint32_t));
-    cudaMemset(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t));
+    cudaMalloc(&g.d_st_count, 2 * WT_MAX_STATES * sizeof(uint32_t));
+    cudaMemset(g.d_st_count, 0, 2 * WT_MAX_STATES * sizeof(uint32_t));
     cudaMalloc(&g.d_status, sizeof(unsigned int));
     cudaMemset(g.d_status, 0, sizeof(unsigned int));
     cudaMallocHost(&g.h_status, sizeof(unsigned int));
@@ -479,7 +479,7 @@ void wt_exec_state_reset(void) {
         g.st_count[i] = 0;
         if (g.kv[i].ready) cudaMemsetAsync(g.kv[i].posmap, 0xFF, (size_t)g.kv[i].nslots * 4, g.stream);
     }
-    cudaMemsetAsync(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t), g.stream);
+    cudaMemsetAsync(g.d_st_count, 0, 2 * WT_MAX_STATES * sizeof(uint32_t), g.stream);
     cudaStreamSynchronize(g.stream);
 }
 

@@ -16,9 +16,11 @@
 // the rows of a 16-row tensor-core tile, so K and V are read once per group.
 // K/V tiles of 64 positions are staged in shared memory with cp.async (3
 // stages, 16-byte chunks XOR-swizzled by row), read back with ldmatrix and
-// multiplied with mma.sync m16n8k16. Each CTA writes (max, sum, unnormalised
-// output) for its slice to a scratch buffer; a second small kernel merges the
-// slices in slice order.
+// multiplied with mma.sync m16n8k16. The context is cut into chunks of 256
+// positions; a (KV head, chunk) pair is a work item, items are dealt round-robin
+// to 2 CTAs per SM, and a CTA streams the tiles of its items back to back. Each
+// item leaves (max, sum, unnormalised output) in a scratch buffer; a second
+// small kernel merges the chunks in chunk order.
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "launchers_attn.h"
@@ -30,6 +32,7 @@ namespace {
 constexpr int TILE = 64;      // positions per stage
 constexpr int STAGES = 3;
 constexpr int NWARP = 4;      // 16 positions of a tile each
+constexpr int CHUNK_POS = 256;   // positions per work item (4 tiles)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -71,56 +74,49 @@ __device__ __forceinline__ float chain_score(float dot, float scale, int scale_d
 
 template <int HD>
 __global__ void __launch_bounds__(NWARP * 32)
-attn_decode_split_kernel(AttnDecodeArgs A) {
+attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     constexpr int ROWB = HD * 2;          // bytes per K or V row
     constexpr int CHUNKS = ROWB / 16;     // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
     constexpr int DBLK = HD / 8;
+    constexpr int STAGE_B = 2 * TILE * ROWB;
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t kvh = blockIdx.x, split = blockIdx.y;
     const uint32_t rep = A.rep;
     const uint32_t n_kv = A.counter ? *A.counter + A.n_kv_add : A.n_kv;
-    uint32_t per = (n_kv + A.nsplit - 1) / A.nsplit;
-    per = (per + TILE - 1) / TILE * TILE;
-    const uint32_t p_begin = split * per;
-    const uint32_t p_end = (p_begin + per < n_kv) ? p_begin + per : n_kv;
+    const uint32_t n_chunks = (n_kv + CHUNK_POS - 1) / CHUNK_POS;   // <= A.nsplit by construction
+    const uint32_t n_items = kv_heads_total * n_chunks;
     const uint32_t kv_elems = A.kv_heads * HD;
-    const uint16_t* ring_k = A.ring + (size_t)kvh * HD;
-    const uint16_t* maskp = A.mask ? A.mask + (size_t)(kvh / A.kvh_per_seq) * A.mask_seq_stride : nullptr;
+    float* sm_o = (float*)(smem + STAGES * STAGE_B);     // [NWARP][rep][HD]
+    float* sm_ml = sm_o + NWARP * rep * HD;               // [NWARP][rep][2]
 
-    // Q fragments: rows = the group's query heads (zero rows beyond rep)
-    uint32_t qa[KSTEPS][4];
-    {
-        const uint16_t* q0 = A.q + ((size_t)kvh * rep + g) * HD;
-        const uint16_t* q1 = A.q + ((size_t)kvh * rep + g + 8) * HD;
-#pragma unroll
-        for (int j = 0; j < KSTEPS; j++) {
-            qa[j][0] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t) : 0u;
-            qa[j][1] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t) : 0u;
-            qa[j][2] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t + 8) : 0u;
-            qa[j][3] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t + 8) : 0u;
-        }
-    }
-
-    float o[DBLK][4];
-#pragma unroll
-    for (int i = 0; i < DBLK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-
-    const int ntiles = p_end > p_begin ? (int)((p_end - p_begin + TILE - 1) / TILE) : 0;
-    auto issue = [&](int tile) {
-        if (tile < ntiles) {
-            unsigned char* sk = smem + (size_t)(tile % STAGES) * (2 * TILE * ROWB);
+    // A work item = (KV head, chunk of CHUNK_POS positions); this CTA takes items
+    // blockIdx.x, blockIdx.x + gridDim.x, ... and streams their tiles back to back,
+    // so the copy pipeline never drains between items.
+    struct Cursor { uint32_t item, tile; };
+    auto tiles_of = [&](uint32_t item) -> uint32_t {
+        uint32_t pb = (item % n_chunks) * CHUNK_POS;
+        uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
+        return (pe - pb + TILE - 1) / TILE;
+    };
+    auto advance = [&](Cursor& c) {
+        if (++c.tile >= tiles_of(c.item)) { c.item += gridDim.x; c.tile = 0; }
+    };
+    auto issue = [&](const Cursor& c, uint32_t stage) {
+        if (c.item < n_items) {
+            const uint32_t kvh = c.item / n_chunks;
+            const uint32_t pb = (c.item % n_chunks) * CHUNK_POS;
+            const uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
+            const uint32_t p0 = pb + c.tile * TILE;
+            unsigned char* sk = smem + (size_t)stage * STAGE_B;
             unsigned char* sv = sk + TILE * ROWB;
-            const uint32_t p0 = p_begin + tile * TILE;
+            const uint16_t* base = A.ring + (size_t)kvh * HD;
             for (int idx = tid; idx < TILE * CHUNKS; idx += NWARP * 32) {
                 int row = idx / CHUNKS, ch = idx % CHUNKS;
                 uint32_t p = p0 + row;
-                bool ok = p < p_end;
-                uint32_t slot = ok ? p % A.nslots : 0;
-                const uint16_t* src = ring_k + (size_t)slot * kv_elems * 2 + ch * 8;
+                bool ok = p < pe;
+                const uint16_t* src = base + (size_t)(ok ? p : 0) * kv_elems * 2 + ch * 8;   // slot = position: no wrap below nslots
                 int so = row * ROWB + ((ch ^ (row & 7)) << 4);
                 cp_async16(sk + so, src, ok);
                 cp_async16(sv + so, src + kv_elems, ok);
@@ -128,18 +124,48 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
         }
         cp_async_commit();
     };
-    issue(0);
-    issue(1);
 
-    for (int tile = 0; tile < ntiles; tile++) {
-        issue(tile + 2);
-        cp_async_wait<2>();
+    Cursor ic{blockIdx.x, 0}, cc{blockIdx.x, 0};
+    uint32_t si = 0, sc = 0;
+    for (int s = 0; s < STAGES - 1; s++) {
+        issue(ic, si % STAGES);
+        if (ic.item < n_items) advance(ic);
+        si++;
+    }
+
+    uint32_t qa[KSTEPS][4];
+    float o[DBLK][4];
+    float m_run[2], l_run[2];
+    while (cc.item < n_items) {
+        const uint32_t kvh = cc.item / n_chunks, chunk = cc.item % n_chunks;
+        const uint32_t pb = chunk * CHUNK_POS;
+        const uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
+        if (cc.tile == 0) {
+            const uint16_t* q0 = A.q + ((size_t)kvh * rep + g) * HD;
+            const uint16_t* q1 = A.q + ((size_t)kvh * rep + g + 8) * HD;
+#pragma unroll
+            for (int j = 0; j < KSTEPS; j++) {
+                qa[j][0] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t) : 0u;
+                qa[j][1] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t) : 0u;
+                qa[j][2] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t + 8) : 0u;
+                qa[j][3] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t + 8) : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < DBLK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+            m_run[0] = m_run[1] = -INFINITY;
+            l_run[0] = l_run[1] = 0.0f;
+        }
+        issue(ic, si % STAGES);
+        if (ic.item < n_items) advance(ic);
+        si++;
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
-        const unsigned char* sk = smem + (size_t)(tile % STAGES) * (2 * TILE * ROWB);
+        const unsigned char* sk = smem + (size_t)(sc % STAGES) * STAGE_B;
         const unsigned char* sv = sk + TILE * ROWB;
         const int wrow0 = warp * 16;
-        const uint32_t pw0 = p_begin + tile * TILE + wrow0;
-        if (pw0 < p_end) {
+        const uint32_t pw0 = pb + cc.tile * TILE + wrow0;
+        const uint16_t* maskp = A.mask ? A.mask + (size_t)(kvh / A.kvh_per_seq) * A.mask_seq_stride : nullptr;
+        if (pw0 < pe) {
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int j = 0; j < KSTEPS; j++) {
@@ -151,7 +177,6 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
                 mma_f16(s[0], qa[j], kb[0], kb[1]);
                 mma_f16(s[1], qa[j], kb[2], kb[3]);
             }
-            // scores -> chain roundings, mask, running max
             float x[2][4];
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -160,7 +185,7 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
                 for (int c = 0; c < 4; c++) {
                     uint32_t p = pw0 + nb * 8 + 2 * t + (c & 1);
                     float v = -INFINITY;
-                    if (p < p_end) {
+                    if (p < pe) {
                         float mk = maskp ? __half2float(__ushort_as_half(maskp[p])) : 0.0f;
                         v = chain_score(s[nb][c], A.scale, A.scale_div, mk);
                     }
@@ -173,7 +198,7 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
                 float m_new = fmaxf(m_run[h], mx[h]);
-                alpha[h] = (m_new == -INFINITY) ? 1.0f : expf(m_run[h] - m_new);
+                alpha[h] = (m_new == -INFINITY) ? 1.0f : __expf(m_run[h] - m_new);
                 m_run[h] = m_new;
                 l_run[h] *= alpha[h];
             }
@@ -185,7 +210,7 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
                         float mr = m_run[c >> 1];
-                        float e = (mr == -INFINITY) ? 0.0f : expf(x[nb][c] - mr);
+                        float e = (mr == -INFINITY) ? 0.0f : __expf(x[nb][c] - mr);
                         pv[nb][c] = e;
                         l_run[c >> 1] += e;
                     }
@@ -194,10 +219,12 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
                 pa[2] = pack_h2(pv[1][0], pv[1][1]);
                 pa[3] = pack_h2(pv[1][2], pv[1][3]);
             }
+            if (alpha[0] != 1.0f || alpha[1] != 1.0f) {
 #pragma unroll
-            for (int i = 0; i < DBLK; i++) {
-                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                for (int i = 0; i < DBLK; i++) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                    o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
             }
 #pragma unroll
             for (int dp = 0; dp < DBLK / 2; dp++) {
@@ -210,85 +237,90 @@ attn_decode_split_kernel(AttnDecodeArgs A) {
                 mma_f16(o[dp * 2 + 1], pa, vb[2], vb[3]);
             }
         }
-        __syncthreads();
+        sc++;
+        const bool last = cc.tile + 1 >= tiles_of(cc.item);
+        if (last) {
+            // merge the four warps (disjoint quarters of every tile) and store the item's partial result
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+                l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+            }
+#pragma unroll
+            for (int i = 0; i < DBLK; i++) {
+                int d = i * 8 + 2 * t;
+                if ((uint32_t)g < rep) { sm_o[(warp * rep + g) * HD + d] = o[i][0]; sm_o[(warp * rep + g) * HD + d + 1] = o[i][1]; }
+                if ((uint32_t)(g + 8) < rep) { sm_o[(warp * rep + g + 8) * HD + d] = o[i][2]; sm_o[(warp * rep + g + 8) * HD + d + 1] = o[i][3]; }
+            }
+            if (t == 0) {
+                if ((uint32_t)g < rep) { sm_ml[(warp * rep + g) * 2] = m_run[0]; sm_ml[(warp * rep + g) * 2 + 1] = l_run[0]; }
+                if ((uint32_t)(g + 8) < rep) { sm_ml[(warp * rep + g + 8) * 2] = m_run[1]; sm_ml[(warp * rep + g + 8) * 2 + 1] = l_run[1]; }
+            }
+        }
+        __syncthreads();   // stage (sc-1) is free for the next copy; merge buffers are complete
+        if (last) {
+            float* po = A.part_o + ((size_t)kvh * A.nsplit + chunk) * rep * HD;
+            float* pml = A.part_ml + ((size_t)kvh * A.nsplit + chunk) * rep * 2;
+            for (uint32_t e = tid; e < rep * HD; e += NWARP * 32) {
+                uint32_t r = e / HD, d = e % HD;
+                float mt = -INFINITY;
+                for (int w = 0; w < NWARP; w++) mt = fmaxf(mt, sm_ml[(w * rep + r) * 2]);
+                float acc = 0.0f, lt = 0.0f;
+                for (int w = 0; w < NWARP; w++) {
+                    float mw = sm_ml[(w * rep + r) * 2];
+                    float wgt = (mw == -INFINITY) ? 0.0f : __expf(mw - mt);
+                    acc += sm_o[(w * rep + r) * HD + d] * wgt;
+                    lt += sm_ml[(w * rep + r) * 2 + 1] * wgt;
+                }
+                po[e] = acc;
+                if (d == 0) { pml[r * 2] = mt; pml[r * 2 + 1] = lt; }
+            }
+        }
+        advance(cc);
     }
     cp_async_wait<0>();
-    __syncthreads();
-
-    // merge the four warps (each saw a disjoint quarter of every tile)
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
-    float* sm_o = (float*)smem;                       // [NWARP][16][HD]
-    float* sm_ml = sm_o + NWARP * 16 * HD;            // [NWARP][16][2]
-#pragma unroll
-    for (int i = 0; i < DBLK; i++) {
-        int d = i * 8 + 2 * t;
-        sm_o[(warp * 16 + g) * HD + d] = o[i][0];
-        sm_o[(warp * 16 + g) * HD + d + 1] = o[i][1];
-        sm_o[(warp * 16 + g + 8) * HD + d] = o[i][2];
-        sm_o[(warp * 16 + g + 8) * HD + d + 1] = o[i][3];
-    }
-    if (t == 0) {
-        sm_ml[(warp * 16 + g) * 2] = m_run[0];
-        sm_ml[(warp * 16 + g) * 2 + 1] = l_run[0];
-        sm_ml[(warp * 16 + g + 8) * 2] = m_run[1];
-        sm_ml[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
-    }
-    __syncthreads();
-    float* po = A.part_o + ((size_t)kvh * A.nsplit + split) * rep * HD;
-    float* pml = A.part_ml + ((size_t)kvh * A.nsplit + split) * rep * 2;
-    for (uint32_t e = tid; e < rep * HD; e += NWARP * 32) {
-        uint32_t r = e / HD, d = e % HD;
-        float mt = -INFINITY;
-        for (int w = 0; w < NWARP; w++) mt = fmaxf(mt, sm_ml[(w * 16 + r) * 2]);
-        float acc = 0.0f, lt = 0.0f;
-        for (int w = 0; w < NWARP; w++) {
-            float mw = sm_ml[(w * 16 + r) * 2];
-            float wgt = (mw == -INFINITY) ? 0.0f : expf(mw - mt);
-            acc += sm_o[(w * 16 + r) * HD + d] * wgt;
-            lt += sm_ml[(w * 16 + r) * 2 + 1] * wgt;
-        }
-        po[e] = acc;
-        if (d == 0) { pml[r * 2] = mt; pml[r * 2 + 1] = lt; }
-    }
 }
 
-// out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}, slices in order.
+// out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}, chunks in order.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit,
+                                         const uint32_t* counter, uint32_t n_kv_add, uint32_t n_kv_const,
                                          uint32_t* bump_counter) {
     const uint32_t h = blockIdx.x;           // query head, = kvh * rep + r
     const uint32_t kvh = h / rep, r = h % rep;
+    const uint32_t n_kv = counter ? *counter + n_kv_add : n_kv_const;
+    const uint32_t n_chunks = (n_kv + CHUNK_POS - 1) / CHUNK_POS;
     float mt = -INFINITY;
-    for (uint32_t s = 0; s < nsplit; s++) mt = fmaxf(mt, part_ml[(((size_t)kvh * nsplit + s) * rep + r) * 2]);
+    for (uint32_t s = 0; s < n_chunks; s++) mt = fmaxf(mt, part_ml[(((size_t)kvh * nsplit + s) * rep + r) * 2]);
     for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.0f, lt = 0.0f;
-        for (uint32_t s = 0; s < nsplit; s++) {
+        for (uint32_t s = 0; s < n_chunks; s++) {
             size_t base = ((size_t)kvh * nsplit + s) * rep + r;
             float ms = part_ml[base * 2];
-            float w = (ms == -INFINITY) ? 0.0f : expf(ms - mt);
+            float w = (ms == -INFINITY) ? 0.0f : __expf(ms - mt);
             acc += part_o[base * hd + d] * w;
             lt += part_ml[base * 2 + 1] * w;
         }
         out[(size_t)h * hd + d] = f2h(lt > 0.0f ? acc / lt : 0.0f);
     }
-    // every reader of the counter (the split kernel) has finished: stream order
-    if (bump_counter && blockIdx.x == 0 && threadIdx.x == 0) *bump_counter += 1;
+    // all readers of the counter in this launch must be done before it moves: the
+    // last block to finish advances it
+    if (bump_counter) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            unsigned int done = atomicAdd(bump_counter + 64, 1u) + 1;   // arrival count kept beside the counters
+            if (done == gridDim.x) { bump_counter[64] = 0; *bump_counter += 1; }
+        }
+    }
 }
 
 }  // namespace
 
 uint32_t attn_decode_pick_splits(uint32_t kv_heads_total, uint32_t max_positions) {
-    // aim at two CTAs per SM, at least one 64-position tile per slice
-    uint32_t want = (2 * 148 + kv_heads_total - 1) / kv_heads_total;
-    uint32_t most = (max_positions + TILE - 1) / TILE;
-    if (want > most) want = most;
-    if (want < 1) want = 1;
-    if (want > 64) want = 64;
-    return want;
+    (void)kv_heads_total;
+    uint32_t n = (max_positions + CHUNK_POS - 1) / CHUNK_POS;
+    return n ? n : 1;
 }
 
 size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_t hd, uint32_t nsplit) {
@@ -297,20 +329,20 @@ size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_
 
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out, uint32_t kv_heads_total) {
     if (a.rep == 0 || a.rep > 16 || (hd != 128 && hd != 64)) return false;
-    dim3 grid(kv_heads_total, a.nsplit);
-    size_t smem = (size_t)STAGES * 2 * TILE * hd * 2;
-    size_t merge = (size_t)NWARP * 16 * (hd + 2) * sizeof(float);
-    if (merge > smem) smem = merge;
+    size_t smem = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)NWARP * a.rep * (hd + 2) * sizeof(float);
+    uint32_t items = kv_heads_total * a.nsplit;
+    uint32_t grid = items < 2 * 148 ? items : 2 * 148;
     if (hd == 128) {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(attn_decode_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
-        attn_decode_split_kernel<128><<<grid, NWARP * 32, smem, st>>>(a);
+        static size_t attr = 0;
+        if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
+        attn_decode_split_kernel<128><<<grid, NWARP * 32, smem, st>>>(a, kv_heads_total);
     } else {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(attn_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
-        attn_decode_split_kernel<64><<<grid, NWARP * 32, smem, st>>>(a);
+        static size_t attr = 0;
+        if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
+        attn_decode_split_kernel<64><<<grid, NWARP * 32, smem, st>>>(a, kv_heads_total);
     }
-    attn_decode_merge_kernel<<<kv_heads_total * a.rep, hd < 128 ? 64 : 128, 0, st>>>(a.part_o, a.part_ml, out, a.rep, hd, a.nsplit, a.bump_counter);
+    attn_decode_merge_kernel<<<kv_heads_total * a.rep, hd < 128 ? 64 : 128, 0, st>>>(
+        a.part_o, a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter);
     g_launches += 2;
     return true;
 }

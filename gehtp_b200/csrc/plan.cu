@@ -733,7 +733,7 @@ int load_states(const wt_blob* b, char* err, size_t errn) {
             g.kv[i] = KvGeom();
         }
         g.n_states = 0;
-        cudaMemsetAsync(g.d_st_count, 0, WT_MAX_STATES * sizeof(uint32_t), g.stream);
+        cudaMemsetAsync(g.d_st_count, 0, 2 * WT_MAX_STATES * sizeof(uint32_t), g.stream);
         for (uint32_t i = 0; i < n; i++) {
             uint32_t bytes = wt_rd_u32(p + 4 + (size_t)i * 4);
             if (bytes == 0) { std::snprintf(err, errn, "state %u bytes bad %u", i, bytes); return -1; }
