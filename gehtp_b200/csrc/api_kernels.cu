@@ -45,7 +45,9 @@ int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y
     }
     if (!done) k_w4a16_skinny(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep);
     cudaMemcpyAsync(y_f16, dy.p, (size_t)M * N * 2, cudaMemcpyDeviceToHost, g.stream);
-    return finish("w4a16 matmul");
+    if (finish("w4a16 matmul")) return -1;
+    if (done && w4a16_gemm_timeouts()) return fail("tcgen05 GEMM: a barrier wait ran out");
+    return 0;
 }
 
 int gehtp_w4a16_unpack(const uint8_t* w_slot, int8_t* out_i8, uint32_t K, uint32_t N) {

@@ -47,4 +47,7 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
                         const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
                         const W4Epilogue& ep);
 
+// CTAs of the tcgen05 GEMM that gave up on a barrier since the process started (0 in a healthy run).
+unsigned int w4a16_gemm_timeouts();
+
 }  // namespace gehtp

@@ -53,6 +53,23 @@ def test_w4a16_matmul_vs_oracle(cuda, orc, M, K, N):
     assert_fp16_close(got, want, "w4a16 %dx%dx%d" % (M, K, N))
 
 
+@pytest.mark.parametrize("M,K,N", [(128, 1024, 3072), (128, 64, 128), (256, 512, 384), (200, 2560, 1280), (512, 1024, 4096)])
+def test_w4a16_tcgen05_gemm_vs_oracle(cuda, orc, M, K, N):
+    """The tensor-core (tcgen05 / TMEM) path on its own, config 1 of the baseline first."""
+    rng = np.random.default_rng(1001)
+    a = rng.standard_normal((M, K)).astype(np.float16)
+    nib, scales = rand_w4(rng, K, N)
+    slot = slot_bytes(nib, scales)
+    got = np.zeros((M, N), np.float16)
+    assert cuda.gehtp_w4a16_matmul(ptr(a), ptr(slot), ptr(got), M, K, N, 2) == 0, cuda.gehtp_cuda_last_error()
+    want = np.zeros((M, N), np.float16)
+    orc.orc_w4a16_matmul(ptr(a), ptr(slot), ptr(want), M, K, N)
+    assert_fp16_close(got, want, "tcgen05 w4a16 %dx%dx%d" % (M, K, N))
+    skinny = np.zeros((M, N), np.float16)
+    assert cuda.gehtp_w4a16_matmul(ptr(a), ptr(slot), ptr(skinny), M, K, N, 1) == 0
+    assert_fp16_close(got, skinny, "tcgen05 vs streaming kernel")
+
+
 def test_w4a16_exact_on_small_integers(cuda, orc):
     """With integer activations and power-of-two scales every product and sum is
     exact in fp32, so the result must equal the oracle bit for bit whatever the
