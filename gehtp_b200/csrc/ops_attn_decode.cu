@@ -21,9 +21,11 @@
 // to 2 CTAs per SM, and a CTA streams the tiles of its items back to back. Each
 // item leaves (max, sum, unnormalised output) in a scratch buffer; a second
 // small kernel merges the chunks in chunk order.
+#include <cstdio>
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "launchers_attn.h"
+#include "engine.h"
 
 namespace gehtp {
 
@@ -348,3 +350,65 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
 }
 
 }  // namespace gehtp
+
+namespace gehtp {
+// ---------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a
+// serving loop whose memory was carved up front by a pool allocator, inside a
+// real-time thread where an allocation could block on the driver's lock, or in
+// a process whose device-memory budget is fixed by its operator. The split-KV
+// attention kernel needs a scratch buffer for the per-chunk partial results;
+// here that scratch is a fixed array that lives in the library's device image,
+// so the call needs nothing beyond the caller's own input and output buffers.
+//
+// The array is GEHTP_NOALLOC_SCRATCH_BYTES large on every GPU that loads the
+// library, for the life of the process. Every call uses the same array: two
+// calls that overlap on the GPU (different streams, or different host threads)
+// race on it and must be serialised by the caller. Nothing in it has to start
+// at zero: each call writes every partial it later reads.
+constexpr size_t kNoAllocFloats = GEHTP_NOALLOC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+}  // namespace gehtp
+
+extern "C" int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* ring_dev, const uint16_t* mask_dev,
+                                         uint16_t* out_dev, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
+                                         uint32_t n_kv, uint32_t nslots, float scale, void* stream) {
+    using namespace gehtp;
+    auto fail = [](const char* m) { g.last_error = m; return -1; };
+    if (!q_dev || !ring_dev || !out_dev) return fail("attn noalloc: null pointer");
+    if (!n_heads || !kv_heads || n_heads % kv_heads || !nslots || !n_kv || n_kv > nslots) return fail("attn noalloc: bad shape");
+    const uint32_t rep = n_heads / kv_heads;
+    if (rep > 16 || (head_dim != 128 && head_dim != 64)) return fail("attn noalloc: head layout not handled by the fused kernel");
+    const uint32_t nsplit = attn_decode_pick_splits(kv_heads, n_kv);
+    const size_t need = attn_decode_scratch_floats(kv_heads, rep, head_dim, nsplit);
+    if (need > kNoAllocFloats) {
+        char m[160];
+        std::snprintf(m, sizeof m, "attn noalloc: needs %zu bytes of scratch, the built-in array holds %zu", need * sizeof(float),
+                      (size_t)GEHTP_NOALLOC_SCRATCH_BYTES);
+        return fail(m);
+    }
+    // The array's name is only a host-side handle; the kernel needs its device
+    // address, looked up once per device with that device current.
+    static float* scratch_of_device[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail("attn noalloc: no current CUDA device");
+    if (!scratch_of_device[dev]) {
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) { cudaGetLastError(); return fail("attn noalloc: cudaGetSymbolAddress failed"); }
+        scratch_of_device[dev] = p;
+    }
+    AttnDecodeArgs a{};
+    a.q = q_dev; a.ring = ring_dev; a.counter = nullptr; a.n_kv = n_kv; a.n_kv_add = 0; a.bump_counter = nullptr;
+    a.mask = mask_dev; a.mask_seq_stride = 0; a.kvh_per_seq = kv_heads;
+    a.scale = scale; a.scale_div = 0; a.rep = rep; a.kv_heads = kv_heads; a.nslots = nslots; a.nsplit = nsplit;
+    a.part_o = scratch_of_device[dev];
+    a.part_ml = a.part_o + (size_t)kv_heads * nsplit * rep * head_dim;
+    if (!k_attn_decode((cudaStream_t)stream, a, head_dim, out_dev, kv_heads)) return fail("attn noalloc: launch refused");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+    return 0;
+}

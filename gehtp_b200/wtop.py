@@ -203,6 +203,8 @@ def bind(lib):
         lib.gehtp_rmsnorm.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32]
         lib.gehtp_attn_decode.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32,
                                           c.c_uint32, c.c_uint32, c.c_uint32, c.c_float]
+        lib.gehtp_attn_decode_noalloc.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32,
+                                                  c.c_uint32, c.c_uint32, c.c_uint32, c.c_float, c.c_void_p]
     return lib
 
 

@@ -210,6 +210,28 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
                       uint16_t* out, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
                       uint32_t n_kv, uint32_t nslots, float scale);
 
+/* No counterpart in the reference. The same decode attention as
+ * gehtp_attn_decode, for callers that are not allowed to allocate device memory
+ * (a serving loop living inside a pre-carved memory pool, a latency-critical
+ * thread that must not take the driver's allocation lock, a process with a fixed
+ * device-memory budget). All four buffers are DEVICE pointers owned by the caller
+ * (q and out: n_heads*head_dim fp16; ring: nslots*2*kv_heads*head_dim fp16; mask:
+ * n_kv fp16 or NULL). The kernel's scratch is a fixed array inside the library's
+ * device image: GEHTP_NOALLOC_SCRATCH_BYTES on every GPU that loads the library,
+ * held until the process exits. The call allocates and frees nothing, only
+ * queues work on `stream` (a cudaStream_t, NULL = default stream) of the current
+ * device, and does not wait for it.
+ * Limit: kv_heads * ceil(n_kv/256) * (n_heads/kv_heads) * (head_dim+2) * 4 bytes
+ * must fit in the array; larger problems return -1 with a message in
+ * gehtp_cuda_last_error(). The first call on each device looks up the array's
+ * device address; make that first call before starting any stream capture.
+ * All calls share the one array and it keeps whatever the last call left in it:
+ * calls that overlap on the GPU race and must be serialised by the caller. */
+#define GEHTP_NOALLOC_SCRATCH_BYTES (5u * 1024u * 1024u)
+int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* ring_dev, const uint16_t* mask_dev,
+                              uint16_t* out_dev, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
+                              uint32_t n_kv, uint32_t nslots, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
