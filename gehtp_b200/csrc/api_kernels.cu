@@ -84,7 +84,7 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
     if (!n_heads || !kv_heads || n_heads % kv_heads || !nslots || n_kv > nslots) return fail("attn shape");
     uint32_t rep = n_heads / kv_heads;
     size_t ring_b = (size_t)nslots * kv_heads * head_dim * 4, q_b = (size_t)n_heads * head_dim * 2;
-    uint32_t nsplit = attn_decode_pick_splits(kv_heads, n_kv);
+    uint32_t nsplit = attn_decode_nsplit(kv_heads, n_kv, rep, head_dim, 0);
     size_t scr = attn_decode_scratch_floats(kv_heads, rep, head_dim, nsplit);
     DevBuf dq(q_b), dr(ring_b), dm((size_t)n_kv * 2), dout(q_b), dscr(scr * 4);
     if (!dq.p || !dr.p || !dm.p || !dout.p || !dscr.p) return fail("device alloc");
@@ -100,6 +100,49 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
     if (!k_attn_decode(g.stream, a, head_dim, dout.as<uint16_t>(), kv_heads)) return fail("attn shape not handled by the fused kernel");
     cudaMemcpyAsync(out, dout.p, q_b, cudaMemcpyDeviceToHost, g.stream);
     return finish("attn decode");
+}
+
+}  // extern "C"
+
+// ---- device-pointer entry points: the caller owns every buffer (device
+// memory) and the work is queued on the engine stream without waiting. Used by
+// the bench to time single kernels with inputs resident in HBM.
+extern "C" {
+
+int gehtp_dev_w4_repack(const uint8_t* slot_dev, uint32_t* packed_dev, uint32_t K, uint32_t N) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (!K || !N || K % 64 || N % 16) return fail("w4a16 shape");
+    k_w4_repack(g.stream, slot_dev, packed_dev, K, N);
+    return 0;
+}
+
+// path: 0 = engine's choice by M, 1 = streaming kernel, 2 = tcgen05 GEMM
+int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
+                           uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N, int path) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (!M || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
+    W4Epilogue ep;
+    if (path == 2 || (path == 0 && M >= 128)) {
+        if (k_w4a16_gemm_sm100(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep)) return 0;
+        if (path == 2) return fail("tcgen05 GEMM does not take this shape");
+    }
+    k_w4a16_skinny(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep);
+    return 0;
+}
+
+int gehtp_dev_w4a16_swiglu(const uint16_t* a_dev, const uint32_t* pg, const uint16_t* sg, const uint32_t* pu,
+                           const uint16_t* su, uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (!M || M > 16 || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
+    k_w4a16_skinny_swiglu(g.stream, a_dev, pg, sg, pu, su, y_dev, M, K, N);
+    return 0;
+}
+
+int gehtp_dev_rmsnorm(const uint16_t* x_dev, const uint16_t* res_dev, const uint16_t* gamma_dev, const uint16_t* beta_dev,
+                      uint16_t* sum_dev, uint16_t* y_dev, uint32_t rows, uint32_t width) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    k_add_rmsnorm(g.stream, x_dev, res_dev, gamma_dev, beta_dev, sum_dev, y_dev, rows, width);
+    return 0;
 }
 
 }  // extern "C"

@@ -36,4 +36,19 @@ __device__ __forceinline__ void raise_status(unsigned int* status, unsigned int 
     if (status) atomicCAS(status, 0u, code);
 }
 
+// Launch with programmatic dependent launch allowed: the grid may start while
+// its predecessor in the stream is still running; the kernel orders itself
+// after the predecessor with griddepcontrol.wait before it touches anything the
+// predecessor wrote (and writes nothing before that point).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace gehtp

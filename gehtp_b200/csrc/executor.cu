@@ -623,6 +623,37 @@ int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes) {
     return cudaMemcpy(dst, g.st_buf[idx], bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
 }
 
+// Capture whatever the caller queues on the engine stream between begin and
+// end into a CUDA graph, replay it `reps` times and report the mean device time
+// of one replay (CUDA events on the engine stream). For timing short kernels
+// without per-launch host overhead.
+int gehtp_cuda_capture_begin(void) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    return cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess ? 0 : -1;
+}
+int gehtp_cuda_capture_end_replay(int reps, float* ms_per_replay) {
+    if (!g.dev_ok) return -1;
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamEndCapture(g.stream, &graph) != cudaSuccess || !graph) { cudaGetLastError(); return -1; }
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { cudaGetLastError(); return -1; }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaGraphLaunch(exec, g.stream);                 // warm
+    cudaEventRecord(e0, g.stream);
+    for (int i = 0; i < reps; i++) cudaGraphLaunch(exec, g.stream);
+    cudaEventRecord(e1, g.stream);
+    e = cudaStreamSynchronize(g.stream);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    if (ms_per_replay) *ms_per_replay = reps > 0 ? ms / reps : 0.0f;
+    return e == cudaSuccess ? 0 : -1;
+}
+
 size_t gehtp_w4a16_slot_bytes(uint32_t K, uint32_t N) { return (size_t)K * N / 2 + (size_t)2 * (K / GEHTP_W4_GROUP) * N; }
 
 }  // extern "C"

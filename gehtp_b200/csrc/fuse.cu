@@ -339,7 +339,7 @@ void fuse_materialize(const wt_blob* b) {
     size_t scratch_floats = 0;
     for (const Span& sp : g_spans)
         if (sp.kind == 0) {
-            uint32_t ns = attn_decode_pick_splits(sp.B * sp.kvh, sp.nslots);
+            uint32_t ns = attn_decode_nsplit(sp.B * sp.kvh, sp.nslots, sp.nh / sp.kvh, sp.hd, 0);
             size_t f = attn_decode_scratch_floats(sp.B * sp.kvh, sp.nh / sp.kvh, sp.hd, ns);
             if (f > scratch_floats) scratch_floats = f;
         }
@@ -366,7 +366,7 @@ void fuse_materialize(const wt_blob* b) {
             a.q = q_out; a.ring = ring; a.counter = ctr; a.n_kv = 0; a.n_kv_add = 1; a.bump_counter = ctr;
             a.mask = mask; a.mask_seq_stride = nh * nslots; a.kvh_per_seq = kvh;
             a.scale = sp.scale; a.scale_div = sp.scale_div; a.rep = nh / kvh; a.kv_heads = B * kvh; a.nslots = nslots;
-            a.nsplit = attn_decode_pick_splits(B * kvh, nslots);
+            a.nsplit = attn_decode_nsplit(B * kvh, nslots, nh / kvh, hd, 0);
             a.part_o = g_attn_scratch;
             a.part_ml = g_attn_scratch + (size_t)B * kvh * a.nsplit * a.rep * hd;
             head.fused = [=](cudaStream_t st) {

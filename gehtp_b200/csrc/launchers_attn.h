@@ -19,12 +19,12 @@ struct AttnDecodeArgs {
     uint32_t rep;              // query heads per KV head (<= 16)
     uint32_t kv_heads;         // KV heads per ring slot (= kv_heads_total)
     uint32_t nslots;
-    uint32_t nsplit;           // context slices = gridDim.y
+    uint32_t nsplit;           // context slices per KV head (= slots per head in the scratch buffers)
     float* part_o;             // scratch [kv_heads_total][nsplit][rep][hd]
     float* part_ml;            // scratch [kv_heads_total][nsplit][rep][2]
 };
 
-uint32_t attn_decode_pick_splits(uint32_t kv_heads_total, uint32_t max_positions);
+uint32_t attn_decode_nsplit(uint32_t kv_heads_total, uint32_t max_positions, uint32_t rep, uint32_t hd, size_t max_floats);
 size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_t hd, uint32_t nsplit);
 // false: shape not handled (rep > 16 or head_dim not 64/128); nothing launched
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out,

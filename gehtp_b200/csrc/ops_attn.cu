@@ -21,17 +21,44 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* _
     extern __shared__ float row[];  // width floats
     __shared__ double part[BLOCK / 32];
     __shared__ float s_rms;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t base = (size_t)blockIdx.x * width;
     double acc = 0.0;
-    for (uint32_t i = threadIdx.x; i < width; i += BLOCK) {
-        float v = h2f(a[base + i]);
-        if (r) {
-            uint16_t s = f2h(__fadd_rn(v, h2f(r[base + i])));
-            if (sum_out) sum_out[base + i] = s;
-            v = h2f(s);
+    if ((width & 7u) == 0 && ((((uintptr_t)a) | ((uintptr_t)r) | ((uintptr_t)sum_out)) & 15u) == 0) {
+        // 8 values per 16-byte load
+        for (uint32_t i = threadIdx.x * 8; i < width; i += BLOCK * 8) {
+            uint4 qa = *(const uint4*)(a + base + i), qr = make_uint4(0, 0, 0, 0), qs;
+            if (r) qr = *(const uint4*)(r + base + i);
+            const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wr[4] = {qr.x, qr.y, qr.z, qr.w};
+            uint32_t ws[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                float v0 = h2f((uint16_t)(wa[k] & 0xffffu)), v1 = h2f((uint16_t)(wa[k] >> 16));
+                if (r) {
+                    uint16_t s0 = f2h(__fadd_rn(v0, h2f((uint16_t)(wr[k] & 0xffffu))));
+                    uint16_t s1 = f2h(__fadd_rn(v1, h2f((uint16_t)(wr[k] >> 16))));
+                    ws[k] = (uint32_t)s0 | ((uint32_t)s1 << 16);
+                    v0 = h2f(s0); v1 = h2f(s1);
+                }
+                row[i + 2 * k] = v0;
+                row[i + 2 * k + 1] = v1;
+                acc += (double)v0 * (double)v0;
+                acc += (double)v1 * (double)v1;
+            }
+            if (r && sum_out) { qs = make_uint4(ws[0], ws[1], ws[2], ws[3]); *(uint4*)(sum_out + base + i) = qs; }
         }
-        row[i] = v;
-        acc += (double)v * (double)v;
+    } else {
+        for (uint32_t i = threadIdx.x; i < width; i += BLOCK) {
+            float v = h2f(a[base + i]);
+            if (r) {
+                uint16_t s = f2h(__fadd_rn(v, h2f(r[base + i])));
+                if (sum_out) sum_out[base + i] = s;
+                v = h2f(s);
+            }
+            row[i] = v;
+            acc += (double)v * (double)v;
+        }
     }
     acc = warp_sum_d(acc);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
@@ -54,9 +81,9 @@ void k_add_rmsnorm(cudaStream_t st, const uint16_t* a, const uint16_t* r, const 
                    const uint16_t* b, uint16_t* sum_out, uint16_t* y, uint32_t rows, uint32_t width) {
     if (!rows || !width) return;
     if (width <= 512)
-        rmsnorm_kernel<64><<<rows, 64, width * sizeof(float), st>>>(a, r, g, b, sum_out, y, width);
+        launch_pdl(rmsnorm_kernel<64>, dim3(rows), dim3(64), width * sizeof(float), st, a, r, g, b, sum_out, y, width);
     else
-        rmsnorm_kernel<256><<<rows, 256, width * sizeof(float), st>>>(a, r, g, b, sum_out, y, width);
+        launch_pdl(rmsnorm_kernel<256>, dim3(rows), dim3(256), width * sizeof(float), st, a, r, g, b, sum_out, y, width);
     g_launches++;
 }
 

@@ -34,7 +34,6 @@ namespace {
 constexpr int TILE = 64;      // positions per stage
 constexpr int STAGES = 3;
 constexpr int NWARP = 4;      // 16 positions of a tile each
-constexpr int CHUNK_POS = 256;   // positions per work item (4 tiles)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -86,19 +85,25 @@ attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t rep = A.rep;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t n_kv = A.counter ? *A.counter + A.n_kv_add : A.n_kv;
+    uint32_t CHUNK_POS = (n_kv + A.nsplit - 1) / A.nsplit;           // even split of the context over nsplit slices
+    CHUNK_POS = (CHUNK_POS + TILE - 1) / TILE * TILE;
     const uint32_t n_chunks = (n_kv + CHUNK_POS - 1) / CHUNK_POS;   // <= A.nsplit by construction
     const uint32_t n_items = kv_heads_total * n_chunks;
     const uint32_t kv_elems = A.kv_heads * HD;
     float* sm_o = (float*)(smem + STAGES * STAGE_B);     // [NWARP][rep][HD]
     float* sm_ml = sm_o + NWARP * rep * HD;               // [NWARP][rep][2]
 
-    // A work item = (KV head, chunk of CHUNK_POS positions); this CTA takes items
-    // blockIdx.x, blockIdx.x + gridDim.x, ... and streams their tiles back to back,
-    // so the copy pipeline never drains between items.
+    // A work item = (KV head, chunk of CHUNK_POS positions), heads fastest: CTAs that
+    // run side by side read neighbouring heads of the same positions, i.e. one
+    // contiguous stretch of the ring, which keeps DRAM pages open. This CTA takes
+    // items blockIdx.x, blockIdx.x + gridDim.x, ... and streams their tiles back to
+    // back, so the copy pipeline never drains between items.
     struct Cursor { uint32_t item, tile; };
     auto tiles_of = [&](uint32_t item) -> uint32_t {
-        uint32_t pb = (item % n_chunks) * CHUNK_POS;
+        uint32_t pb = (item / kv_heads_total) * CHUNK_POS;
         uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
         return (pe - pb + TILE - 1) / TILE;
     };
@@ -107,8 +112,8 @@ attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     };
     auto issue = [&](const Cursor& c, uint32_t stage) {
         if (c.item < n_items) {
-            const uint32_t kvh = c.item / n_chunks;
-            const uint32_t pb = (c.item % n_chunks) * CHUNK_POS;
+            const uint32_t kvh = c.item % kv_heads_total;
+            const uint32_t pb = (c.item / kv_heads_total) * CHUNK_POS;
             const uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
             const uint32_t p0 = pb + c.tile * TILE;
             unsigned char* sk = smem + (size_t)stage * STAGE_B;
@@ -139,7 +144,7 @@ attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     float o[DBLK][4];
     float m_run[2], l_run[2];
     while (cc.item < n_items) {
-        const uint32_t kvh = cc.item / n_chunks, chunk = cc.item % n_chunks;
+        const uint32_t kvh = cc.item % kv_heads_total, chunk = cc.item / kv_heads_total;
         const uint32_t pb = chunk * CHUNK_POS;
         const uint32_t pe = pb + CHUNK_POS < n_kv ? pb + CHUNK_POS : n_kv;
         if (cc.tile == 0) {
@@ -283,27 +288,245 @@ attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     cp_async_wait<0>();
 }
 
-// out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}, chunks in order.
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit,
-                                         const uint32_t* counter, uint32_t n_kv_add, uint32_t n_kv_const,
-                                         uint32_t* bump_counter) {
+// Grouped form: one CTA = NW neighbouring KV heads (one per warp) x one chunk of
+// positions. A ring row of NW heads is NW*HD*2 contiguous bytes, so the CTA's
+// copies are 1 KB (NW = 4) stretches instead of 256-byte ones, and each warp
+// owns a whole (head, chunk) result: no cross-warp merge, the partial goes from
+// registers to the scratch buffer.
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32)
+attn_decode_group_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
+    constexpr int ROWB = HD * 2;
+    constexpr int CHUNKS = ROWB / 16;
+    constexpr int KSTEPS = HD / 16;
+    constexpr int DBLK = HD / 8;
+    constexpr int TP = 16;                               // positions per tile
+    constexpr int HEAD_B = TP * ROWB;                    // one head's K (or V) rows of a tile
+    constexpr int STAGE_B = 2 * NW * HEAD_B;
+    constexpr int GSTAGES = 3;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t rep = A.rep;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t n_kv = A.counter ? *A.counter + A.n_kv_add : A.n_kv;
+    const uint32_t n_groups = kv_heads_total / NW;
+    const uint32_t grp = blockIdx.x % n_groups, split = blockIdx.x / n_groups;   // groups fastest: neighbours share ring rows
+    uint32_t per = (n_kv + A.nsplit - 1) / A.nsplit;
+    per = (per + TP - 1) / TP * TP;
+    const uint32_t pb = split * per;
+    const uint32_t pe = pb + per < n_kv ? pb + per : n_kv;
+    const uint32_t kv_elems = A.kv_heads * HD;
+    const uint32_t kvh = grp * NW + warp;
+    const int ntiles = pe > pb ? (int)((pe - pb + TP - 1) / TP) : 0;
+
+    auto issue = [&](int tile) {
+        if (tile < ntiles) {
+            const uint32_t p0 = pb + tile * TP;
+            unsigned char* sk = smem + (size_t)(tile % GSTAGES) * STAGE_B;
+            unsigned char* sv = sk + NW * HEAD_B;
+            const uint16_t* base = A.ring + (size_t)grp * NW * HD;
+            for (int idx = tid; idx < TP * NW * CHUNKS; idx += NW * 32) {
+                int row = idx / (NW * CHUNKS), c2 = idx % (NW * CHUNKS);
+                int head = c2 / CHUNKS, ch = c2 % CHUNKS;
+                uint32_t p = p0 + row;
+                bool ok = p < pe;
+                const uint16_t* src = base + (size_t)(ok ? p : 0) * kv_elems * 2 + c2 * 8;
+                int so = head * HEAD_B + row * ROWB + ((ch ^ (row & 7)) << 4);
+                cp_async16(sk + so, src, ok);
+                cp_async16(sv + so, src + kv_elems, ok);
+            }
+        }
+        cp_async_commit();
+    };
+    for (int s2 = 0; s2 < GSTAGES - 1; s2++) issue(s2);
+
+    uint32_t qa[KSTEPS][4];
+    float o[DBLK][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    {
+        const uint16_t* q0 = A.q + ((size_t)kvh * rep + g) * HD;
+        const uint16_t* q1 = A.q + ((size_t)kvh * rep + g + 8) * HD;
+#pragma unroll
+        for (int j = 0; j < KSTEPS; j++) {
+            qa[j][0] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t) : 0u;
+            qa[j][1] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t) : 0u;
+            qa[j][2] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t + 8) : 0u;
+            qa[j][3] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t + 8) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < DBLK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    }
+    const uint16_t* maskp = A.mask ? A.mask + (size_t)(kvh / A.kvh_per_seq) * A.mask_seq_stride : nullptr;
+    for (int tile = 0; tile < ntiles; tile++) {
+        issue(tile + GSTAGES - 1);
+        cp_async_wait<GSTAGES - 1>();
+        __syncthreads();
+        const unsigned char* sk = smem + (size_t)(tile % GSTAGES) * STAGE_B + warp * HEAD_B;
+        const unsigned char* sv = sk + NW * HEAD_B;
+        const uint32_t pw0 = pb + tile * TP;
+        {
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int j = 0; j < KSTEPS; j++) {
+                uint32_t kb[4];
+                int mat = lane >> 3, r = lane & 7;
+                int row = (mat >> 1) * 8 + r;
+                int ch = j * 2 + (mat & 1);
+                ldsm_x4(kb, sk + row * ROWB + ((ch ^ (row & 7)) << 4));
+                mma_f16(s[0], qa[j], kb[0], kb[1]);
+                mma_f16(s[1], qa[j], kb[2], kb[3]);
+            }
+            float x[2][4];
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t p = pw0 + nb * 8 + 2 * t + (c & 1);
+                    float v = -INFINITY;
+                    if (p < pe) {
+                        float mk = maskp ? __half2float(__ushort_as_half(maskp[p])) : 0.0f;
+                        v = chain_score(s[nb][c], A.scale, A.scale_div, mk);
+                    }
+                    x[nb][c] = v;
+                    mx[c >> 1] = fmaxf(mx[c >> 1], v);
+                }
+            float alpha[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                float m_new = fmaxf(m_run[h], mx[h]);
+                alpha[h] = (m_new == -INFINITY) ? 1.0f : __expf(m_run[h] - m_new);
+                m_run[h] = m_new;
+                l_run[h] *= alpha[h];
+            }
+            uint32_t pa[4];
+            {
+                float pv[2][4];
+#pragma unroll
+                for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        float mr = m_run[c >> 1];
+                        float e = (mr == -INFINITY) ? 0.0f : __expf(x[nb][c] - mr);
+                        pv[nb][c] = e;
+                        l_run[c >> 1] += e;
+                    }
+                pa[0] = pack_h2(pv[0][0], pv[0][1]);
+                pa[1] = pack_h2(pv[0][2], pv[0][3]);
+                pa[2] = pack_h2(pv[1][0], pv[1][1]);
+                pa[3] = pack_h2(pv[1][2], pv[1][3]);
+            }
+            if (alpha[0] != 1.0f || alpha[1] != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < DBLK; i++) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                    o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
+            }
+#pragma unroll
+            for (int dp = 0; dp < DBLK / 2; dp++) {
+                uint32_t vb[4];
+                int mat = lane >> 3, r = lane & 7;
+                int row = (mat & 1) * 8 + r;
+                int ch = dp * 2 + (mat >> 1);
+                ldsm_x4_t(vb, sv + row * ROWB + ((ch ^ (row & 7)) << 4));
+                mma_f16(o[dp * 2], pa, vb[0], vb[1]);
+                mma_f16(o[dp * 2 + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();   // every warp is done with this stage
+    }
+    cp_async_wait<0>();
+    // this warp's (head, split) partial, straight from registers (empty slices leave max = -inf, sum = 0)
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* po = A.part_o + ((size_t)kvh * A.nsplit + split) * rep * HD;
+    float* pml = A.part_ml + ((size_t)kvh * A.nsplit + split) * rep * 2;
+#pragma unroll
+    for (int i = 0; i < DBLK; i++) {
+        int d = i * 8 + 2 * t;
+        if ((uint32_t)g < rep) *(float2*)(po + (size_t)g * HD + d) = make_float2(o[i][0], o[i][1]);
+        if ((uint32_t)(g + 8) < rep) *(float2*)(po + (size_t)(g + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+    }
+    if (t == 0) {
+        if ((uint32_t)g < rep) { pml[g * 2] = m_run[0]; pml[g * 2 + 1] = l_run[0]; }
+        if ((uint32_t)(g + 8) < rep) { pml[(g + 8) * 2] = m_run[1]; pml[(g + 8) * 2 + 1] = l_run[1]; }
+    }
+}
+
+// out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}.
+// One CTA of 4 warps per query head: warp w takes chunks w, w+4, ... (all its
+// loads are independent, so they overlap), lanes split head_dim; the four warp
+// sums are added in warp order.
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit,
+                         const uint32_t* counter, uint32_t n_kv_add, uint32_t n_kv_const,
+                         uint32_t* bump_counter, uint32_t round_to) {
+    __shared__ float s_acc[4][256];
+    __shared__ float s_l[4];
+    __shared__ float s_m[4];
     const uint32_t h = blockIdx.x;           // query head, = kvh * rep + r
     const uint32_t kvh = h / rep, r = h % rep;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t n_kv = counter ? *counter + n_kv_add : n_kv_const;
-    const uint32_t n_chunks = (n_kv + CHUNK_POS - 1) / CHUNK_POS;
+    uint32_t per = (n_kv + nsplit - 1) / nsplit;
+    per = (per + round_to - 1) / round_to * round_to;
+    const uint32_t n_chunks = (n_kv + per - 1) / per;          // slices that hold positions
+    const size_t row0 = ((size_t)kvh * nsplit) * rep + r;     // chunk s is at row0 + s*rep
+    // global maximum over the chunks
     float mt = -INFINITY;
-    for (uint32_t s = 0; s < n_chunks; s++) mt = fmaxf(mt, part_ml[(((size_t)kvh * nsplit + s) * rep + r) * 2]);
-    for (uint32_t d = threadIdx.x; d < hd; d += blockDim.x) {
-        float acc = 0.0f, lt = 0.0f;
-        for (uint32_t s = 0; s < n_chunks; s++) {
-            size_t base = ((size_t)kvh * nsplit + s) * rep + r;
-            float ms = part_ml[base * 2];
-            float w = (ms == -INFINITY) ? 0.0f : __expf(ms - mt);
-            acc += part_o[base * hd + d] * w;
-            lt += part_ml[base * 2 + 1] * w;
+    for (uint32_t s = threadIdx.x; s < n_chunks; s += 128) mt = fmaxf(mt, part_ml[(row0 + (size_t)s * rep) * 2]);
+    mt = warp_max(mt);
+    if (lane == 0) s_m[warp] = mt;
+    __syncthreads();
+    mt = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    const uint32_t per_lane = hd / 32;       // 4 for head_dim 128, 2 for 64
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float lt = 0.0f;
+    // batches of 8 slices: all loads of a batch are issued before any is used
+    for (uint32_t s0 = warp; s0 < n_chunks; s0 += 32) {
+        float ms[8], ls[8], ov[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const uint32_t s = s0 + 4 * u;
+            const bool ok = s < n_chunks;
+            const size_t base = row0 + (size_t)(ok ? s : s0) * rep;
+            ms[u] = ok ? part_ml[base * 2] : -INFINITY;
+            ls[u] = ok ? part_ml[base * 2 + 1] : 0.0f;
+            const float* po = part_o + base * hd + lane * per_lane;
+            if (per_lane == 4) {
+                float4 v = *(const float4*)po;
+                ov[u][0] = v.x; ov[u][1] = v.y; ov[u][2] = v.z; ov[u][3] = v.w;
+            } else {
+                float2 v = *(const float2*)po;
+                ov[u][0] = v.x; ov[u][1] = v.y; ov[u][2] = 0.0f; ov[u][3] = 0.0f;
+            }
         }
-        out[(size_t)h * hd + d] = f2h(lt > 0.0f ? acc / lt : 0.0f);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const float w = (ms[u] == -INFINITY) ? 0.0f : __expf(ms[u] - mt);
+            lt += ls[u] * w;
+#pragma unroll
+            for (int k = 0; k < 4; k++) acc[k] += ov[u][k] * w;
+        }
+    }
+    for (uint32_t k = 0; k < per_lane; k++) s_acc[warp][lane * per_lane + k] = acc[k];
+    if (lane == 0) s_l[warp] = lt;
+    __syncthreads();
+    const float ltot = s_l[0] + s_l[1] + s_l[2] + s_l[3];
+    for (uint32_t d = threadIdx.x; d < hd; d += 128) {
+        float a = s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d];
+        out[(size_t)h * hd + d] = f2h(ltot > 0.0f ? a / ltot : 0.0f);
     }
     // all readers of the counter in this launch must be done before it moves: the
     // last block to finish advances it
@@ -319,10 +542,22 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
 
 }  // namespace
 
-uint32_t attn_decode_pick_splits(uint32_t kv_heads_total, uint32_t max_positions) {
-    (void)kv_heads_total;
-    uint32_t n = (max_positions + CHUNK_POS - 1) / CHUNK_POS;
-    return n ? n : 1;
+// Context slices per KV head: as many as give every one of the 2 x 148 CTAs one
+// evenly sized work item (a group of 4 neighbouring heads x a slice when the
+// head count is a multiple of 4, else one head x a slice), at least 64
+// positions per slice, and, when max_floats != 0, few enough for the scratch
+// buffers to fit in that many floats. 0 = does not fit even unsliced.
+uint32_t attn_decode_nsplit(uint32_t kv_heads_total, uint32_t max_positions, uint32_t rep, uint32_t hd, size_t max_floats) {
+    const uint32_t group = (kv_heads_total % 4 == 0 && hd == 128) ? 4 : 1;
+    const uint32_t n_groups = kv_heads_total / group;
+    uint32_t ns = (2 * 148) / n_groups;
+    if (ns < 1) ns = 1;
+    uint32_t most = (max_positions + 63) / 64;
+    if (ns > most) ns = most;
+    if (ns < 1) ns = 1;
+    while (max_floats && ns > 1 && attn_decode_scratch_floats(kv_heads_total, rep, hd, ns) > max_floats) ns--;
+    if (max_floats && attn_decode_scratch_floats(kv_heads_total, rep, hd, ns) > max_floats) return 0;
+    return ns;
 }
 
 size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_t hd, uint32_t nsplit) {
@@ -331,20 +566,32 @@ size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_
 
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out, uint32_t kv_heads_total) {
     if (a.rep == 0 || a.rep > 16 || (hd != 128 && hd != 64)) return false;
+    if (!a.nsplit) return false;
+    if (hd == 128 && kv_heads_total % 4 == 0) {
+        size_t gsmem = (size_t)3 * 2 * 4 * 16 * hd * 2;
+        uint32_t ggrid = (kv_heads_total / 4) * a.nsplit;
+        static bool gattr = false;
+        if (!gattr) { cudaFuncSetAttribute(attn_decode_group_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsmem); gattr = true; }
+        launch_pdl(attn_decode_group_kernel<128, 4>, dim3(ggrid), dim3(128), gsmem, st, a, kv_heads_total);
+        launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
+                   (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, 16u);
+        g_launches += 2;
+        return true;
+    }
     size_t smem = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)NWARP * a.rep * (hd + 2) * sizeof(float);
     uint32_t items = kv_heads_total * a.nsplit;
     uint32_t grid = items < 2 * 148 ? items : 2 * 148;
     if (hd == 128) {
         static size_t attr = 0;
         if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
-        attn_decode_split_kernel<128><<<grid, NWARP * 32, smem, st>>>(a, kv_heads_total);
+        launch_pdl(attn_decode_split_kernel<128>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total);
     } else {
         static size_t attr = 0;
         if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
-        attn_decode_split_kernel<64><<<grid, NWARP * 32, smem, st>>>(a, kv_heads_total);
+        launch_pdl(attn_decode_split_kernel<64>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total);
     }
-    attn_decode_merge_kernel<<<kv_heads_total * a.rep, hd < 128 ? 64 : 128, 0, st>>>(
-        a.part_o, a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter);
+    launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
+               (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, (uint32_t)TILE);
     g_launches += 2;
     return true;
 }
@@ -382,9 +629,9 @@ extern "C" int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* 
     if (!n_heads || !kv_heads || n_heads % kv_heads || !nslots || !n_kv || n_kv > nslots) return fail("attn noalloc: bad shape");
     const uint32_t rep = n_heads / kv_heads;
     if (rep > 16 || (head_dim != 128 && head_dim != 64)) return fail("attn noalloc: head layout not handled by the fused kernel");
-    const uint32_t nsplit = attn_decode_pick_splits(kv_heads, n_kv);
-    const size_t need = attn_decode_scratch_floats(kv_heads, rep, head_dim, nsplit);
-    if (need > kNoAllocFloats) {
+    const uint32_t nsplit = attn_decode_nsplit(kv_heads, n_kv, rep, head_dim, kNoAllocFloats);
+    const size_t need = attn_decode_scratch_floats(kv_heads, rep, head_dim, nsplit ? nsplit : 1);
+    if (!nsplit) {
         char m[160];
         std::snprintf(m, sizeof m, "attn noalloc: needs %zu bytes of scratch, the built-in array holds %zu", need * sizeof(float),
                       (size_t)GEHTP_NOALLOC_SCRATCH_BYTES);

@@ -402,36 +402,74 @@ void k_scatter_nd(cudaStream_t st, const int32_t* idx, const uint16_t* upd, uint
 }
 
 // Argmax, first maximum wins, start value -1e30 (oplist_exec.c:1990-2004).
-__global__ void argmax_kernel(const uint16_t* __restrict__ x, int32_t* __restrict__ y, uint32_t n) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
+// Up to 128 CTAs scan contiguous ranges with 16-byte loads; the last CTA to
+// finish merges the per-CTA winners (lower index wins ties), so one launch
+// covers a vocabulary-sized row in a few microseconds.
+__device__ float g_argmax_val[128];
+__device__ int g_argmax_idx[128];
+__device__ unsigned int g_argmax_done = 0;
+
+__device__ __forceinline__ void argmax_take(float v, int i, float& bv, int& bi) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const uint16_t* __restrict__ x, int32_t* __restrict__ y, uint32_t n) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ bool s_last;
+    const uint32_t per = ((n + gridDim.x - 1) / gridDim.x + 7u) & ~7u;
+    const uint32_t lo = blockIdx.x * per, hi = (lo + per < n) ? lo + per : n;
     float bv = -1e30f;
     int bi = 0x7fffffff;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = h2f(x[i]);
-        if (v > bv) { bv = v; bi = (int)i; }
+    if (lo < hi) {
+        if ((((uintptr_t)x) & 15u) == 0) {
+            for (uint32_t i = lo + threadIdx.x * 8; i < hi; i += blockDim.x * 8) {
+                if (i + 8 <= hi) {
+                    uint4 q = *(const uint4*)(x + i);
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        float a = h2f((uint16_t)(w[k] & 0xffffu)), b = h2f((uint16_t)(w[k] >> 16));
+                        if (a > bv) { bv = a; bi = (int)(i + 2 * k); }
+                        if (b > bv) { bv = b; bi = (int)(i + 2 * k + 1); }
+                    }
+                } else {
+                    for (uint32_t k = i; k < hi; k++) { float a = h2f(x[k]); if (a > bv) { bv = a; bi = (int)k; } }
+                }
+            }
+        } else {
+            for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) { float a = h2f(x[i]); if (a > bv) { bv = a; bi = (int)i; } }
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        argmax_take(ov, oi, bv, bi);
     }
     if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
-    if (threadIdx.x < 32) {
-        int nw = blockDim.x >> 5;
-        bv = threadIdx.x < nw ? sv[threadIdx.x] : -1e30f;
-        bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (threadIdx.x == 0) y[0] = (bi == 0x7fffffff) ? 0 : bi;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) argmax_take(sv[w], si[w], bv, bi);
+        g_argmax_val[blockIdx.x] = bv;
+        g_argmax_idx[blockIdx.x] = bi;
+        __threadfence();
+        s_last = atomicAdd(&g_argmax_done, 1u) + 1 == gridDim.x;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence();
+        float fv = -1e30f;
+        int fi = 0x7fffffff;
+        for (uint32_t b = 0; b < gridDim.x; b++) argmax_take(g_argmax_val[b], g_argmax_idx[b], fv, fi);
+        y[0] = (fi == 0x7fffffff) ? 0 : fi;
+        g_argmax_done = 0;
     }
 }
 void k_argmax(cudaStream_t st, const uint16_t* x, int32_t* y, uint32_t n) {
-    argmax_kernel<<<1, 1024, 0, st>>>(x, y, n);
+    unsigned grid = (n + 4095) / 4096;
+    if (grid < 1) grid = 1;
+    if (grid > 128) grid = 128;
+    argmax_kernel<<<grid, 256, 0, st>>>(x, y, n);
     g_launches++;
 }
 

@@ -18,6 +18,8 @@ __global__ void rope_kv_append_kernel(const uint16_t* __restrict__ qkv, const ui
                                       uint16_t* __restrict__ ring, uint32_t* __restrict__ posmap,
                                       const uint32_t* __restrict__ counter, uint32_t B, uint32_t nh,
                                       uint32_t kvh, uint32_t hd, uint32_t nslots, uint32_t pos_const) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t pos = (pos_const == 0xFFFFFFFAu) ? *counter : pos_const;
     const uint32_t slot = pos % nslots;
     const uint32_t row_w = (nh + 2 * kvh) * hd, h = hd / 2;
@@ -60,8 +62,8 @@ void k_rope_kv_append(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_
     uint32_t total = B * (nh + 2 * kvh) * hd;
     uint32_t grid = (total + 255) / 256;
     if (grid > 148 * 8) grid = 148 * 8;
-    rope_kv_append_kernel<<<grid, 256, 0, st>>>(qkv, cos_q, sin_q, cos_k, sin_k, q_out, ring, posmap, counter,
-                                               B, nh, kvh, hd, nslots, pos_const);
+    launch_pdl(rope_kv_append_kernel, dim3(grid), dim3(256), 0, st, qkv, cos_q, sin_q, cos_k, sin_k, q_out, ring, posmap, counter,
+               B, nh, kvh, hd, nslots, pos_const);
     g_launches++;
 }
 

@@ -141,13 +141,18 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
 }
 
 template <int MT, int UNROLL, bool DUAL>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
                     const uint16_t* __restrict__ sc2, uint16_t* __restrict__ y, uint32_t M,
                     uint32_t K, uint32_t N, uint32_t kgw, W4Epilogue ep) {
     extern __shared__ float red[];  // [nwarps][NACC][32]
     constexpr int NACC = MT * 4 * (DUAL ? 2 : 1);
+    // Programmatic dependent launch: let the next kernel start early, and order
+    // this one after its predecessor only once the first batch of weight loads
+    // (constants, independent of the predecessor) is in flight.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    bool waited = false;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t nb = blockIdx.x, NB = N / 16, KG = K / 64;
@@ -184,6 +189,7 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
                 if (DUAL) { wq2[u] = wq[u]; t0[u] = 0; t1[u] = 0; }
             }
         }
+        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             if (kg + u >= kg1) break;
@@ -227,6 +233,7 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
         }
     }
 
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < MT; i++)
 #pragma unroll
@@ -254,7 +261,7 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
 
 static uint32_t skinny_kgw(uint32_t KG) {
     uint32_t kgw = 8;
-    while ((KG + kgw - 1) / kgw > 16) kgw += 8;
+    while ((KG + kgw - 1) / kgw > 20) kgw += 8;
     return kgw;
 }
 
@@ -265,11 +272,11 @@ void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, 
     if (M <= 8) {
         dim3 grid(N / 16, 1);
         size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
-        w4a16_skinny_kernel<1, 8, false><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, nullptr, nullptr, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<1, 8, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
     } else {
         dim3 grid(N / 16, (M + 15) / 16);
         size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        w4a16_skinny_kernel<2, 4, false><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)packed, sc, nullptr, nullptr, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<2, 4, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
     }
     g_launches++;
 }
@@ -284,11 +291,11 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
     if (M <= 8) {
         dim3 grid(N / 16, 1);
         size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        w4a16_skinny_kernel<1, 4, true><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<1, 4, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
     } else {
         dim3 grid(N / 16, (M + 15) / 16);
         size_t smem = (size_t)nwarps * 16 * 32 * sizeof(float);
-        w4a16_skinny_kernel<2, 2, true><<<grid, nwarps * 32, smem, st>>>(a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<2, 2, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
     }
     g_launches++;
 }

@@ -210,6 +210,30 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
                       uint16_t* out, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
                       uint32_t n_kv, uint32_t nslots, float scale);
 
+/* Device-pointer forms of the kernels above: every buffer is device memory of
+ * the caller, work is queued on the engine stream (gehtp_cuda_stream) and not
+ * waited for. `packed_dev` is the strip-major layout made by gehtp_dev_w4_repack
+ * from the nibble part of a weight slot (K*N/2 bytes in, K*N/2 bytes out);
+ * `scales_dev` is the fp16 [K/64][N] part of the slot. gehtp_dev_w4a16_swiglu
+ * computes silu-gated gate/up projections in one pass (M <= 16);
+ * gehtp_dev_rmsnorm normalises f16(x + res) when res_dev is given (and stores
+ * that sum to sum_dev when not NULL). */
+int gehtp_dev_w4_repack(const uint8_t* slot_dev, uint32_t* packed_dev, uint32_t K, uint32_t N);
+int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
+                           uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N, int path);
+int gehtp_dev_w4a16_swiglu(const uint16_t* a_dev, const uint32_t* pg, const uint16_t* sg,
+                           const uint32_t* pu, const uint16_t* su, uint16_t* y_dev,
+                           uint32_t M, uint32_t K, uint32_t N);
+int gehtp_dev_rmsnorm(const uint16_t* x_dev, const uint16_t* res_dev, const uint16_t* gamma_dev,
+                      const uint16_t* beta_dev, uint16_t* sum_dev, uint16_t* y_dev,
+                      uint32_t rows, uint32_t width);
+
+/* Timing aid: everything queued on the engine stream between begin and end is
+ * captured into one CUDA graph, replayed `reps` times, and the mean device time
+ * of a replay is returned in milliseconds. */
+int gehtp_cuda_capture_begin(void);
+int gehtp_cuda_capture_end_replay(int reps, float* ms_per_replay);
+
 /* No counterpart in the reference. The same decode attention as
  * gehtp_attn_decode, for callers that are not allowed to allocate device memory
  * (a serving loop living inside a pre-carved memory pool, a latency-critical
@@ -221,8 +245,9 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
  * held until the process exits. The call allocates and frees nothing, only
  * queues work on `stream` (a cudaStream_t, NULL = default stream) of the current
  * device, and does not wait for it.
- * Limit: kv_heads * ceil(n_kv/256) * (n_heads/kv_heads) * (head_dim+2) * 4 bytes
- * must fit in the array; larger problems return -1 with a message in
+ * Limit: the context is cut into as many slices as keep every SM busy, fewer
+ * when the partial results (n_heads * slices * (head_dim+2) * 4 bytes) would not
+ * fit; unsliced, n_heads * (head_dim+2) * 4 bytes must fit in the array; larger problems return -1 with a message in
  * gehtp_cuda_last_error(). The first call on each device looks up the array's
  * device address; make that first call before starting any stream capture.
  * All calls share the one array and it keeps whatever the last call left in it:

@@ -50,8 +50,8 @@ def test_noalloc_matches_regular_entry_point_twice(cuda):
 
 def test_noalloc_refuses_what_does_not_fit(cuda):
     import torch
-    # 512 KV heads x 64 chunks x 4 x 130 floats = 68 MB of partials: far beyond the built-in array
-    nh, kvh, hd, n_kv = 2048, 512, 128, 16384
+    # 16384 query heads x 130 floats = 8.5 MB of partial results even unsliced: beyond the built-in array
+    nh, kvh, hd, n_kv = 16384, 4096, 128, 16384
     buf = torch.zeros(16, dtype=torch.int16, device="cuda")   # never touched: the call must fail before launching
     rc = cuda.gehtp_attn_decode_noalloc(buf.data_ptr(), buf.data_ptr(), None, buf.data_ptr(), nh, kvh, hd, n_kv, n_kv, 0.1, None)
     assert rc != 0
