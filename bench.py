@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default=None, choices=["gemv", "gemm", "attn", "norm", "all"],
+                    help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
 
@@ -269,6 +271,94 @@ def run_ours(args, rank, world):
                 setup_s=setup_s, fused_ops=fused_ops, blob_bytes=int(buf.size))
 
 
+def run_micro(which):
+    """Single-kernel timings through the device-pointer C entry points: operands
+    live in HBM, `copies` rotating weight sets larger than L2 defeat cache reuse,
+    launches are captured into one CUDA graph and replayed (no host overhead).
+    Returns a list of dicts."""
+    import torch
+    import gehtp_b200
+    lib = gehtp_b200.lib()
+    assert lib.gehtp_cuda_set_device(0) == 0
+    peak_hbm, _ = load_peaks()
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+    out = []
+
+    def timeit(fn, n=32, warm=3):
+        for i in range(warm):
+            fn(i)
+        lib.gehtp_cuda_sync()
+        torch.cuda.synchronize()
+        assert lib.gehtp_cuda_capture_begin() == 0
+        for i in range(n):
+            fn(i + warm)
+        ms = ctypes.c_float()
+        assert lib.gehtp_cuda_capture_end_replay(5, ctypes.byref(ms)) == 0, lib.gehtp_cuda_last_error()
+        return ms.value * 1e3 / n
+
+    def w4(M, K, N, path, dual=False, n=32):
+        nb = K * N // 2
+        copies = min(max(2, int(300e6 // nb) + 1), 64)
+        packed = torch.randint(0, 2 ** 31 - 1, (copies, nb // 4), dtype=torch.int32, device="cuda")
+        scales = (torch.rand(copies, K // 64, N, device="cuda") * 0.015 + 0.005).half()
+        a = torch.randn(M, K, device="cuda").half()
+        y = torch.zeros(M, N, dtype=torch.half, device="cuda")
+
+        def f(i):
+            c, c2 = i % copies, (i + 1) % copies
+            if dual:
+                rc = lib.gehtp_dev_w4a16_swiglu(a.data_ptr(), packed[c].data_ptr(), scales[c].data_ptr(), packed[c2].data_ptr(),
+                                                scales[c2].data_ptr(), y.data_ptr(), M, K, N)
+            else:
+                rc = lib.gehtp_dev_w4a16_matmul(a.data_ptr(), packed[c].data_ptr(), scales[c].data_ptr(), y.data_ptr(), M, K, N, path)
+            assert rc == 0, lib.gehtp_cuda_last_error()
+        us = timeit(f, n=n)
+        nbytes = (nb + 2 * (K // 64) * N) * (2 if dual else 1) + 2 * M * K + 2 * M * N
+        flops = 2.0 * M * K * N * (2 if dual else 1)
+        return us, nbytes, flops
+
+    if which in ("gemv", "all"):
+        for M in (1, 8):
+            for (K, N, dual) in ((1024, 3072, False), (2560, 6144, False), (4096, 2560, False), (2560, 9728, True),
+                                 (9728, 2560, False), (2560, 151936, False)):
+                us, nbytes, _ = w4(M, K, N, 1, dual)
+                out.append({"kernel": "w4a16_gemv" + ("_swiglu" if dual else ""), "M": M, "K": K, "N": N, "us": us,
+                            "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak_hbm})
+    if which in ("gemm", "all"):
+        for (M, K, N) in ((128, 1024, 3072), (512, 1024, 4096), (512, 1024, 3072), (512, 3072, 1024), (2048, 2560, 9728),
+                          (4096, 2560, 9728), (8192, 2560, 9728), (8192, 9728, 2560)):
+            us, _, flops = w4(M, K, N, 2, n=8)
+            out.append({"kernel": "w4a16_gemm_tcgen05", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
+                        "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
+    if which in ("attn", "all"):
+        for (nh, kvh, n_kv) in ((256, 64, 8192), (32, 8, 8192), (16, 8, 4096)):
+            hd = 128
+            ring = torch.randn(n_kv, 2, kvh * hd, device="cuda").half()
+            q = torch.randn(nh, hd, device="cuda").half()
+            o = torch.zeros_like(q)
+            mask = torch.zeros(n_kv, device="cuda").half()
+
+            def f(i):
+                rc = lib.gehtp_attn_decode_noalloc(q.data_ptr(), ring.data_ptr(), mask.data_ptr(), o.data_ptr(), nh, kvh, hd,
+                                                   n_kv, n_kv, 0.088, lib.gehtp_cuda_stream())
+                assert rc == 0, lib.gehtp_cuda_last_error()
+            us = timeit(f, n=8)
+            nbytes = ring.numel() * 2
+            out.append({"kernel": "attn_decode (split + merge)", "n_heads": nh, "kv_heads": kvh, "n_kv": n_kv, "us": us,
+                        "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak_hbm})
+    if which in ("norm", "all"):
+        for rows, width in ((1, 1024), (8, 2560), (64, 2560), (512, 1024)):
+            x = torch.randn(64, rows, width, device="cuda").half()
+            r = torch.randn_like(x)
+            gam = torch.ones(width, device="cuda").half()
+            y, sm = torch.zeros_like(x[0]), torch.zeros_like(x[0])
+            us = timeit(lambda i: lib.gehtp_dev_rmsnorm(x[i % 64].data_ptr(), r[i % 64].data_ptr(), gam.data_ptr(), None,
+                                                        sm.data_ptr(), y.data_ptr(), rows, width))
+            out.append({"kernel": "add_rmsnorm", "rows": rows, "width": width, "us": us, "GBps": 8.0 * rows * width / us / 1e3})
+    return out
+
+
 def reference_sample(args, reps):
     """Times the reference's own executor (compiled for the host, scalar code,
     one thread as the reference runs it) on a bounded sample of the workload:
@@ -350,6 +440,12 @@ def main():
               "batch": B, "kv_context": args.ctx, "layers": args.layers,
               "parallelism": "tp%d" % world if world > 1 else "single GPU",
               "l2": "inputs larger than L2: every step streams the weights and the KV rings (GBs) once"}
+
+    if args.micro:
+        if rank == 0:
+            for row in run_micro(args.micro):
+                print(json.dumps(row))
+        return
 
     if args.impl == "reference":
         if rank != 0:

@@ -140,7 +140,7 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
     return f2h(__fmul_rn(act, up));
 }
 
-template <int MT, int UNROLL, bool DUAL>
+template <int MT, int UNROLL, bool DUAL, bool FULL>
 __global__ void __launch_bounds__(640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
@@ -169,12 +169,18 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
 
     const uint4* wbase = wp + (size_t)nb * 32 + lane;
     const uint4* wbase2 = DUAL ? wp2 + (size_t)nb * 32 + lane : nullptr;
-    for (uint32_t kg = kg0; kg < kg1; kg += UNROLL) {
+    const uint4* arow[MT];   // this lane's activation row at the warp's first group, or NULL past M
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+        const uint32_t m = m0 + i * 8 + g;
+        arow[i] = m < M ? (const uint4*)(a + (size_t)m * K + (size_t)kg0 * 64 + t * 16) : nullptr;
+    }
+    for (uint32_t kg = kg0; kg < (FULL ? kg0 + 1 : kg1); kg += UNROLL) {
         uint4 wq[UNROLL], wq2[DUAL ? UNROLL : 1];
         uint16_t s0[UNROLL], s1[UNROLL], t0[DUAL ? UNROLL : 1], t1[DUAL ? UNROLL : 1];
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
-            if (kg + u < kg1) {
+            if (FULL || kg + u < kg1) {
                 wq[u] = __ldcs(wbase + (size_t)(kg + u) * NB * 32);  // streamed once: evict first
                 s0[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo);
                 s1[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo + 8);
@@ -192,7 +198,7 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
         if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
-            if (kg + u >= kg1) break;
+            if (!FULL && kg + u >= kg1) break;
             uint32_t af[4][4], af2[DUAL ? 4 : 1][4];
             {
                 const __half2 slo = __half2half2(__ushort_as_half(s0[u]));
@@ -212,10 +218,9 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
             }
 #pragma unroll
             for (int i = 0; i < MT; i++) {
-                const uint32_t m = m0 + i * 8 + g;
                 uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-                if (m < M) {
-                    const uint4* ap = (const uint4*)(a + (size_t)m * K + (size_t)(kg + u) * 64 + t * 16);
+                if (arow[i]) {
+                    const uint4* ap = arow[i] + (size_t)(kg - kg0 + u) * 8;   // 64 fp16 per group
                     b0 = __ldg(ap);
                     b1 = __ldg(ap + 1);
                 }
@@ -272,11 +277,12 @@ void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, 
     if (M <= 8) {
         dim3 grid(N / 16, 1);
         size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<1, 8, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
+        if (kgw == 8 && KG % 8 == 0) launch_pdl(w4a16_skinny_kernel<1, 8, false, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
+        else launch_pdl(w4a16_skinny_kernel<1, 8, false, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
     } else {
         dim3 grid(N / 16, (M + 15) / 16);
         size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<2, 4, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<2, 4, false, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
     }
     g_launches++;
 }
@@ -291,11 +297,11 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
     if (M <= 8) {
         dim3 grid(N / 16, 1);
         size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<1, 4, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<1, 4, true, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
     } else {
         dim3 grid(N / 16, (M + 15) / 16);
         size_t smem = (size_t)nwarps * 16 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<2, 2, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        launch_pdl(w4a16_skinny_kernel<2, 2, true, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
     }
     g_launches++;
 }
