@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemv", "gemm", "attn", "norm", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "attn", "norm", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -325,6 +325,11 @@ def run_micro(which):
                 us, nbytes, _ = w4(M, K, N, 1, dual)
                 out.append({"kernel": "w4a16_gemv" + ("_swiglu" if dual else ""), "M": M, "K": K, "N": N, "us": us,
                             "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak_hbm})
+    if which == "lmhead":   # the vocabulary projection alone: a small case for profiler captures
+        for M in (1, 8):
+            us, nbytes, _ = w4(M, 2560, 151936, 1, False, n=8)
+            out.append({"kernel": "w4a16_gemv", "M": M, "K": 2560, "N": 151936, "us": us, "GBps": nbytes / us / 1e3,
+                        "frac_of_measured_hbm": nbytes / us / 1e3 / peak_hbm})
     if which in ("gemm", "all"):
         for (M, K, N) in ((128, 1024, 3072), (512, 1024, 4096), (512, 1024, 3072), (512, 3072, 1024), (2048, 2560, 9728),
                           (4096, 2560, 9728), (8192, 2560, 9728), (8192, 9728, 2560)):

@@ -23,6 +23,7 @@
 // 16-byte loads issued up front, accumulates in fp32 through mma.sync, and the
 // warps' partial sums are added in warp order through shared memory, so the
 // result does not depend on scheduling.
+#include <cstdlib>
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "launchers_w4.h"
@@ -95,38 +96,75 @@ void k_w4_unpack_i8(cudaStream_t st, const uint32_t* packed, int8_t* out, uint32
 // ------------------------------------------------------------------ skinny matmul
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
                                          uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// One packed word -> four fp16 pairs (q - 8) * scale. `slo` / `shi` hold the
-// scale of column g / g+8 in both halves.
-__device__ __forceinline__ void dequant_word(uint32_t w, __half2 slo, __half2 shi,
-                                             uint32_t (&a)[4]) {
+// Activations are written by the preceding kernel of the stream, so they may
+// only be read after griddepcontrol.wait. A read-only (.nc) load could be moved
+// above the wait by the compiler; this one cannot.
+__device__ __forceinline__ uint4 ld_ordered(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// (a & b) | c in one LOP3 (truth table 0xEA).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// One packed word -> four fp16 pairs holding q - 8 (exact). The group scale is
+// applied to the fp32 partial sum of the 64-deep group after the MMAs: the
+// scale is constant along k inside a group and per output column, i.e. per
+// accumulator row, so 4 FFMAs per group replace 16 half2 multiplies.
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&a)[4]) {
     const uint32_t MAGIC = 0x64006400u;          // 1024.0 in both halves
     const __half2 c1032 = __half2half2(__ushort_as_half(0x6408));   // 1032
     const __half2 c16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
     const __half2 cm72 = __half2half2(__ushort_as_half(0xd480));    // -72
-    uint32_t w8 = w >> 8;
-    uint32_t p0 = (w & 0x000f000fu) | MAGIC;    // 1024 + q
-    uint32_t p1 = (w & 0x00f000f0u) | MAGIC;    // 1024 + 16 q
-    uint32_t p2 = (w8 & 0x000f000fu) | MAGIC;
-    uint32_t p3 = (w8 & 0x00f000f0u) | MAGIC;
+    const uint32_t w8 = w >> 8;
+    const uint32_t p0 = and_or(w, 0x000f000fu, MAGIC);    // 1024 + q
+    const uint32_t p1 = and_or(w, 0x00f000f0u, MAGIC);    // 1024 + 16 q
+    const uint32_t p2 = and_or(w8, 0x000f000fu, MAGIC);
+    const uint32_t p3 = and_or(w8, 0x00f000f0u, MAGIC);
     __half2 h0 = __hsub2(*(__half2*)&p0, c1032);
     __half2 h1 = __hfma2(*(__half2*)&p1, c16th, cm72);
     __half2 h2 = __hsub2(*(__half2*)&p2, c1032);
     __half2 h3 = __hfma2(*(__half2*)&p3, c16th, cm72);
-    h0 = __hmul2(h0, slo);
-    h1 = __hmul2(h1, shi);
-    h2 = __hmul2(h2, slo);
-    h3 = __hmul2(h3, shi);
     a[0] = *(uint32_t*)&h0;
     a[1] = *(uint32_t*)&h1;
     a[2] = *(uint32_t*)&h2;
     a[3] = *(uint32_t*)&h3;
+}
+
+// Same with C = 0 (starts a fresh partial sum).
+__device__ __forceinline__ void mma16816_first(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+__device__ __forceinline__ void mma_group(float (&acc)[4], const uint32_t (&af)[4][4], uint4 b0,
+                                          uint4 b1, float slo, float shi) {
+    float gacc[4];
+    mma16816_first(gacc, af[0], b0.x, b0.y);
+    mma16816(gacc, af[1], b0.z, b0.w);
+    mma16816(gacc, af[2], b1.x, b1.y);
+    mma16816(gacc, af[3], b1.z, b1.w);
+    acc[0] = fmaf(gacc[0], slo, acc[0]);     // rows g: columns 2t, 2t+1
+    acc[1] = fmaf(gacc[1], slo, acc[1]);
+    acc[2] = fmaf(gacc[2], shi, acc[2]);     // rows g+8
+    acc[3] = fmaf(gacc[3], shi, acc[3]);
 }
 
 // SwiGLU on two accumulators with the op chain's roundings: gate -> fp16,
@@ -140,7 +178,14 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
     return f2h(__fmul_rn(act, up));
 }
 
-template <int MT, int UNROLL, bool DUAL, bool FULL>
+// Walk modes of the streaming kernel.
+//   WALK_ONE  : every warp owns exactly UNROLL groups; one batch, all offsets
+//               are compile-time multiples of the strides (the decode shapes).
+//   WALK_FULL : every warp owns a whole number of batches; rolling refill.
+//   WALK_ANY  : ragged tail; per-group bounds tests.
+enum { WALK_ANY = 0, WALK_FULL = 1, WALK_ONE = 2 };
+
+template <int MT, int UNROLL, bool DUAL, int WALK>
 __global__ void __launch_bounds__(640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
@@ -148,18 +193,18 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
                     uint32_t K, uint32_t N, uint32_t kgw, W4Epilogue ep) {
     extern __shared__ float red[];  // [nwarps][NACC][32]
     constexpr int NACC = MT * 4 * (DUAL ? 2 : 1);
+    constexpr bool FULL = WALK != WALK_ANY, ONE = WALK == WALK_ONE;
     // Programmatic dependent launch: let the next kernel start early, and order
     // this one after its predecessor only once the first batch of weight loads
     // (constants, independent of the predecessor) is in flight.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    bool waited = false;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t nb = blockIdx.x, NB = N / 16, KG = K / 64;
     const uint32_t m0 = blockIdx.y * (8 * MT);
     const uint32_t n_lo = nb * 16 + g;
-    uint32_t kg0 = warp * kgw, kg1 = kg0 + kgw;
-    if (kg1 > KG) kg1 = KG;
+    const uint32_t kg0 = warp * (ONE ? (uint32_t)UNROLL : kgw);
+    const uint32_t kg1 = ONE ? kg0 + UNROLL : min(kg0 + kgw, KG);
 
     float acc[MT][4], acc2[DUAL ? MT : 1][4];
 #pragma unroll
@@ -167,78 +212,103 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
 #pragma unroll
         for (int c = 0; c < 4; c++) { acc[i][c] = 0.0f; if (DUAL) acc2[i][c] = 0.0f; }
 
-    const uint4* wbase = wp + (size_t)nb * 32 + lane;
-    const uint4* wbase2 = DUAL ? wp2 + (size_t)nb * 32 + lane : nullptr;
-    const uint4* arow[MT];   // this lane's activation row at the warp's first group, or NULL past M
+    // Per-lane pointers at the warp's first group; group `rel` lies rel strides
+    // further (a weight slot is < 4 GB by its format, so 32-bit products do).
+    const uint32_t wstride = NB * 512u, sstride = N * 2u;   // bytes per k group
+    const char* wl = (const char*)(wp + ((size_t)kg0 * NB + nb) * 32 + lane);
+    const char* wl2 = DUAL ? (const char*)(wp2 + ((size_t)kg0 * NB + nb) * 32 + lane) : nullptr;
+    const char* sl = (const char*)(sc + (size_t)kg0 * N + n_lo);
+    const char* sl2 = DUAL ? (const char*)(sc2 + (size_t)kg0 * N + n_lo) : nullptr;
+    // This lane's activation row at the warp's first group. Rows past M read
+    // row M-1 instead (no branch in the loop); their results are never stored.
+    const char* arow[MT];
 #pragma unroll
     for (int i = 0; i < MT; i++) {
-        const uint32_t m = m0 + i * 8 + g;
-        arow[i] = m < M ? (const uint4*)(a + (size_t)m * K + (size_t)kg0 * 64 + t * 16) : nullptr;
-    }
-    for (uint32_t kg = kg0; kg < (FULL ? kg0 + 1 : kg1); kg += UNROLL) {
-        uint4 wq[UNROLL], wq2[DUAL ? UNROLL : 1];
-        uint16_t s0[UNROLL], s1[UNROLL], t0[DUAL ? UNROLL : 1], t1[DUAL ? UNROLL : 1];
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            if (FULL || kg + u < kg1) {
-                wq[u] = __ldcs(wbase + (size_t)(kg + u) * NB * 32);  // streamed once: evict first
-                s0[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo);
-                s1[u] = __ldg(sc + (size_t)(kg + u) * N + n_lo + 8);
-                if (DUAL) {
-                    wq2[u] = __ldcs(wbase2 + (size_t)(kg + u) * NB * 32);
-                    t0[u] = __ldg(sc2 + (size_t)(kg + u) * N + n_lo);
-                    t1[u] = __ldg(sc2 + (size_t)(kg + u) * N + n_lo + 8);
-                }
-            } else {
-                wq[u] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-                s0[u] = 0; s1[u] = 0;
-                if (DUAL) { wq2[u] = wq[u]; t0[u] = 0; t1[u] = 0; }
-            }
-        }
-        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++) {
-            if (!FULL && kg + u >= kg1) break;
-            uint32_t af[4][4], af2[DUAL ? 4 : 1][4];
-            {
-                const __half2 slo = __half2half2(__ushort_as_half(s0[u]));
-                const __half2 shi = __half2half2(__ushort_as_half(s1[u]));
-                dequant_word(wq[u].x, slo, shi, af[0]);
-                dequant_word(wq[u].y, slo, shi, af[1]);
-                dequant_word(wq[u].z, slo, shi, af[2]);
-                dequant_word(wq[u].w, slo, shi, af[3]);
-            }
-            if (DUAL) {
-                const __half2 slo = __half2half2(__ushort_as_half(t0[u]));
-                const __half2 shi = __half2half2(__ushort_as_half(t1[u]));
-                dequant_word(wq2[u].x, slo, shi, af2[0]);
-                dequant_word(wq2[u].y, slo, shi, af2[1]);
-                dequant_word(wq2[u].z, slo, shi, af2[2]);
-                dequant_word(wq2[u].w, slo, shi, af2[3]);
-            }
-#pragma unroll
-            for (int i = 0; i < MT; i++) {
-                uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0;
-                if (arow[i]) {
-                    const uint4* ap = arow[i] + (size_t)(kg - kg0 + u) * 8;   // 64 fp16 per group
-                    b0 = __ldg(ap);
-                    b1 = __ldg(ap + 1);
-                }
-                mma16816(acc[i], af[0], b0.x, b0.y);
-                mma16816(acc[i], af[1], b0.z, b0.w);
-                mma16816(acc[i], af[2], b1.x, b1.y);
-                mma16816(acc[i], af[3], b1.z, b1.w);
-                if (DUAL) {
-                    mma16816(acc2[i], af2[0], b0.x, b0.y);
-                    mma16816(acc2[i], af2[1], b0.z, b0.w);
-                    mma16816(acc2[i], af2[2], b1.x, b1.y);
-                    mma16816(acc2[i], af2[3], b1.z, b1.w);
-                }
-            }
-        }
+        const uint32_t m = min(m0 + i * 8 + g, M - 1);
+        arow[i] = (const char*)(a + (size_t)m * K + (size_t)kg0 * 64 + t * 16);
     }
 
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Rolling window of UNROLL k groups per warp: the first batch is requested
+    // before the dependency wait, and (beyond WALK_ONE) every register slot is
+    // refilled as soon as its group has been consumed.
+    uint4 wq[UNROLL], wq2[DUAL ? UNROLL : 1];
+    uint16_t s0[UNROLL], s1[UNROLL], t0[DUAL ? UNROLL : 1], t1[DUAL ? UNROLL : 1];
+    auto fetch = [&](int u, uint32_t rel) {
+        const uint32_t wo = rel * wstride, so = rel * sstride;
+        wq[u] = __ldcs((const uint4*)(wl + wo));   // streamed once: evict first
+        s0[u] = __ldg((const uint16_t*)(sl + so));
+        s1[u] = __ldg((const uint16_t*)(sl + so) + 8);
+        if (DUAL) {
+            wq2[u] = __ldcs((const uint4*)(wl2 + wo));
+            t0[u] = __ldg((const uint16_t*)(sl2 + so));
+            t1[u] = __ldg((const uint16_t*)(sl2 + so) + 8);
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+        if (FULL || kg0 + u < kg1) {
+            fetch(u, (uint32_t)u);
+        } else {
+            wq[u] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+            s0[u] = 0; s1[u] = 0;
+            if (DUAL) { wq2[u] = wq[u]; t0[u] = 0; t1[u] = 0; }
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // activations of group `rel`, fetched one group ahead of their use
+    uint4 bc[MT][2];
+    auto load_act = [&](uint4 (&b)[MT][2], uint32_t rel) {
+#pragma unroll
+        for (int i = 0; i < MT; i++) {
+            const uint4* ap = (const uint4*)(arow[i] + rel * 128u);   // 64 fp16 per group
+            b[i][0] = ld_ordered(ap);
+            b[i][1] = ld_ordered(ap + 1);
+        }
+    };
+    load_act(bc, 0);
+    const uint32_t last = kg1 - kg0 - 1;
+    auto batch = [&](uint32_t relb, bool more) {   // groups relb .. relb+UNROLL-1
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            if (!FULL && relb + u > last) break;
+            uint4 bn[MT][2];
+            const bool have_next = u + 1 < UNROLL || !ONE;
+            if (have_next) load_act(bn, ONE ? (uint32_t)(u + 1) : min(relb + u + 1, last));
+            uint32_t af[4][4];
+            dequant_word(wq[u].x, af[0]);
+            dequant_word(wq[u].y, af[1]);
+            dequant_word(wq[u].z, af[2]);
+            dequant_word(wq[u].w, af[3]);
+            {
+                const float slo = h2f(s0[u]), shi = h2f(s1[u]);
+#pragma unroll
+                for (int i = 0; i < MT; i++) mma_group(acc[i], af, bc[i][0], bc[i][1], slo, shi);
+            }
+            if (DUAL) {
+                dequant_word(wq2[u].x, af[0]);
+                dequant_word(wq2[u].y, af[1]);
+                dequant_word(wq2[u].z, af[2]);
+                dequant_word(wq2[u].w, af[3]);
+                const float tlo = h2f(t0[u]), thi = h2f(t1[u]);
+#pragma unroll
+                for (int i = 0; i < MT; i++) mma_group(acc2[i], af, bc[i][0], bc[i][1], tlo, thi);
+            }
+            if (!ONE && more && (FULL || relb + UNROLL + u <= last)) fetch(u, relb + UNROLL + u);
+            if (have_next) {
+#pragma unroll
+                for (int i = 0; i < MT; i++) {
+                    bc[i][0] = bn[i][0];
+                    bc[i][1] = bn[i][1];
+                }
+            }
+        }
+    };
+    if (ONE) {
+        batch(0, false);
+    } else {
+        for (uint32_t relb = 0; relb <= last; relb += UNROLL) batch(relb, relb + UNROLL <= last);
+    }
+
 #pragma unroll
     for (int i = 0; i < MT; i++)
 #pragma unroll
@@ -270,19 +340,27 @@ static uint32_t skinny_kgw(uint32_t KG) {
     return kgw;
 }
 
+#define SKINNY_ARGS(P1, S1, P2, S2) a, (const uint4*)(P1), S1, (const uint4*)(P2), (const uint16_t*)(S2), y, M, K, N, kgw, ep
+
 void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
                     uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep) {
     if (!M || !N || !K) return;
-    const uint32_t KG = K / 64, kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    const uint32_t KG = K / 64;
+    const uint32_t kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    const dim3 block(nwarps * 32);
     if (M <= 8) {
-        dim3 grid(N / 16, 1);
-        size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
-        if (kgw == 8 && KG % 8 == 0) launch_pdl(w4a16_skinny_kernel<1, 8, false, true>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
-        else launch_pdl(w4a16_skinny_kernel<1, 8, false, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
+        const dim3 grid(N / 16, 1);
+        const size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
+        if (kgw == 8 && KG % 8 == 0)
+            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ONE>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+        else if (kgw % 8 == 0 && KG % kgw == 0)
+            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_FULL>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+        else
+            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     } else {
-        dim3 grid(N / 16, (M + 15) / 16);
-        size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<2, 4, false, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)packed, sc, (const uint4*)nullptr, (const uint16_t*)nullptr, y, M, K, N, kgw, ep);
+        const dim3 grid(N / 16, (M + 15) / 16);
+        const size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
+        launch_pdl(w4a16_skinny_kernel<2, 4, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     }
     g_launches++;
 }
@@ -292,16 +370,21 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
                            const uint32_t* pu, const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K,
                            uint32_t N) {
     if (!M || !N || !K) return;
-    const uint32_t KG = K / 64, kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    const uint32_t KG = K / 64;
+    uint32_t kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
     W4Epilogue ep;
     if (M <= 8) {
-        dim3 grid(N / 16, 1);
-        size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<1, 4, true, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        const dim3 grid(N / 16, 1);
+        if (KG % 4 == 0 && KG / 4 <= 20) {   // whole 4-group warps: the branch-free variant
+            kgw = 4;
+            nwarps = KG / 4;
+            launch_pdl(w4a16_skinny_kernel<1, 4, true, WALK_ONE>, grid, dim3(nwarps * 32), (size_t)nwarps * 8 * 32 * sizeof(float), st, SKINNY_ARGS(pg, sg, pu, su));
+        } else {
+            launch_pdl(w4a16_skinny_kernel<1, 4, true, WALK_ANY>, grid, dim3(nwarps * 32), (size_t)nwarps * 8 * 32 * sizeof(float), st, SKINNY_ARGS(pg, sg, pu, su));
+        }
     } else {
-        dim3 grid(N / 16, (M + 15) / 16);
-        size_t smem = (size_t)nwarps * 16 * 32 * sizeof(float);
-        launch_pdl(w4a16_skinny_kernel<2, 2, true, false>, grid, dim3(nwarps * 32), smem, st, a, (const uint4*)pg, sg, (const uint4*)pu, su, y, M, K, N, kgw, ep);
+        const dim3 grid(N / 16, (M + 15) / 16);
+        launch_pdl(w4a16_skinny_kernel<2, 2, true, WALK_ANY>, grid, dim3(nwarps * 32), (size_t)nwarps * 16 * 32 * sizeof(float), st, SKINNY_ARGS(pg, sg, pu, su));
     }
     g_launches++;
 }
