@@ -39,6 +39,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="profiling aid for 1 GPU: run rank 0's shard of an N-way tensor-parallel split without the "
+                         "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "attn", "norm", "all"],
@@ -158,8 +161,9 @@ def run_ours(args, rank, world):
         init_tp(lib, rank, world)
 
     t0 = time.time()
-    buf, man = build_decode_runlist(cfg, B, ctx, seed=1004, quant="w4", n_layers=args.layers, tp=world, rank=rank)
-    kvh, nh, hd = cfg.kv_heads // world, cfg.n_heads // world, cfg.head_dim
+    shard = world if world > 1 else max(args.shard_of, 1)
+    buf, man = build_decode_runlist(cfg, B, ctx, seed=1004, quant="w4", n_layers=args.layers, tp=shard, rank=rank)
+    kvh, nh, hd = cfg.kv_heads // shard, cfg.n_heads // shard, cfg.head_dim
     man["kv_elems"], man["q_elems"] = B * kvh * hd, B * nh * hd
     eng = Engine(lib, buf)
     err = ctypes.create_string_buffer(256)
@@ -433,32 +437,62 @@ def init_tp(lib, rank, world):
     raw = bytes(t.cpu().tolist())
     cbuf = (ctypes.c_uint8 * 128).from_buffer_copy(raw)
     assert lib.gehtp_cuda_tp_init(rank, world, cbuf, 128) == 0, lib.gehtp_cuda_last_error()
+    if os.environ.get("GEHTP_TP_P2P", "1") != "0":
+        # mailboxes for the one-kernel all-reduce over peer memory: gather the IPC handles in rank order
+        hb = (ctypes.c_uint8 * 64)()
+        assert lib.gehtp_cuda_tp_p2p_export(hb, 64) == 0, lib.gehtp_cuda_last_error()
+        mine = torch.tensor(list(hb), dtype=torch.uint8, device="cuda")
+        allh = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        raw = b"".join(bytes(h.cpu().tolist()) for h in allh)
+        hbuf = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(raw)
+        assert lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) == 0, lib.gehtp_cuda_last_error()
+        dist.barrier()
 
 
 def main():
     args = parse_args()
+    # stdout carries the JSON line(s) only: libraries that print banners there (NCCL's
+    # version line) are pointed at stderr while the run lasts.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        lines = run_main(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    for ln in lines:
+        print(ln)
+    sys.stdout.flush()
+
+
+def run_main(args):
+    out = []
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     B = args.batch
     config = {"workload": "Qwen3-4B-shaped decoder decode step, W4A16 group-64, batch %d, KV context %d, %d layers + lm_head 151936"
                           % (B, args.ctx, args.layers),
               "batch": B, "kv_context": args.ctx, "layers": args.layers,
-              "parallelism": "tp%d" % world if world > 1 else "single GPU",
+              "parallelism": "tp%d" % world if world > 1 else
+                             ("single GPU" if args.shard_of <= 1 else "rank 0's shard of tp%d, no all-reduce (profiling aid)" % args.shard_of),
               "l2": "inputs larger than L2: every step streams the weights and the KV rings (GBs) once"}
 
     if args.micro:
         if rank == 0:
             for row in run_micro(args.micro):
-                print(json.dumps(row))
-        return
+                out.append(json.dumps(row))
+        return out
 
     if args.impl == "reference":
         if rank != 0:
-            return
+            return out
         probe = reference_sample(args, 1)
         if probe is None:
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libgehtp_ref.so was not built"}))
-            return
+            out.append(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libgehtp_ref.so was not built"}))
+            return out
         reps = int(max(1, min(args.steps, 150.0 // max(probe["sample_wall_s"], 1e-3)))) - 1
         res = reference_sample(args, reps) if reps >= 1 else probe
         line = {"impl": "reference", "metric": METRIC, "value": res["tok_s"], "unit": UNIT, "n_gpus": args.gpus,
@@ -467,12 +501,12 @@ def main():
                 "config": config, "gpu_launches": 0,
                 "cpu_baseline": {"value": res["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": res["sample"]},
                 "e2e": {"value": res["tok_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
-        return
+        out.append(json.dumps(line))
+        return out
 
     r = run_ours(args, rank, world)
     if rank != 0:
-        return
+        return out
     K = args.steps
     peak, peak_src = load_peaks()
     value = B * K / (r["dev_ms"] * 1e-3)
@@ -499,7 +533,8 @@ def main():
         cb = reference_sample(args, 1)
         if cb:
             line["cpu_baseline"] = {"value": cb["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": cb["sample"]}
-    print(json.dumps(line))
+    out.append(json.dumps(line))
+    return out
 
 
 if __name__ == "__main__":

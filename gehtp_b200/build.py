@@ -30,6 +30,7 @@ UNITS = {
     "ops_w4a16.cu": [],
     "w4a16_gemm_sm100.cu": [],
     "tp.cu": [],
+    "tp_p2p.cu": [],
 }
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]

@@ -105,8 +105,6 @@ struct Engine {
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_out_temp = kNoOff;
     bool graph_has_in = false, graph_has_out = false;
-    const void* graph_in_dev = nullptr;
-    void* graph_out_dev = nullptr;
     uint32_t warm_runs = 0;
     unsigned long long graph_launches = 0;  // kernels inside the captured graph
 
@@ -138,6 +136,10 @@ void drop_plan(bool keep_states);
 // tp.cu
 extern std::vector<uint8_t> g_allreduce_after;   // per op: 1 = all-reduce its first output over the ranks
 int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
+// tp_p2p.cu
+bool tp_p2p_ready();
+bool tp_p2p_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
+void tp_p2p_shutdown();
 // fuse.cu
 void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal);
 void fuse_materialize(const wt_blob* b);

@@ -243,7 +243,8 @@ static int finish_run(char* err, size_t errn) {
         *g.h_status = 0;
         cudaMemsetAsync(g.d_status, 0, sizeof(unsigned int), g.stream);
         char m[96];
-        std::snprintf(m, sizeof m, "kv gather miss (state bug) at op %u", code - 1);
+        if (code & 0x80000000u) std::snprintf(m, sizeof m, "tensor-parallel all-reduce timed out waiting for a peer rank");
+        else std::snprintf(m, sizeof m, "kv gather miss (state bug) at op %u", code - 1);
         set_err(err, errn, m);
         return (int)code;
     }
@@ -281,9 +282,11 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
     const bool eager_only = timing || hooks_active() || g.trace_on || !g.opt_graph || !whole || g.prof_ms;
 
     int rc = 0;
-    if (!eager_only && g.graph && (g.graph_out_temp != out_temp || g.graph_has_in != has_in ||
-                                   g.graph_has_out != (out_host != nullptr) || g.graph_in_dev != in_dev ||
-                                   g.graph_out_dev != out_dev)) {
+    // Device-side input and output copies stay outside the graph (their pointers
+    // may change from run to run); host staging goes through fixed pinned buffers
+    // and is part of it.
+    if (!eager_only && g.graph && (g.graph_out_temp != out_temp || g.graph_has_in != (in_host != nullptr) ||
+                                   g.graph_has_out != (out_host != nullptr))) {
         cudaGraphExecDestroy(g.graph);   // same blob, different I/O binding: capture again
         g.graph = nullptr;
     }
@@ -302,8 +305,11 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
             for (auto& kv : g.d_ext)
                 if (b->slots[kv.first].addr == WT_SLOT_EXT_IN) std::memcpy(g.h_in, in_host, b->slots[kv.first].len);
         }
+        if (in_dev) stage_inputs(b, nullptr, in_dev);
         cudaGraphLaunch(g.graph, g.stream);
         g_launches += g.graph_launches;
+        if (out_dev && out_temp < kMaxTemps && g.temp_cap[out_temp])
+            cudaMemcpyAsync(out_dev, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToDevice, g.stream);
         if (!sync_end) return 0;
         rc = finish_run(err, errn);
         if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);
@@ -322,6 +328,7 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
             out_bytes_planned = g.temp_last[out_temp];
             grow_pinned(g.h_out, g.h_out_cap, out_bytes_planned ? out_bytes_planned : 4);
         }
+        if (in_dev) stage_inputs(b, nullptr, in_dev);
         if (cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
             cudaGetLastError();
             g.opt_graph = 0;
@@ -329,7 +336,8 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
         }
     }
     const unsigned long long launches0 = g_launches;
-    if (has_in) stage_inputs(b, in_host, in_dev);
+    if (capture) { if (in_host) stage_inputs(b, in_host, nullptr); }
+    else if (has_in) stage_inputs(b, in_host, in_dev);
     rc = queue_range(first, count, g.opt_fuse != 0, timing, engine_m, op_us, err, errn);
     if (rc == kNeedUnfused) {
         // an op inside a fused chain has to run on its own: plan again with every temp in memory
@@ -364,8 +372,6 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
     if (capture) {
         if (rc == 0 && out_host && out_temp < kMaxTemps && g.temp_cap[out_temp])
             cudaMemcpyAsync(g.h_out, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToHost, g.stream);
-        if (rc == 0 && out_dev && out_temp < kMaxTemps && g.temp_cap[out_temp])
-            cudaMemcpyAsync(out_dev, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToDevice, g.stream);
         cudaGraph_t graph = nullptr;
         cudaError_t ce = cudaStreamEndCapture(g.stream, &graph);
         if (rc != 0 || ce != cudaSuccess || !graph) {
@@ -387,9 +393,10 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
             return run_impl(b, first, count, in_host, in_dev, out_host, out_dev, out_temp, sync_end, engine_m, op_us, err, errn);
         }
         g.graph_launches = g_launches - launches0;
-        g.graph_out_temp = out_temp; g.graph_has_in = has_in; g.graph_has_out = out_host != nullptr;
-        g.graph_in_dev = in_dev; g.graph_out_dev = out_dev;
+        g.graph_out_temp = out_temp; g.graph_has_in = in_host != nullptr; g.graph_has_out = out_host != nullptr;
         cudaGraphLaunch(g.graph, g.stream);
+        if (out_dev && out_temp < kMaxTemps && g.temp_cap[out_temp])
+            cudaMemcpyAsync(out_dev, g.temp_dev[out_temp], g.temp_last[out_temp], cudaMemcpyDeviceToDevice, g.stream);
         if (!sync_end) return 0;
         rc = finish_run(err, errn);
         if (rc == 0 && out_host && out_temp < kMaxTemps) std::memcpy(out_host, g.h_out, g.temp_last[out_temp]);

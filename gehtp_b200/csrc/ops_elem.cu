@@ -277,8 +277,57 @@ __global__ void reduce_kernel(const uint16_t* __restrict__ x, uint16_t* __restri
         y[e] = f2h(acc);
     }
 }
+// Max / min over a long contiguous axis (inner == 1): one CTA per output. The
+// sequential scan keeps the first of equal candidates (it matters for +0 / -0),
+// so candidates carry their position and ties go to the smaller one.
+__global__ void __launch_bounds__(256)
+reduce_minmax_row_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, uint32_t L, int is_max) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    const uint16_t* row = x + (size_t)blockIdx.x * L;
+    float best = is_max ? -3.0e38f : 3.0e38f;
+    uint32_t bi = 0xffffffffu;
+    auto take = [&](uint16_t h, uint32_t l) {
+        const float v = h2f(h);
+        if (is_max ? v > best : v < best) { best = v; bi = l; }
+    };
+    // unaligned head, 16-byte body (ascending positions per thread), tail
+    uint32_t head = (uint32_t)((16 - ((uintptr_t)row & 15)) & 15) / 2;
+    if (head > L) head = L;
+    const uint32_t nvec = (L - head) / 8;
+    if (threadIdx.x < head) take(row[threadIdx.x], threadIdx.x);
+    const uint4* rv = (const uint4*)(row + head);
+    for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 q = __ldg(rv + v);
+        const uint16_t* h = (const uint16_t*)&q;
+#pragma unroll
+        for (int i = 0; i < 8; i++) take(h[i], head + v * 8 + i);
+    }
+    for (uint32_t l = head + nvec * 8 + threadIdx.x; l < L; l += blockDim.x) take(row[l], l);
+    auto better = [&](float v, uint32_t i, float w, uint32_t j) {   // is (v,i) ahead of (w,j)?
+        return (is_max ? v > w : v < w) || (v == w && i < j);
+    };
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t i = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(v, i, best, bi)) { best = v; bi = i; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (better(sv[w], si[w], best, bi)) { best = sv[w]; bi = si[w]; }
+        y[blockIdx.x] = f2h(best);
+    }
+}
+
 void k_reduce(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t outer, uint32_t L,
               uint32_t inner, uint32_t subtype) {
+    if (inner == 1 && L >= 1024 && (subtype == 2 || subtype == 3)) {
+        reduce_minmax_row_kernel<<<outer, 256, 0, st>>>(x, y, L, subtype == 2);
+        g_launches++;
+        return;
+    }
     reduce_kernel<<<grid_for((size_t)outer * inner, 128), 128, 0, st>>>(x, y, outer, L, inner,
                                                                       subtype);
     g_launches++;

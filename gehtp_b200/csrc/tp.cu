@@ -38,6 +38,7 @@ int gehtp_cuda_tp_init(int rank, int world, const void* nccl_unique_id, size_t i
 }
 
 void gehtp_cuda_tp_shutdown(void) {
+    tp_p2p_shutdown();
     if (g.nccl_comm) { ncclCommDestroy((ncclComm_t)g.nccl_comm); g.nccl_comm = nullptr; }
     g.tp_world = 1; g.tp_rank = 0;
     g_allreduce_after.clear();
@@ -59,7 +60,9 @@ int gehtp_cuda_tp_allreduce_after(const uint32_t* op_idx, uint32_t n) {
 namespace gehtp {
 // In-place fp16 sum over the ranks, queued on `st`.
 int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems) {
-    if (g.tp_world <= 1 || !g.nccl_comm) return 0;
+    if (g.tp_world <= 1) return 0;
+    if (tp_p2p_allreduce_f16(st, buf, elems)) return 0;   // small vectors: one kernel over peer memory
+    if (!g.nccl_comm) return -1;
     ncclResult_t r = ncclAllReduce(buf, buf, elems, ncclHalf, ncclSum, (ncclComm_t)g.nccl_comm, st);
     return r == ncclSuccess ? 0 : -1;
 }

@@ -1,0 +1,208 @@
+// One-shot all-reduce over NVLink peer memory for the small vectors of a
+// tensor-parallel decode step (one row of the hidden state per sequence).
+//
+// Every rank owns a mailbox in its own HBM: two banks (epoch parity) of one data
+// slot and one flag row per source rank. An all-reduce is ONE kernel per rank:
+//   push : each CTA copies its chunk of the local partial sums into slot
+//          [bank][my rank] of every rank's mailbox (its own included), fences,
+//          and stores the epoch into flag [bank][my rank][cta] of every mailbox;
+//   wait : the CTA polls its own mailbox until the flags of all ranks for this
+//          chunk carry the epoch (bounded: on a timeout it raises the engine's
+//          status word and goes on, the step is then reported as failed);
+//   sum  : the CTA adds the world slots in rank order in fp32 and stores fp16,
+//          so every rank gets the same bits.
+// The epoch lives in device memory and is advanced by the last CTA of each
+// launch, so a captured CUDA graph replays correctly. Bank k%2 is only written
+// again by all-reduce k+2, which a rank can reach only after every peer has
+// flagged k+1, i.e. finished reading k: two banks suffice.
+//
+// Only plain peer loads/stores are used (no multimem, no bulk copies).
+#include <cstdio>
+#include <cstring>
+#include "common.cuh"
+#include "engine.h"
+#include "launchers.h"
+
+namespace gehtp {
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxCtas = 64;
+constexpr size_t kSlotBytes = 1u << 20;                       // per source rank and bank
+constexpr size_t kDataBytes = 2 * kMaxWorld * kSlotBytes;
+constexpr size_t kFlagBytes = 2 * kMaxWorld * kMaxCtas * sizeof(uint32_t);
+constexpr size_t kBoxBytes = kDataBytes + kFlagBytes;
+constexpr uint32_t kSpinLimit = 4u * 1000u * 1000u;           // polls (with a short sleep) before giving up
+constexpr unsigned int kStatusTimeout = 0x80000001u;
+
+struct P2PCtx {
+    unsigned char* box[kMaxWorld];   // mailbox of every rank as mapped in this process (own one included)
+    uint32_t* epoch;                 // [0] epoch of the last finished all-reduce, [1] CTAs done in this launch
+    unsigned int* status;
+    int rank, world;
+};
+
+struct P2PState {
+    unsigned char* my_box = nullptr;
+    void* peer_base[kMaxWorld] = {};
+    uint32_t* epoch = nullptr;
+    P2PCtx ctx{};
+    bool ready = false;
+} p2p;
+
+__device__ __forceinline__ unsigned char* slot_ptr(unsigned char* box, uint32_t bank, int src) {
+    return box + ((size_t)bank * kMaxWorld + src) * kSlotBytes;
+}
+__device__ __forceinline__ uint32_t* flag_ptr(unsigned char* box, uint32_t bank, int src, uint32_t cta) {
+    return (uint32_t*)(box + kDataBytes) + ((size_t)bank * kMaxWorld + src) * kMaxCtas + cta;
+}
+
+// vecs: number of 16-byte vectors of the fp16 vector.
+__global__ void __launch_bounds__(256)
+p2p_allreduce_kernel(P2PCtx c, const uint4* in, uint4* out, uint32_t vecs) {   // in == out is allowed
+    const uint32_t epoch = c.epoch[0] + 1, bank = epoch & 1u;
+    const uint32_t per = (vecs + gridDim.x - 1) / gridDim.x;
+    const uint32_t v0 = blockIdx.x * per, v1 = min(v0 + per, vecs);
+
+    // push
+    for (uint32_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+        const uint4 x = in[v];
+        for (int p = 0; p < c.world; p++) ((uint4*)slot_ptr(c.box[p], bank, c.rank))[v] = x;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < (uint32_t)c.world) {
+        uint32_t* f = flag_ptr(c.box[threadIdx.x], bank, c.rank, blockIdx.x);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+    // wait
+    if (threadIdx.x < (uint32_t)c.world) {
+        const uint32_t* f = flag_ptr(c.box[c.rank], bank, (int)threadIdx.x, blockIdx.x);
+        uint32_t seen = 0, it = 0;
+        for (; it < kSpinLimit; it++) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+            if ((int32_t)(seen - epoch) >= 0) break;
+            __nanosleep(64);
+        }
+        if (it == kSpinLimit) raise_status(c.status, kStatusTimeout);
+    }
+    __syncthreads();
+    // sum, rank order
+    for (uint32_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+        for (int r = 0; r < c.world; r++) {
+            const uint4 x = __ldcg((const uint4*)slot_ptr(c.box[c.rank], bank, r) + v);
+            const __half2* h = (const __half2*)&x;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(h[i]);
+                acc[2 * i] += f.x;
+                acc[2 * i + 1] += f.y;
+            }
+        }
+        uint4 o;
+        uint32_t* ow = (uint32_t*)&o;
+#pragma unroll
+        for (int i = 0; i < 4; i++) ow[i] = (uint32_t)f2h(acc[2 * i]) | ((uint32_t)f2h(acc[2 * i + 1]) << 16);
+        out[v] = o;
+    }
+    // last CTA of the launch publishes the epoch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&c.epoch[1], 1u) == gridDim.x - 1) {
+            c.epoch[1] = 0;
+            __threadfence();
+            c.epoch[0] = epoch;
+        }
+    }
+}
+
+}  // namespace
+
+bool tp_p2p_ready() { return p2p.ready; }
+
+// In-place all-reduce of `elems` fp16 values; false when the vector does not
+// fit the mailbox or is not 16-byte sized/aligned (the caller then uses NCCL).
+bool tp_p2p_allreduce_f16(cudaStream_t st, void* buf, size_t elems) {
+    if (!p2p.ready) return false;
+    const size_t bytes = elems * 2;
+    if (bytes > kSlotBytes || (bytes & 15) || ((uintptr_t)buf & 15)) return false;
+    const uint32_t vecs = (uint32_t)(bytes / 16);
+    uint32_t ctas = (vecs + 511) / 512;       // two vectors per thread
+    if (ctas < 1) ctas = 1;
+    if (ctas > kMaxCtas) ctas = kMaxCtas;
+    p2p_allreduce_kernel<<<ctas, 256, 0, st>>>(p2p.ctx, (const uint4*)buf, (uint4*)buf, vecs);
+    g_launches++;
+    return true;
+}
+
+void tp_p2p_shutdown() {
+    if (!p2p.my_box) return;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < kMaxWorld; r++)
+        if (p2p.peer_base[r]) { cudaIpcCloseMemHandle(p2p.peer_base[r]); p2p.peer_base[r] = nullptr; }
+    cudaFree(p2p.my_box);
+    cudaFree(p2p.epoch);
+    p2p = P2PState();
+}
+
+}  // namespace gehtp
+
+using namespace gehtp;
+
+extern "C" {
+
+int gehtp_cuda_tp_p2p_export(void* handle_out, size_t handle_bytes) {
+    if (!handle_out || handle_bytes < sizeof(cudaIpcMemHandle_t)) return -1;
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (!p2p.my_box) {
+        if (cudaMalloc(&p2p.my_box, kBoxBytes) != cudaSuccess || cudaMalloc(&p2p.epoch, 2 * sizeof(uint32_t)) != cudaSuccess) {
+            g.last_error = "tp p2p: mailbox allocation failed";
+            cudaGetLastError();
+            return -1;
+        }
+        cudaMemset(p2p.my_box, 0, kBoxBytes);
+        cudaMemset(p2p.epoch, 0, 2 * sizeof(uint32_t));
+        cudaDeviceSynchronize();
+    }
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, p2p.my_box) != cudaSuccess) {
+        g.last_error = "tp p2p: cudaIpcGetMemHandle failed";
+        cudaGetLastError();
+        return -1;
+    }
+    std::memcpy(handle_out, &h, sizeof h);
+    return 0;
+}
+
+int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int world) {
+    if (!handles || handle_stride < sizeof(cudaIpcMemHandle_t) || world != g.tp_world || world > kMaxWorld || !p2p.my_box) {
+        g.last_error = "tp p2p: bad import arguments (export first, world must match tp_init)";
+        return -1;
+    }
+    P2PCtx c{};
+    c.rank = g.tp_rank; c.world = world; c.epoch = p2p.epoch; c.status = g.d_status;
+    for (int r = 0; r < world; r++) {
+        if (r == g.tp_rank) { c.box[r] = p2p.my_box; continue; }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, (const unsigned char*)handles + (size_t)r * handle_stride, sizeof h);
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            g.last_error = "tp p2p: cudaIpcOpenMemHandle failed (no peer access between the ranks' GPUs?)";
+            cudaGetLastError();
+            return -1;
+        }
+        p2p.peer_base[r] = p;
+        c.box[r] = (unsigned char*)p;
+    }
+    p2p.ctx = c;
+    p2p.ready = true;
+    if (g.planned) drop_plan(true);
+    return 0;
+}
+
+}  // extern "C"

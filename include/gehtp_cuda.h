@@ -129,6 +129,16 @@ void gehtp_cuda_tp_shutdown(void);
  * row-parallel projections): the engine all-reduces it in place right after
  * the op. Indices come from the blob's sideband manifest. */
 int gehtp_cuda_tp_allreduce_after(const uint32_t* op_idx, uint32_t n);
+/* Optional fast path for the small all-reduces of a decode step: a one-kernel
+ * all-reduce over NVLink peer memory (each rank pushes its partial sums into a
+ * mailbox in every rank's HBM, waits for the peers' flags with a bounded poll,
+ * and adds the slots in rank order). After gehtp_cuda_tp_init, every rank
+ * calls _export (64-byte CUDA IPC handle of its mailbox), the caller gathers
+ * the handles of all ranks in rank order (`handle_stride` bytes apart) and
+ * every rank calls _import. Vectors above 1 MiB keep using NCCL. A peer that
+ * never arrives makes the run return an error instead of hanging. */
+int gehtp_cuda_tp_p2p_export(void* handle_out, size_t handle_bytes);
+int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int world);
 
 /* Kernels launched by the engine since the process started. */
 uint64_t gehtp_cuda_launch_count(void);

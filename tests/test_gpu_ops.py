@@ -180,6 +180,28 @@ def test_data_movement_ops(cuda, ref):
         assert x1 is not None and np.array_equal(x1, x2), "output %d (temp %d) differs" % (i, outs[i])
 
 
+def test_reduce_minmax_long_rows_bit_exact(cuda, ref):
+    """Max / min over long rows take the CTA-per-row kernel; +0 / -0 ties must resolve as in a sequential scan."""
+    rng = np.random.default_rng(12)
+    L = 5000
+    x = rnd16(rng, (4, L))
+    x[1] = -np.abs(x[1]) - 1.0          # max is the least negative
+    x[2] = -np.abs(x[2])
+    x[2, 777] = np.float16(-0.0)        # -0 first, +0 later: max keeps -0
+    x[2, 3000] = np.float16(0.0)
+    x[3] = np.abs(x[3])
+    x[3, 4000] = np.float16(0.0)        # +0 first, -0 later: min keeps +0
+    x[3, 4500] = np.float16(-0.0)
+    b = BlobBuilder()
+    sx = b.add_slot(x)
+    outs = [1, 2]
+    b.add_op(OP.REDUCE, [S(sx), 1, x.size, 1, 2, 4, L, 1, 1])
+    b.add_op(OP.REDUCE, [S(sx), 2, x.size, 1, 3, 4, L, 1, 1])
+    g, r = run_both(cuda, ref, b, outs)
+    for x1, x2 in zip(g, r):
+        assert x1 is not None and np.array_equal(x1, x2)
+
+
 def test_kv_ring_append_gather_bit_exact(cuda, ref):
     """KV append -> GQA gather byte round trip, ring wrap, zero tail (test_kv_ssm_ops.c of the reference)."""
     rng = np.random.default_rng(3)
