@@ -53,7 +53,10 @@ def test_w4a16_matmul_vs_oracle(cuda, orc, M, K, N):
     assert_fp16_close(got, want, "w4a16 %dx%dx%d" % (M, K, N))
 
 
-@pytest.mark.parametrize("M,K,N", [(128, 1024, 3072), (128, 64, 128), (256, 512, 384), (200, 2560, 1280), (512, 1024, 4096)])
+# the last two shapes give a CTA more than one tile (both TMEM accumulator buffers in use),
+# with one and with two 128-row halves per tile; M = 1000 leaves a ragged last tile
+@pytest.mark.parametrize("M,K,N", [(128, 1024, 3072), (128, 64, 128), (256, 512, 384), (200, 2560, 1280), (512, 1024, 4096),
+                                   (640, 256, 6144), (1000, 512, 5120)])
 def test_w4a16_tcgen05_gemm_vs_oracle(cuda, orc, M, K, N):
     """The tensor-core (tcgen05 / TMEM) path on its own, config 1 of the baseline first."""
     rng = np.random.default_rng(1001)
