@@ -44,7 +44,7 @@ def parse_args():
                          "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "attn", "norm", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "attn", "norm", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -329,6 +329,11 @@ def run_micro(which):
                 us, nbytes, _ = w4(M, K, N, 1, dual)
                 out.append({"kernel": "w4a16_gemv" + ("_swiglu" if dual else ""), "M": M, "K": K, "N": N, "us": us,
                             "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak_hbm})
+    if which == "gemm1":    # one mid-size GEMM: a small case for profiler captures
+        M, K, N = 2048, 2560, 9728
+        us, _, flops = w4(M, K, N, 2, n=4)
+        out.append({"kernel": "w4a16_gemm_tcgen05", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
+                    "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
     if which == "lmhead":   # the vocabulary projection alone: a small case for profiler captures
         for M in (1, 8):
             us, nbytes, _ = w4(M, 2560, 151936, 1, False, n=8)

@@ -15,7 +15,8 @@
 //                scales with bulk copies into an RSTAGES-deep ring.
 //   warp 3     : owns the TMEM allocation.
 //   warps 4-7  : epilogue (tcgen05.ld -> fp16 -> 64-byte row segments).
-//   warps 8-15 : dequant. Warp w turns strip unit w of the stage into fp16 with
+//   warps 8-23 : dequant, four groups of four warps; group q takes every fourth
+//                k block. A warp turns two strip units (32 columns) into fp16 with
 //                the magic-number trick, multiplies by the group scale and stores
 //                16-byte chunks into the stage's B tile in the 128B-swizzled
 //                K-major form tcgen05.mma reads.
@@ -36,8 +37,8 @@ constexpr int STAGES = 4;          // A/B operand ring
 constexpr int RSTAGES = 6;         // int4 + scale ring
 constexpr int HALF_A_BYTES = 128 * BK * 2, B_BYTES = BN * BK * 2;
 constexpr int RAW_BYTES = BN * BK / 2, RAW_SLOT = RAW_BYTES + BN * 2;   // nibbles + 128 fp16 scales
-constexpr int NTHREADS = 512;
-constexpr int DQ_WARPS = 8, EPI_WARPS = 4;
+constexpr int NTHREADS = 768;
+constexpr int DQ_PER_STAGE = 4, EPI_WARPS = 4;   // 16 dequant warps, 4 of them per k block
 constexpr uint32_t SPIN_LIMIT = 2u * 1000u * 1000u;   // try_wait polls before a role gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -164,10 +165,10 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&bars->full_a[s], 1);
-            mbar_init(&bars->full_b[s], DQ_WARPS);
+            mbar_init(&bars->full_b[s], DQ_PER_STAGE);
             mbar_init(&bars->empty[s], 1);
         }
-        for (int s = 0; s < RSTAGES; s++) { mbar_init(&bars->raw_full[s], 1); mbar_init(&bars->raw_empty[s], DQ_WARPS); }
+        for (int s = 0; s < RSTAGES; s++) { mbar_init(&bars->raw_full[s], 1); mbar_init(&bars->raw_empty[s], DQ_PER_STAGE); }
         for (int s = 0; s < 2; s++) { mbar_init(&bars->tmem_full[s], 1); mbar_init(&bars->tmem_empty[s], EPI_WARPS); }
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -302,43 +303,62 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             if (lane == 0) mbar_arrive(&bars->tmem_empty[buf]);
         }
     } else if (warp >= 8) {
-        // ---- dequant: warp dw owns strip unit dw (16 columns) of every k block
-        const uint32_t dw = warp - 8, g = lane >> 2, t = lane & 3;
-        const uint32_t col = dw * 16 + g, r0 = col, r1 = col + 8;
-        // row r, 16-byte chunk c (8 k) lives at r*128 + ((c ^ (r & 7)) << 4)
-        const uint32_t o00 = r0 * 128 + (((2 * t) ^ (r0 & 7)) << 4), o01 = r0 * 128 + (((2 * t + 1) ^ (r0 & 7)) << 4);
-        const uint32_t o10 = r1 * 128 + (((2 * t) ^ (r1 & 7)) << 4), o11 = r1 * 128 + (((2 * t + 1) ^ (r1 & 7)) << 4);
-        uint32_t it = 0;
-        bool live = true;
-        for (uint32_t tile = blockIdx.x; tile < tiles && live; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < KG; kb++, it++) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                const uint32_t r = it % RSTAGES, rph = (it / RSTAGES) & 1;
-                // warp-uniform decisions: every lane polls, the warp leaves together
-                if (__any_sync(0xffffffffu, *abort_flag != 0) ||
-                    !__all_sync(0xffffffffu, mbar_wait(&bars->raw_full[r], rph))) { *abort_flag = 1; live = false; break; }
-                const unsigned char* raw = sRaw + r * RAW_SLOT;
-                const uint4 w = *(const uint4*)(raw + (dw * 32 + lane) * 16);
-                const uint16_t* ss = (const uint16_t*)(raw + RAW_BYTES);
-                const __half2 slo = __half2half2(__ushort_as_half(ss[col]));
-                const __half2 shi = __half2half2(__ushort_as_half(ss[col + 8]));
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->raw_empty[r]);      // the slot is in registers now
-                uint32_t o[4][4];
-                dequant_word(w.x, slo, shi, o[0]);
-                dequant_word(w.y, slo, shi, o[1]);
-                dequant_word(w.z, slo, shi, o[2]);
-                dequant_word(w.w, slo, shi, o[3]);
-                if (!__all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ph ^ 1))) { *abort_flag = 1; live = false; break; }
-                unsigned char* bt = sB + s * B_BYTES;
-                *(uint4*)(bt + o00) = make_uint4(o[0][0], o[0][2], o[1][0], o[1][2]);
-                *(uint4*)(bt + o01) = make_uint4(o[2][0], o[2][2], o[3][0], o[3][2]);
-                *(uint4*)(bt + o10) = make_uint4(o[0][1], o[0][3], o[1][1], o[1][3]);
-                *(uint4*)(bt + o11) = make_uint4(o[2][1], o[2][3], o[3][1], o[3][3]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->full_b[s]);
+        // ---- dequant: 16 warps in 4 groups; group q takes the k blocks with it % 4 == q, and
+        // warp j of a group turns strip units 2j, 2j+1 (32 columns) of that block into fp16.
+        // A warp so has four k-block periods for its two units, and pays one proxy fence for both.
+        const uint32_t dw = warp - 8, q = dw >> 2, j = dw & 3, g = lane >> 2, t = lane & 3;
+        const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = my_tiles * KG;
+        const uint32_t sB_u32 = smem_u32(sB), sRaw_u32 = smem_u32(sRaw);
+        uint32_t off[2][4];     // byte offsets of this lane's four 16-byte chunks inside a B stage, per unit
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t r0 = (2 * j + u) * 16 + g, r1 = r0 + 8;
+            // row r, 16-byte chunk c (8 k) lives at r*128 + ((c ^ (r & 7)) << 4)
+            off[u][0] = r0 * 128 + (((2 * t) ^ (r0 & 7)) << 4);
+            off[u][1] = r0 * 128 + (((2 * t + 1) ^ (r0 & 7)) << 4);
+            off[u][2] = r1 * 128 + (((2 * t) ^ (r1 & 7)) << 4);
+            off[u][3] = r1 * 128 + (((2 * t + 1) ^ (r1 & 7)) << 4);
+        }
+        for (uint32_t it = q; it < total; it += 4) {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            const uint32_t r = it % RSTAGES, rph = (it / RSTAGES) & 1;
+            // warp-uniform decisions: every lane polls, the warp leaves together
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->raw_full[r], rph))) { *abort_flag = 1; break; }
+            const uint32_t raw = sRaw_u32 + r * RAW_SLOT;
+            uint4 w[2];
+            uint16_t sl[2], sh[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint32_t unit = 2 * j + u;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w[u].x), "=r"(w[u].y), "=r"(w[u].z), "=r"(w[u].w) : "r"(raw + (unit * 32 + lane) * 16));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sl[u]) : "r"(raw + RAW_BYTES + (unit * 16 + g) * 2));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sh[u]) : "r"(raw + RAW_BYTES + (unit * 16 + g + 8) * 2));
             }
+            uint32_t o[2][4][4];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const __half2 slo = __half2half2(__ushort_as_half(sl[u])), shi = __half2half2(__ushort_as_half(sh[u]));
+                dequant_word(w[u].x, slo, shi, o[u][0]);
+                dequant_word(w[u].y, slo, shi, o[u][1]);
+                dequant_word(w[u].z, slo, shi, o[u][2]);
+                dequant_word(w[u].w, slo, shi, o[u][3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->raw_empty[r]);      // the slot has been consumed into registers
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ph ^ 1))) { *abort_flag = 1; break; }
+            const uint32_t bt = sB_u32 + s * B_BYTES;
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][0]), "r"(o[u][0][0]), "r"(o[u][0][2]), "r"(o[u][1][0]), "r"(o[u][1][2]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][1]), "r"(o[u][2][0]), "r"(o[u][2][2]), "r"(o[u][3][0]), "r"(o[u][3][2]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][2]), "r"(o[u][0][1]), "r"(o[u][0][3]), "r"(o[u][1][1]), "r"(o[u][1][3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][3]), "r"(o[u][2][1]), "r"(o[u][2][3]), "r"(o[u][3][1]), "r"(o[u][3][3]) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full_b[s]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
