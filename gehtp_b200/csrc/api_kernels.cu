@@ -92,6 +92,7 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
     cudaMemcpyAsync(dr.p, kv_ring, ring_b, cudaMemcpyHostToDevice, g.stream);
     if (mask) cudaMemcpyAsync(dm.p, mask, (size_t)n_kv * 2, cudaMemcpyHostToDevice, g.stream);
     AttnDecodeArgs a{};
+    a.status = g.d_status;
     a.q = dq.as<uint16_t>(); a.ring = dr.as<uint16_t>(); a.counter = nullptr; a.n_kv = n_kv; a.n_kv_add = 0; a.bump_counter = nullptr;
     a.mask = mask ? dm.as<uint16_t>() : nullptr; a.mask_seq_stride = 0; a.kvh_per_seq = kv_heads;
     a.scale = scale; a.scale_div = 0; a.rep = rep; a.kv_heads = kv_heads; a.nslots = nslots; a.nsplit = nsplit;

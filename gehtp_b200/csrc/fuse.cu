@@ -363,6 +363,7 @@ void fuse_materialize(const wt_blob* b) {
             uint32_t* ctr = g.d_st_count + si;
             uint32_t B = sp.B, nh = sp.nh, kvh = sp.kvh, hd = sp.hd, nslots = sp.nslots, pos = sp.pos;
             AttnDecodeArgs a{};
+            a.status = g.d_status;
             a.q = q_out; a.ring = ring; a.counter = ctr; a.n_kv = 0; a.n_kv_add = 1; a.bump_counter = ctr;
             a.mask = mask; a.mask_seq_stride = nh * nslots; a.kvh_per_seq = kvh;
             a.scale = sp.scale; a.scale_div = sp.scale_div; a.rep = nh / kvh; a.kv_heads = B * kvh; a.nslots = nslots;

@@ -22,6 +22,8 @@ struct AttnDecodeArgs {
     uint32_t nsplit;           // context slices per KV head (= slots per head in the scratch buffers)
     float* part_o;             // scratch [kv_heads_total][nsplit][rep][hd]
     float* part_ml;            // scratch [kv_heads_total][nsplit][rep][2]
+    unsigned int* status;      // engine status word (bounded waits report here), or NULL
+    int no_cache;              // 1: keep no host-side record of this ring (its tensor map is built per call)
 };
 
 uint32_t attn_decode_nsplit(uint32_t kv_heads_total, uint32_t max_positions, uint32_t rep, uint32_t hd, size_t max_floats);

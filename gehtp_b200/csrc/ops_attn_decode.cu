@@ -22,6 +22,9 @@
 // item leaves (max, sum, unnormalised output) in a scratch buffer; a second
 // small kernel merges the chunks in chunk order.
 #include <cstdio>
+#include <map>
+#include <tuple>
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "launchers_attn.h"
@@ -461,6 +464,227 @@ attn_decode_group_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     }
 }
 
+// ---------------------------------------------------------------- TMA-fed grouped form
+// Same work split as the grouped kernel above (one CTA = 4 neighbouring KV heads
+// x one even slice of the context, one head per consumer warp), but the K/V
+// tiles are brought in by a fifth warp with tiled bulk copies (TMA): the ring
+// is described as a 2-D tensor [slot][K face | V face], a tile of 16 positions
+// is 16 boxes of 64 elements x 16 rows with the 128-byte swizzle, which is the
+// XOR pattern ldmatrix wants. The consumers issue no copy instructions and meet
+// the producer only on mbarriers (no CTA-wide barrier in the loop). Tiles that
+// cannot hold the row the preceding kernel appends are requested before the
+// dependency wait. Waits are bounded; a timeout raises the engine status word.
+constexpr int TMA_TP = 16;                    // positions per tile
+constexpr int TMA_BOX_B = TMA_TP * 128;       // one box: 16 rows x 64 fp16
+constexpr int TMA_NW = 4;
+constexpr int TMA_STAGE_B = 2 * TMA_NW * 2 * TMA_BOX_B;   // K,V x heads x halves = 32 KB
+constexpr int TMA_STAGES = 3;
+constexpr uint32_t TMA_SPIN = 4u * 1000u * 1000u;
+constexpr unsigned int kStatusAttnTimeout = 0x80000002u;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < TMA_SPIN; it++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void ldsm_x4_s(uint32_t (&r)[4], uint32_t s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_t_s(uint32_t (&r)[4], uint32_t s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
+__global__ void __launch_bounds__((TMA_NW + 1) * 32)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, AttnDecodeArgs A, uint32_t kv_heads_total) {
+    constexpr int HD = 128, DBLK = HD / 8, KSTEPS = HD / 16, NW = TMA_NW, TP = TMA_TP;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + TMA_STAGES * TMA_STAGE_B);     // full[STAGES], empty[STAGES]
+    const uint32_t full0 = s_u32(bars), empty0 = s_u32(bars + TMA_STAGES);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t rep = A.rep;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        for (int s = 0; s < TMA_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full0 + 8 * s), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * s), "r"(NW));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // The position counter of this state is advanced by the merge kernel of the
+    // previous step, not by the kernel right before this one: it may be read now.
+    const uint32_t n_kv = A.counter ? *A.counter + A.n_kv_add : A.n_kv;
+    const uint32_t n_groups = kv_heads_total / NW;
+    const uint32_t grp = blockIdx.x % n_groups, split = blockIdx.x / n_groups;   // groups fastest: neighbours share ring rows
+    uint32_t per = (n_kv + A.nsplit - 1) / A.nsplit;
+    per = (per + TP - 1) / TP * TP;
+    const uint32_t pb = split * per;
+    const uint32_t pe = pb + per < n_kv ? pb + per : n_kv;
+    const uint32_t kv_elems = A.kv_heads * HD;
+    const int ntiles = pe > pb ? (int)((pe - pb + TP - 1) / TP) : 0;
+
+    if (warp == NW) {
+        // ---- producer
+        if (lane == 0) {
+            bool waited = false;
+            int tile = 0;
+            for (; tile < ntiles; tile++) {
+                const uint32_t p0 = pb + tile * TP;
+                // the row appended by the preceding kernel is position n_kv - 1
+                if (!waited && p0 + TP >= n_kv) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+                const int s = tile % TMA_STAGES;
+                if (!mbar_wait_bounded(empty0 + 8 * s, ((tile / TMA_STAGES) & 1) ^ 1)) { raise_status(A.status, kStatusAttnTimeout); break; }
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * s), "r"(TMA_STAGE_B) : "memory");
+                const uint32_t dst = s_u32(smem + (size_t)s * TMA_STAGE_B);
+#pragma unroll
+                for (int b = 0; b < 2 * NW * 2; b++) {      // b = (kv * NW + head) * 2 + half
+                    const int kv = b / (NW * 2), head = (b >> 1) % NW, half = b & 1;
+                    const int x = (int)(kv * kv_elems + (grp * NW + head) * HD + half * 64);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                        ::"r"(dst + b * TMA_BOX_B), "l"(&tmap), "r"(full0 + 8 * s), "r"(x), "r"((int)p0) : "memory");
+                }
+            }
+            // requested copies must have landed before the CTA may go away
+            for (int j = tile > TMA_STAGES ? tile - TMA_STAGES : 0; j < tile; j++)
+                mbar_wait_bounded(full0 + 8 * (j % TMA_STAGES), (j / TMA_STAGES) & 1);
+            if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+        }
+        return;
+    }
+
+    // ---- consumers: warp = KV head of the group
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t kvh = grp * NW + warp;
+    uint32_t qa[KSTEPS][4];
+    float o[DBLK][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    {
+        const uint16_t* q0 = A.q + ((size_t)kvh * rep + g) * HD;
+        const uint16_t* q1 = A.q + ((size_t)kvh * rep + g + 8) * HD;
+#pragma unroll
+        for (int j = 0; j < KSTEPS; j++) {
+            qa[j][0] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t) : 0u;
+            qa[j][1] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t) : 0u;
+            qa[j][2] = (uint32_t)g < rep ? *(const uint32_t*)(q0 + 16 * j + 2 * t + 8) : 0u;
+            qa[j][3] = (uint32_t)(g + 8) < rep ? *(const uint32_t*)(q1 + 16 * j + 2 * t + 8) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < DBLK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    }
+    const uint16_t* maskp = A.mask ? A.mask + (size_t)(kvh / A.kvh_per_seq) * A.mask_seq_stride : nullptr;
+    // per-lane ldmatrix offsets inside a box (row stride 128 B, chunk XOR row & 7)
+    const int mat = lane >> 3, r8 = lane & 7;
+    const int krow = (mat >> 1) * 8 + r8, vrow = (mat & 1) * 8 + r8;
+    const uint32_t smem0 = s_u32(smem);
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int s = tile % TMA_STAGES;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(full0 + 8 * s, (tile / TMA_STAGES) & 1))) {
+            raise_status(A.status, kStatusAttnTimeout);
+            break;
+        }
+        const uint32_t sk = smem0 + s * TMA_STAGE_B + (warp * 2) * TMA_BOX_B;            // K boxes of this head
+        const uint32_t sv = smem0 + s * TMA_STAGE_B + ((NW + warp) * 2) * TMA_BOX_B;     // V boxes
+        const uint32_t pw0 = pb + tile * TP;
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int j = 0; j < KSTEPS; j++) {
+            uint32_t kb[4];
+            const int ch = (j & 3) * 2 + (mat & 1);
+            ldsm_x4_s(kb, sk + (j >> 2) * TMA_BOX_B + krow * 128 + ((ch ^ (krow & 7)) << 4));
+            mma_f16(sc[0], qa[j], kb[0], kb[1]);
+            mma_f16(sc[1], qa[j], kb[2], kb[3]);
+        }
+        float x[2][4];
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t p = pw0 + nb * 8 + 2 * t + (c & 1);
+                float v = -INFINITY;
+                if (p < pe) {
+                    float mk = maskp ? __half2float(__ushort_as_half(maskp[p])) : 0.0f;
+                    v = chain_score(sc[nb][c], A.scale, A.scale_div, mk);
+                }
+                x[nb][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            }
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            float m_new = fmaxf(m_run[h], mx[h]);
+            alpha[h] = (m_new == -INFINITY) ? 1.0f : __expf(m_run[h] - m_new);
+            m_run[h] = m_new;
+            l_run[h] *= alpha[h];
+        }
+        uint32_t pa[4];
+        {
+            float pv[2][4];
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    float mr = m_run[c >> 1];
+                    float e = (mr == -INFINITY) ? 0.0f : __expf(x[nb][c] - mr);
+                    pv[nb][c] = e;
+                    l_run[c >> 1] += e;
+                }
+            pa[0] = pack_h2(pv[0][0], pv[0][1]);
+            pa[1] = pack_h2(pv[0][2], pv[0][3]);
+            pa[2] = pack_h2(pv[1][0], pv[1][1]);
+            pa[3] = pack_h2(pv[1][2], pv[1][3]);
+        }
+        if (alpha[0] != 1.0f || alpha[1] != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < DBLK; i++) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
+        }
+#pragma unroll
+        for (int dp = 0; dp < DBLK / 2; dp++) {
+            uint32_t vb[4];
+            const int ch = (dp & 3) * 2 + (mat >> 1);
+            ldsm_x4_t_s(vb, sv + (dp >> 2) * TMA_BOX_B + vrow * 128 + ((ch ^ (vrow & 7)) << 4));
+            mma_f16(o[dp * 2], pa, vb[0], vb[1]);
+            mma_f16(o[dp * 2 + 1], pa, vb[2], vb[3]);
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+    }
+    // this warp's (head, split) partial, straight from registers (empty slices leave max = -inf, sum = 0)
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* po = A.part_o + ((size_t)kvh * A.nsplit + split) * rep * HD;
+    float* pml = A.part_ml + ((size_t)kvh * A.nsplit + split) * rep * 2;
+#pragma unroll
+    for (int i = 0; i < DBLK; i++) {
+        int d = i * 8 + 2 * t;
+        if ((uint32_t)g < rep) *(float2*)(po + (size_t)g * HD + d) = make_float2(o[i][0], o[i][1]);
+        if ((uint32_t)(g + 8) < rep) *(float2*)(po + (size_t)(g + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+    }
+    if (t == 0) {
+        if ((uint32_t)g < rep) { pml[g * 2] = m_run[0]; pml[g * 2 + 1] = l_run[0]; }
+        if ((uint32_t)(g + 8) < rep) { pml[(g + 8) * 2] = m_run[1]; pml[(g + 8) * 2 + 1] = l_run[1]; }
+    }
+}
+
 // out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}.
 // One CTA of 4 warps per query head: warp w takes chunks w, w+4, ... (all its
 // loads are independent, so they overlap), lanes split head_dim; the four warp
@@ -564,10 +788,62 @@ size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_
     return (size_t)kv_heads_total * nsplit * rep * (hd + 2);
 }
 
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn attn_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Tensor map of a KV ring: [nslots][K face | V face] fp16, boxes of 64 elements x 16 slots, 128-byte swizzle.
+const CUtensorMap* ring_tensor_map(const uint16_t* ring, uint32_t nslots, uint32_t kv_elems, bool no_cache) {
+    static std::map<std::tuple<const void*, uint32_t, uint32_t>, CUtensorMap> cache;
+    static thread_local CUtensorMap tm;
+    auto key = std::make_tuple((const void*)ring, nslots, kv_elems);
+    if (!no_cache) {
+        auto it = cache.find(key);
+        if (it != cache.end()) return &it->second;
+    }
+    EncodeTiledFn enc = attn_encode_fn();
+    if (!enc || ((uintptr_t)ring & 15) || (kv_elems % 64) || !nslots) return nullptr;
+    cuuint64_t dims[2] = {(cuuint64_t)2 * kv_elems, nslots};
+    cuuint64_t strides[1] = {(cuuint64_t)2 * kv_elems * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)TMA_TP};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)ring, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    if (no_cache) return &tm;
+    if (cache.size() > 4096) cache.clear();
+    return &(cache[key] = tm);
+}
+}  // namespace
+
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out, uint32_t kv_heads_total) {
     if (a.rep == 0 || a.rep > 16 || (hd != 128 && hd != 64)) return false;
     if (!a.nsplit) return false;
     if (hd == 128 && kv_heads_total % 4 == 0) {
+        if (const CUtensorMap* tm = ring_tensor_map(a.ring, a.nslots, a.kv_heads * hd, a.no_cache != 0)) {
+            const size_t tsmem = 1024 + (size_t)TMA_STAGES * TMA_STAGE_B + 2 * TMA_STAGES * sizeof(uint64_t);
+            static bool tattr = false;
+            if (!tattr) { cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem); tattr = true; }
+            launch_pdl(attn_decode_tma_kernel, dim3((kv_heads_total / 4) * a.nsplit), dim3((TMA_NW + 1) * 32), tsmem, st, *tm, a, kv_heads_total);
+            launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
+                       (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, 16u);
+            g_launches += 2;
+            return true;
+        }
         size_t gsmem = (size_t)3 * 2 * 4 * 16 * hd * 2;
         uint32_t ggrid = (kv_heads_total / 4) * a.nsplit;
         static bool gattr = false;
@@ -654,6 +930,7 @@ extern "C" int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* 
     a.scale = scale; a.scale_div = 0; a.rep = rep; a.kv_heads = kv_heads; a.nslots = nslots; a.nsplit = nsplit;
     a.part_o = scratch_of_device[dev];
     a.part_ml = a.part_o + (size_t)kv_heads * nsplit * rep * head_dim;
+    a.no_cache = 1;
     if (!k_attn_decode((cudaStream_t)stream, a, head_dim, out_dev, kv_heads)) return fail("attn noalloc: launch refused");
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
