@@ -29,9 +29,12 @@ struct Planner {
     bool build;
     uint32_t opi = 0;
     bool written[kMaxTemps];
-    uint32_t cap[kMaxTemps], last[kMaxTemps];
+    // 64-bit: a temp that only exists inside a fused chain may exceed the 4 GB a
+    // materialised temp is limited to (e.g. the GQA-expanded K/V faces at batch 64)
+    uint64_t cap[kMaxTemps], last[kMaxTemps];
     // measuring walk results
-    uint32_t maxb[kMaxTemps];
+    uint64_t maxb[kMaxTemps];
+    bool oversize[kMaxTemps];
     std::vector<LiveRange> live[kMaxTemps];
     // building walk inputs
     uint8_t* addr[kMaxTemps];
@@ -80,12 +83,17 @@ struct Planner {
     uint32_t ref_count(uint32_t arg) const {
         if (arg & 0x8000u) { uint32_t s = arg & 0x7FFFu; return s < b->n_slots ? b->slots[s].count : 0; }
         if (arg & 0x4000u) return 0;
-        return arg < kMaxTemps ? last[arg] / 2u : 0;
+        return arg < kMaxTemps ? (uint32_t)(last[arg] / 2u) : 0;
     }
     // temp_get, oplist_exec.c:257-335
     uint8_t* temp_get(uint32_t id, uint64_t bytes64, PlanOp& p) {
-        if (id >= kMaxTemps || bytes64 > 0xFFFFFFFFull) return nullptr;
-        uint32_t bytes = (uint32_t)bytes64;
+        if (id >= kMaxTemps || bytes64 > (1ull << 40)) return nullptr;
+        // Above 4 GB (the reference's temp sizes are 32-bit) only as a temp that fusion removes.
+        if (bytes64 > 0xFFFFFFFFull) {
+            if (!build) oversize[id] = true;
+            else if (!internal[id]) return nullptr;
+        }
+        const uint64_t bytes = bytes64;
         bool vt = g.vtcm_off[id] != kNoOff, stc = !vt && g.have_static && g.static_off[id] != kNoOff;
         if (vt && (uint64_t)g.vtcm_off[id] + bytes > g.vtcm_cap) return nullptr;
         if (stc && (!build || in_static[id]) && (uint64_t)g.static_off[id] + bytes > g.static_cap) return nullptr;
@@ -94,7 +102,7 @@ struct Planner {
         last[id] = bytes;
         written[id] = true;
         for (int k = 0; k < 2; k++)
-            if (p.out_id[k] == kNoOff || p.out_id[k] == id) { p.out_id[k] = id; p.out_bytes[k] = bytes; break; }
+            if (p.out_id[k] == kNoOff || p.out_id[k] == id) { p.out_id[k] = id; p.out_bytes[k] = (uint32_t)(bytes > 0xFFFFFFFFull ? 0xFFFFFFFFull : bytes); break; }
         if (!build) {
             if (bytes > maxb[id]) maxb[id] = bytes;
             live[id].push_back({opi, opi});
@@ -801,6 +809,7 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     reset_walk(false);
     std::memset(P.maxb, 0, sizeof P.maxb);
     std::memset(P.internal, 0, sizeof P.internal);
+    std::memset(P.oversize, 0, sizeof P.oversize);
     std::vector<PlanOp> meas(b->n_ops);
     for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; P.cur = &meas[i]; plan_op(P, b->ops[i], meas[i]); }
     const bool fusing = g.opt_fuse && !g.force_unfused;
