@@ -26,6 +26,7 @@ struct PlanOp {
     int rc = 0;                 // non-zero: the op fails when reached, with `err`
     std::string err;
     std::function<void(cudaStream_t)> launch;
+    std::function<void(cudaStream_t)> launch_local;   // tensor parallel: the op without the all-reduce of its output
     uint32_t engine = WT_ENG_SCALAR;
     uint32_t out_id[2] = {kNoOff, kNoOff};   // temps written, for last-bytes tracking
     uint32_t out_bytes[2] = {0, 0};
@@ -140,6 +141,8 @@ int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
 bool tp_p2p_ready();
 bool tp_p2p_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
 void tp_p2p_shutdown();
+bool tp_p2p_add_rmsnorm(cudaStream_t st, const uint16_t* a, uint16_t* r, const uint16_t* g, const uint16_t* b,
+                        uint16_t* sum_out, uint16_t* y, uint32_t rows, uint32_t width);
 // fuse.cu
 void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal);
 void fuse_materialize(const wt_blob* b);

@@ -298,6 +298,9 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
     std::vector<uint8_t> taken(b->n_ops, 0);
     auto claim = [&](Span& sp) {
         for (uint32_t o : sp.ops) if (taken[o] || meas[o].rc) return false;
+        // an op whose output is all-reduced over the ranks keeps its own launch (the reduction hangs on it)
+        if (g.tp_world > 1)
+            for (uint32_t o : sp.ops) if (o < g_allreduce_after.size() && g_allreduce_after[o]) return false;
         for (uint32_t o : sp.ops) taken[o] = 1;
         g_spans.push_back(sp);
         return true;
@@ -398,6 +401,30 @@ void fuse_materialize(const wt_blob* b) {
             if (!rw || sp.n % rw) continue;
             uint32_t rows = sp.n / rw;
             head.fused = [=](cudaStream_t st) { k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw); };
+            // Tensor parallel: when the addend is the partial sum of the row-parallel
+            // projection right before the ADD, projection + all-reduce + add + norm run
+            // as two launches: the projection, then one kernel that exchanges the rows
+            // with the peers, adds them and normalises.
+            if (g.tp_world > 1 && tp_p2p_ready() && sp.first > 0) {
+                PlanOp& lin = g.plan[sp.first - 1];
+                const bool b_is_partial = is_temp_ref(sp.add_b) && lin.out_id[0] == sp.add_b;
+                const bool a_is_partial = is_temp_ref(sp.add_a) && lin.out_id[0] == sp.add_a;
+                if (lin.launch_local && !lin.fused && !lin.rc && !lin.uses_internal && (a_is_partial != b_is_partial) &&
+                    lin.out_bytes[0] == sp.n * 2u) {
+                    auto local = lin.launch_local;
+                    const uint16_t* res = b_is_partial ? aa : ab;
+                    uint16_t* part = (uint16_t*)(b_is_partial ? ab : aa);
+                    lin.fused = [=](cudaStream_t st) {
+                        local(st);
+                        if (!tp_p2p_add_rmsnorm(st, res, part, gam, bet, sum, y, rows, rw)) {
+                            tp_allreduce_f16(st, part, (size_t)rows * rw);
+                            k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw);
+                        }
+                    };
+                    lin.span = 3;
+                    g.fused_ops += 1;
+                }
+            }
         }
         head.span = sp.count;
         g.fused_ops += sp.count;

@@ -4,15 +4,12 @@
 // exec_kv_append / exec_kv_gather (:2154-2231) over the ring of kvcache.c.
 #include "common.cuh"
 #include "launchers.h"
+#include "norm_row.cuh"
 
 namespace gehtp {
 
 // ------------------------------------------------------------- RMSNorm
-// One CTA per row. Sum of squares in double, rms = float(sqrt(acc/n + 1e-6)),
-// then x / rms, * gamma, + beta, each rounded separately in fp32, one fp16
-// rounding at the end. When `r` is given the row is f16(a + r) first (the
-// residual add that precedes the norm in a decoder block) and that sum is
-// also stored to sum_out.
+// One CTA per row (norm_row.cuh).
 template <int BLOCK>
 __global__ void rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ r,
                                const uint16_t* __restrict__ g, const uint16_t* __restrict__ b,
@@ -24,57 +21,7 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* _
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t base = (size_t)blockIdx.x * width;
-    double acc = 0.0;
-    if ((width & 7u) == 0 && ((((uintptr_t)a) | ((uintptr_t)r) | ((uintptr_t)sum_out)) & 15u) == 0) {
-        // 8 values per 16-byte load
-        for (uint32_t i = threadIdx.x * 8; i < width; i += BLOCK * 8) {
-            uint4 qa = *(const uint4*)(a + base + i), qr = make_uint4(0, 0, 0, 0), qs;
-            if (r) qr = *(const uint4*)(r + base + i);
-            const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wr[4] = {qr.x, qr.y, qr.z, qr.w};
-            uint32_t ws[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                float v0 = h2f((uint16_t)(wa[k] & 0xffffu)), v1 = h2f((uint16_t)(wa[k] >> 16));
-                if (r) {
-                    uint16_t s0 = f2h(__fadd_rn(v0, h2f((uint16_t)(wr[k] & 0xffffu))));
-                    uint16_t s1 = f2h(__fadd_rn(v1, h2f((uint16_t)(wr[k] >> 16))));
-                    ws[k] = (uint32_t)s0 | ((uint32_t)s1 << 16);
-                    v0 = h2f(s0); v1 = h2f(s1);
-                }
-                row[i + 2 * k] = v0;
-                row[i + 2 * k + 1] = v1;
-                acc += (double)v0 * (double)v0;
-                acc += (double)v1 * (double)v1;
-            }
-            if (r && sum_out) { qs = make_uint4(ws[0], ws[1], ws[2], ws[3]); *(uint4*)(sum_out + base + i) = qs; }
-        }
-    } else {
-        for (uint32_t i = threadIdx.x; i < width; i += BLOCK) {
-            float v = h2f(a[base + i]);
-            if (r) {
-                uint16_t s = f2h(__fadd_rn(v, h2f(r[base + i])));
-                if (sum_out) sum_out[base + i] = s;
-                v = h2f(s);
-            }
-            row[i] = v;
-            acc += (double)v * (double)v;
-        }
-    }
-    acc = warp_sum_d(acc);
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        double t = 0.0;
-        for (int w = 0; w < BLOCK / 32; w++) t += part[w];
-        s_rms = (float)sqrt(t / (double)width + 1e-6);
-    }
-    __syncthreads();
-    const float rms = s_rms;
-    for (uint32_t i = threadIdx.x; i < width; i += BLOCK) {
-        float v = __fdiv_rn(row[i], rms);
-        v = __fadd_rn(__fmul_rn(v, h2f(g[i])), b ? h2f(b[i]) : 0.0f);
-        y[base + i] = f2h(v);
-    }
+    rmsnorm_row<BLOCK>(a + base, r ? r + base : nullptr, g, b, sum_out ? sum_out + base : nullptr, y + base, width, row, part, &s_rms);
 }
 
 void k_add_rmsnorm(cudaStream_t st, const uint16_t* a, const uint16_t* r, const uint16_t* g,

@@ -871,6 +871,7 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
             void* buf = P.addr[p.out_id[0]];
             size_t elems = p.out_bytes[0] / 2;
             auto inner = p.launch;
+            p.launch_local = inner;
             p.launch = [=](cudaStream_t st) { inner(st); tp_allreduce_f16(st, buf, elems); };
         }
     // run-time temp table starts empty; addresses appear as ops execute

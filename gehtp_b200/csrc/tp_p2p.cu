@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "engine.h"
 #include "launchers.h"
+#include "norm_row.cuh"
 
 namespace gehtp {
 
@@ -121,9 +122,94 @@ p2p_allreduce_kernel(P2PCtx c, const uint4* in, uint4* out, uint32_t vecs) {   /
     }
 }
 
+// All-reduce of the addend `r` fused with the residual add and the RMSNorm that
+// follow a row-parallel projection: one CTA per row pushes its row of partial
+// sums to every mailbox, waits for the peers' rows (flag index = row), adds them
+// in rank order, stores the reduced row back to `r`, and normalises
+// f16(a + r) as rmsnorm_kernel does.
+template <int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+p2p_add_rmsnorm_kernel(P2PCtx c, const uint16_t* a, uint16_t* r, const uint16_t* __restrict__ g,
+                       const uint16_t* __restrict__ b, uint16_t* sum_out, uint16_t* y, uint32_t width) {
+    extern __shared__ float row[];  // width floats
+    __shared__ double part[BLOCK / 32];
+    __shared__ float s_rms;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t epoch = c.epoch[0] + 1, bank = epoch & 1u;
+    const size_t base = (size_t)blockIdx.x * width;
+    const uint32_t vecs = width / 8, v0 = (uint32_t)(base / 8);
+    // push
+    for (uint32_t v = threadIdx.x; v < vecs; v += BLOCK) {
+        const uint4 x = *(const uint4*)(r + base + 8 * v);
+        for (int p = 0; p < c.world; p++) ((uint4*)slot_ptr(c.box[p], bank, c.rank))[v0 + v] = x;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < (uint32_t)c.world) {
+        uint32_t* f = flag_ptr(c.box[threadIdx.x], bank, c.rank, blockIdx.x);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+        // wait
+        const uint32_t* fw = flag_ptr(c.box[c.rank], bank, (int)threadIdx.x, blockIdx.x);
+        uint32_t seen = 0, it = 0;
+        for (; it < kSpinLimit; it++) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(fw) : "memory");
+            if ((int32_t)(seen - epoch) >= 0) break;
+            __nanosleep(32);
+        }
+        if (it == kSpinLimit) raise_status(c.status, kStatusTimeout);
+    }
+    __syncthreads();
+    // sum in rank order, back into r
+    for (uint32_t v = threadIdx.x; v < vecs; v += BLOCK) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+        for (int q = 0; q < c.world; q++) {
+            const uint4 x = __ldcg((const uint4*)slot_ptr(c.box[c.rank], bank, q) + v0 + v);
+            const __half2* h = (const __half2*)&x;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(h[i]);
+                acc[2 * i] += f.x;
+                acc[2 * i + 1] += f.y;
+            }
+        }
+        uint4 o;
+        uint32_t* ow = (uint32_t*)&o;
+#pragma unroll
+        for (int i = 0; i < 4; i++) ow[i] = (uint32_t)f2h(acc[2 * i]) | ((uint32_t)f2h(acc[2 * i + 1]) << 16);
+        *(uint4*)(r + base + 8 * v) = o;
+    }
+    __syncthreads();     // the row of r is complete (and visible to this CTA) before the norm reads it
+    rmsnorm_row<BLOCK>(a + base, r + base, g, b, sum_out ? sum_out + base : nullptr, y + base, width, row, part, &s_rms);
+    // last CTA of the launch publishes the epoch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&c.epoch[1], 1u) == gridDim.x - 1) {
+            c.epoch[1] = 0;
+            __threadfence();
+            c.epoch[0] = epoch;
+        }
+    }
+}
+
 }  // namespace
 
 bool tp_p2p_ready() { return p2p.ready; }
+
+// y = rmsnorm(f16(a + allreduce(r))) with the reduced r and the sum stored too;
+// false when the shape does not fit the mailbox (the caller then runs the
+// all-reduce and the norm as two launches).
+bool tp_p2p_add_rmsnorm(cudaStream_t st, const uint16_t* a, uint16_t* r, const uint16_t* g, const uint16_t* b,
+                        uint16_t* sum_out, uint16_t* y, uint32_t rows, uint32_t width) {
+    if (!p2p.ready || !rows || rows > (uint32_t)kMaxCtas || (width & 7u) || (size_t)rows * width * 2 > kSlotBytes) return false;
+    if ((((uintptr_t)a) | ((uintptr_t)r) | ((uintptr_t)sum_out) | ((uintptr_t)y)) & 15u) return false;
+    launch_pdl(p2p_add_rmsnorm_kernel<256>, dim3(rows), dim3(256), width * sizeof(float), st, p2p.ctx, a, r, g, b, sum_out, y, width);
+    g_launches++;
+    return true;
+}
 
 // In-place all-reduce of `elems` fp16 values; false when the vector does not
 // fit the mailbox or is not 16-byte sized/aligned (the caller then uses NCCL).
