@@ -25,6 +25,7 @@ UNITS = {
     "ops_gdn.cu": ["--fmad=false"],
     "ops_attn.cu": [],
     "ops_attn_decode.cu": [],
+    "ops_attn_prefill.cu": [],
     "ops_fused.cu": [],
     "ops_matmul.cu": [],
     "ops_w4a16.cu": [],

@@ -18,6 +18,8 @@
 // (run_range pieces, dump hooks) makes the engine rebuild the plan unfused.
 #include <algorithm>
 #include <cstring>
+#include <map>
+#include <utility>
 #include "engine.h"
 #include "launchers_attn.h"
 
@@ -121,7 +123,7 @@ Rope match_rope(const Graph& G, int add_op) {
 }
 
 struct Span {
-    int kind;                // 0 attention, 1 swiglu, 2 add+norm
+    int kind;                // 0 decode attention, 1 swiglu, 2 add+norm, 3 rotary, 4 prefill attention
     uint32_t first, count;
     std::vector<uint32_t> ops;
     // attention
@@ -131,6 +133,9 @@ struct Span {
     uint32_t a_ref, wg, wu, y, M, K, N;
     // add+norm
     uint32_t add_a, add_b, sum_t, gamma_s, beta_s, norm_y, n;
+    // rotary on its own (kind 3): x, cos_q, sin_q, y, rows = M, hd
+    // prefill attention (kind 4): q/k/v inputs, mask operand (+ constant mask slot when known), ctx, seq_q = M, seq_k = N
+    uint32_t pq, pk, pv, mask_slot; bool mask_is_slot;
 };
 
 bool contiguous(std::vector<uint32_t>& ops, uint32_t& first) {
@@ -237,6 +242,78 @@ bool match_attention(const Graph& G, uint32_t ia, Span& sp) {
     return true;
 }
 
+// Standalone rotary chain ending in the ADD at `add_op`.
+bool match_rope_span(const Graph& G, uint32_t add_op, Span& sp) {
+    Rope r = match_rope(G, (int)add_op);
+    if (!r.ok || (r.hd & 3u)) return false;
+    std::vector<uint32_t> ops = r.ops;
+    uint32_t first;
+    if (!contiguous(ops, first) || ops.back() != add_op || !closed(G, ops, {add_op})) return false;
+    sp.kind = 3; sp.first = first; sp.count = (uint32_t)ops.size(); sp.ops = ops;
+    sp.a_ref = r.x; sp.cos_q = r.cos_b; sp.sin_q = r.sin_b; sp.y = G.b->ops[add_op].args[2]; sp.M = r.rows; sp.hd = r.hd;
+    return true;
+}
+
+// Prefill attention chain around the SOFTMAX at `ism`:
+//   TRANSPOSE_GEN q [S,nh,hd]->[nh,S,hd], k [Sk,kvh,hd]->[kvh,hd,Sk], v [Sk,kvh,hd]->[kvh,Sk,hd],
+//   MATMUL_F16 batched over kvh (rows = rep*S), BINARY scale by a broadcast constant, ADD mask,
+//   SOFTMAX, MATMUL_F16 batched with V, TRANSPOSE_GEN [nh,S,hd]->[S,nh,hd].
+bool match_prefill_attention(const Graph& G, uint32_t ism, Span& sp) {
+    const wt_blob* b = G.b;
+    if (ism < 3 || ism + 2 >= b->n_ops) return false;
+    const uint32_t j = ism - 3;
+    const wt_op &sc = b->ops[j], &bi = b->ops[j + 1], &ad = b->ops[j + 2], &sm = b->ops[j + 3], &pv = b->ops[j + 4], &ot = b->ops[j + 5];
+    if (sc.opcode != OP_MATMUL_F16 || bi.opcode != OP_BINARY_F16 || ad.opcode != OP_ADD_F16 || sm.opcode != OP_SOFTMAX_F16 ||
+        pv.opcode != OP_MATMUL_F16 || ot.opcode != OP_TRANSPOSE_GEN_F16) return false;
+    if ((sc.args[6] & 7u) != 4u || (pv.args[6] & 7u) != 4u) return false;
+    const uint32_t kvh = sc.args[6] >> 16, rows = sc.args[3], hd = sc.args[4], seq_k = sc.args[5];
+    if (!kvh || (pv.args[6] >> 16) != kvh || pv.args[3] != rows || pv.args[4] != seq_k || pv.args[5] != hd) return false;
+    if (hd != 128 && hd != 64) return false;
+    const int tq = G.producer_of_arg[0][j], tk = G.producer_of_arg[1][j], tv = G.producer_of_arg[1][j + 4];
+    if (tq < 0 || tk < 0 || tv < 0) return false;
+    const wt_op &oq = b->ops[tq], &ok = b->ops[tk], &ov = b->ops[tv];
+    auto tr = [](const wt_op& o, uint32_t d0, uint32_t d1, uint32_t d2, uint32_t perm) {
+        return o.opcode == OP_TRANSPOSE_GEN_F16 && o.args[2] == 3 && o.args[3] == d0 && o.args[4] == d1 && o.args[5] == d2 &&
+               (o.args[7] & 0xFFFFFFu) == perm;
+    };
+    if (oq.opcode != OP_TRANSPOSE_GEN_F16 || oq.args[2] != 3 || oq.args[5] != hd) return false;
+    const uint32_t seq_q = oq.args[3], nh = oq.args[4];
+    if (!seq_q || !nh || nh % kvh || (nh / kvh) * seq_q != rows) return false;
+    if (!tr(oq, seq_q, nh, hd, 1u | 0u << 8 | 2u << 16) || !tr(ok, seq_k, kvh, hd, 1u | 2u << 8 | 0u << 16) ||
+        !tr(ov, seq_k, kvh, hd, 1u | 0u << 8 | 2u << 16) || !tr(ot, nh, seq_q, hd, 1u | 0u << 8 | 2u << 16)) return false;
+    const uint64_t n_sc = (uint64_t)nh * seq_q * seq_k;
+    if (n_sc > 0xFFFFFFFFull) return false;
+    if (bi.args[0] != sc.args[2] || (bi.args[4] != 2 && bi.args[4] != 3) || bi.args[3] != (uint32_t)n_sc) return false;
+    if (ad.args[0] != bi.args[2] || ad.args[3] != (uint32_t)n_sc) return false;
+    if (sm.args[0] != ad.args[2] || sm.args[2] != nh * seq_q || sm.args[3] != seq_k) return false;
+    if (pv.args[0] != sm.args[1] || ot.args[0] != pv.args[2]) return false;
+    float scale;
+    if (!const_scalar(G, G.producer_of_arg[1][j + 1], scale)) return false;
+    // the mask operand: a [nh][S][Sk] tensor, or the broadcast over heads of a constant [S][Sk] slot
+    sp.mask_is_slot = false;
+    const int mb = G.producer_of_arg[1][j + 2];
+    if (mb >= 0 && b->ops[mb].opcode == OP_BROADCAST_F16) {
+        const wt_op& bo = b->ops[mb];
+        const uint32_t src = bo.args[0];
+        if ((src & 0x8000u) && (src & 0x7FFFu) < b->n_slots) {
+            const wt_slot& sl = b->slots[src & 0x7FFFu];
+            // in dims (1,1,S,Sk) -> out dims (1,nh,S,Sk)
+            if (sl.addr == 0 && sl.len == (uint64_t)seq_q * seq_k * 2u && bo.args[4] == 1 && bo.args[5] == 1 && bo.args[6] == seq_q &&
+                bo.args[7] == seq_k && bo.args[8] == 1 && bo.args[9] == nh && bo.args[10] == seq_q && bo.args[11] == seq_k) {
+                sp.mask_is_slot = true;
+                sp.mask_slot = src & 0x7FFFu;
+            }
+        }
+    }
+    std::vector<uint32_t> ops = {(uint32_t)tq, (uint32_t)tk, (uint32_t)tv, j, j + 1, j + 2, j + 3, j + 4, j + 5};
+    uint32_t first;
+    if (!contiguous(ops, first) || !closed(G, ops, {j + 5})) return false;
+    sp.kind = 4; sp.first = first; sp.count = (uint32_t)ops.size(); sp.ops = ops;
+    sp.pq = oq.args[0]; sp.pk = ok.args[0]; sp.pv = ov.args[0]; sp.mask = ad.args[1]; sp.ctx = ot.args[1];
+    sp.M = seq_q; sp.N = seq_k; sp.nh = nh; sp.kvh = kvh; sp.hd = hd; sp.scale = scale; sp.scale_div = bi.args[4] == 3;
+    return true;
+}
+
 bool match_swiglu(const Graph& G, uint32_t ip, Span& sp) {
     const wt_blob* b = G.b;
     const wt_op& pr = b->ops[ip];
@@ -273,6 +350,7 @@ bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
 
 std::vector<Span> g_spans;
 float* g_attn_scratch = nullptr;
+std::map<std::pair<uint32_t, uint64_t>, uint8_t*> g_skip_maps;   // (mask slot, S<<32|Sk) -> device tile-skip bitmap
 
 const uint8_t* resolve(const wt_blob* b, uint32_t arg) {
     if (arg & 0x8000u) {
@@ -308,6 +386,14 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
     for (uint32_t i = 0; i < b->n_ops; i++) {
         Span sp{};
         if (b->ops[i].opcode == OP_KV_APPEND_F16 && match_attention(G, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        Span sp{};
+        if (!taken[i] && b->ops[i].opcode == OP_SOFTMAX_F16 && match_prefill_attention(G, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        Span sp{};
+        if (!taken[i] && b->ops[i].opcode == OP_ADD_F16 && match_rope_span(G, i, sp)) claim(sp);
     }
     for (uint32_t i = 0; i < b->n_ops; i++) {
         Span sp{};
@@ -391,6 +477,45 @@ void fuse_materialize(const wt_blob* b) {
             const uint16_t *sg = wg->scales, *su = wu->scales;
             uint32_t M = sp.M, K = sp.K, N = sp.N;
             head.fused = [=](cudaStream_t st) { k_w4a16_skinny_swiglu(st, act, pg, sg, pu, su, y, M, K, N); };
+        } else if (sp.kind == 3) {
+            const uint16_t *x = (const uint16_t*)resolve(b, sp.a_ref), *ct = (const uint16_t*)resolve(b, sp.cos_q),
+                           *stb = (const uint16_t*)resolve(b, sp.sin_q);
+            uint16_t* y = (uint16_t*)resolve(b, sp.y);
+            if (!x || !ct || !stb || !y || ((((uintptr_t)x) | ((uintptr_t)ct) | ((uintptr_t)stb) | ((uintptr_t)y)) & 3u)) continue;
+            uint32_t rows = sp.M, hd = sp.hd;
+            head.fused = [=](cudaStream_t st) { k_rope(st, x, ct, stb, y, rows, hd); };
+        } else if (sp.kind == 4) {
+            const uint16_t *q = (const uint16_t*)resolve(b, sp.pq), *k = (const uint16_t*)resolve(b, sp.pk),
+                           *v = (const uint16_t*)resolve(b, sp.pv);
+            uint16_t* out = (uint16_t*)resolve(b, sp.ctx);
+            const uint16_t* mask = (const uint16_t*)resolve(b, sp.mask_is_slot ? (0x8000u | sp.mask_slot) : sp.mask);
+            if (!q || !k || !v || !out || !mask) continue;
+            uint32_t sq = sp.M, sk = sp.N, nh = sp.nh, kvh = sp.kvh, hd = sp.hd;
+            size_t mstride = sp.mask_is_slot ? 0 : (size_t)sq * sk;
+            const uint8_t* skip = nullptr;
+            if (sp.mask_is_slot) {
+                // tiles of the constant mask that are -inf everywhere are never computed
+                const uint32_t T = attn_prefill_tile(), nq = (sq + T - 1) / T, nk = (sk + T - 1) / T;
+                auto key = std::make_pair(sp.mask_slot, (uint64_t)sq << 32 | sk);
+                auto it = g_skip_maps.find(key);
+                if (it == g_skip_maps.end()) {
+                    const uint16_t* hm = (const uint16_t*)(b->weight_base + b->slots[sp.mask_slot].offset);
+                    std::vector<uint8_t> bm((size_t)nq * nk, 1);
+                    for (uint32_t r = 0; r < sq; r++)
+                        for (uint32_t c = 0; c < sk; c++)
+                            if (hm[(size_t)r * sk + c] != 0xFC00u) bm[(size_t)(r / T) * nk + c / T] = 0;
+                    uint8_t* d = nullptr;
+                    if (cudaMalloc(&d, bm.size()) == cudaSuccess) {
+                        cudaMemcpyAsync(d, bm.data(), bm.size(), cudaMemcpyHostToDevice, g.stream);
+                        cudaStreamSynchronize(g.stream);
+                        it = g_skip_maps.emplace(key, d).first;
+                    } else cudaGetLastError();
+                }
+                if (it != g_skip_maps.end()) skip = it->second;
+            }
+            float scale = sp.scale; int sdiv = sp.scale_div;
+            if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v)) & 15u) continue;
+            head.fused = [=](cudaStream_t st) { k_attn_prefill(st, q, k, v, mask, mstride, skip, scale, sdiv, sq, sk, nh, kvh, hd, out); };
         } else {
             const uint16_t *aa = (const uint16_t*)resolve(b, sp.add_a), *ab = (const uint16_t*)resolve(b, sp.add_b);
             uint16_t *sum = (uint16_t*)resolve(b, sp.sum_t), *y = (uint16_t*)resolve(b, sp.norm_y);
@@ -433,6 +558,8 @@ void fuse_materialize(const wt_blob* b) {
 
 void fuse_release() {
     if (g_attn_scratch) { cudaFree(g_attn_scratch); g_attn_scratch = nullptr; }
+    for (auto& kv : g_skip_maps) cudaFree(kv.second);
+    g_skip_maps.clear();
     g_spans.clear();
 }
 

@@ -38,4 +38,15 @@ void k_rope_kv_append(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_
                       uint32_t* posmap, const uint32_t* counter, uint32_t B, uint32_t nh, uint32_t kvh,
                       uint32_t hd, uint32_t nslots, uint32_t pos_const);
 
+// Prefill attention over token-major q [seq_q][nh][hd], k / v [seq_k][kvh][hd] -> out [seq_q][nh*hd]
+// (ops_attn_prefill.cu). `skip` marks (64-row query tile, 64-position key tile) pairs whose mask is -inf
+// everywhere, [ceil(seq_q/64)][ceil(seq_k/64)] bytes, or NULL. false: shape not handled, nothing launched.
+bool k_attn_prefill(cudaStream_t st, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* mask,
+                    size_t mask_head_stride, const uint8_t* skip, float scale, int scale_div, uint32_t seq_q,
+                    uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out);
+uint32_t attn_prefill_tile();
+// rotary embedding, split-half form, with the op chain's roundings: out = f16(f16(x*cos) + f16(rot(x)*sin))
+void k_rope(cudaStream_t st, const uint16_t* x, const uint16_t* cos_t, const uint16_t* sin_t, uint16_t* out,
+            uint32_t rows, uint32_t hd);
+
 }  // namespace gehtp

@@ -67,4 +67,40 @@ void k_rope_kv_append(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_
     g_launches++;
 }
 
+// Rotary embedding on its own (the same seven-op chain, without the split and
+// the append): x, cos, sin and out are [rows][hd].
+__global__ void rope_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ cos_t,
+                            const uint16_t* __restrict__ sin_t, uint16_t* __restrict__ out, uint32_t n, uint32_t hd) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t h = hd / 2;
+    // two elements per thread (d even): both read the same partner pair
+    for (uint32_t e = (blockIdx.x * blockDim.x + threadIdx.x) * 2; e < n; e += gridDim.x * blockDim.x * 2) {
+        const uint32_t d = e % hd;
+        const uint32_t pe = d < h ? e + h : e - h;
+        const uint32_t xv = *(const uint32_t*)(x + e), pv = *(const uint32_t*)(x + pe);
+        const uint32_t cv = *(const uint32_t*)(cos_t + e), sv = *(const uint32_t*)(sin_t + e);
+        uint16_t r[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const float xf = h2f((uint16_t)(xv >> (16 * k))), pf = h2f((uint16_t)(pv >> (16 * k)));
+            const float rot = d < h ? -pf : pf;
+            const float xc = h2f(f2h(__fmul_rn(xf, h2f((uint16_t)(cv >> (16 * k))))));
+            const float xs = h2f(f2h(__fmul_rn(rot, h2f((uint16_t)(sv >> (16 * k))))));
+            r[k] = f2h(__fadd_rn(xc, xs));
+        }
+        *(uint32_t*)(out + e) = (uint32_t)r[0] | ((uint32_t)r[1] << 16);
+    }
+}
+
+void k_rope(cudaStream_t st, const uint16_t* x, const uint16_t* cos_t, const uint16_t* sin_t, uint16_t* out,
+            uint32_t rows, uint32_t hd) {
+    const uint32_t n = rows * hd;
+    if (!n) return;
+    uint32_t grid = (n / 2 + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    launch_pdl(rope_kernel, dim3(grid), dim3(256), 0, st, x, cos_t, sin_t, out, n, hd);
+    g_launches++;
+}
+
 }  // namespace gehtp

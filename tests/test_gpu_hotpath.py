@@ -216,9 +216,12 @@ def test_fused_plan_survives_piecewise_and_hooked_runs(cuda):
     cuda.gehtp_cuda_set_graph(1)
 
 
-def test_prefill_runlist_matches_reference(cuda, ref):
+@pytest.mark.parametrize("seq", [48, 200])
+def test_prefill_runlist_matches_reference(cuda, ref, seq):
+    """Causal prefill (rotary and attention chains fused into their kernels) against the
+    reference executor on the same graph with dequantised weights; 200 tokens span
+    several 64-row tiles with a ragged last one and skipped (fully masked) tiles."""
     cfg = DecoderConfig(256, 2, 4, 2, 128, 512, 512, 1e6, "tiny")
-    seq = 48
     buf_w4, man = build_prefill_runlist(cfg, seq, seed=21, quant="w4")
     buf_f16, man2 = build_prefill_runlist(cfg, seq, seed=21, quant="f16")
     ids = (np.arange(seq, dtype=np.int32) * 37 + 11) % cfg.vocab
@@ -230,6 +233,16 @@ def test_prefill_runlist_matches_reference(cuda, ref):
         eng.shutdown()
     assert_fp16_close(outs[0], outs[1], "prefill logits")
     assert (outs[0].argmax(1) == outs[1].argmax(1)).mean() > 0.9
+    # 2 layers x (2 rotary chains of 7 ops + 1 attention chain of 9 ops) must have been replaced
+    assert cuda.gehtp_cuda_fused_ops() >= 2 * (2 * 7 + 9)
+    # and the op-by-op plan gives the same answer within the same gate
+    cuda.gehtp_cuda_set_fusion(0)
+    eng = Engine(cuda, buf_w4)
+    eng.run_io(ids, man["logits_temp"], None)
+    unfused = eng.temp(man["logits_temp"]).reshape(seq, -1).copy()
+    eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    assert_fp16_close(outs[0], unfused, "fused vs op-by-op prefill")
 
 
 def test_static_offset_table_and_alias_hazard(cuda, ref):
