@@ -87,6 +87,16 @@ def build(verbose=False, force=False):
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    # host runner (job.txt / request-file protocols of the reference's device-side runners)
+    run_src = os.path.join(CSRC, "host", "gehtp_run.cpp")
+    run_bin = os.path.join(os.path.dirname(OUT), "gehtp_run")
+    if force or _stale(run_src, run_bin) or os.path.getmtime(OUT) > os.path.getmtime(run_bin):
+        cmd = ["g++", "-O2", "-std=c++17", "-I" + os.path.join(ROOT, "include"), run_src, "-o", run_bin,
+               "-L" + os.path.dirname(OUT), "-lgehtp_cuda", "-Wl,-rpath,$ORIGIN", "-pthread"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+            raise RuntimeError("gehtp_run link failed")
     return OUT
 
 
