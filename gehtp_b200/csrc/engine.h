@@ -38,6 +38,7 @@ struct PlanOp {
     uint32_t span = 0;
     uint32_t stat = 0;          // index into the stats struct, 0 = none
     bool uses_internal = false; // touches a temp that has no memory in a fused plan
+    bool dead_when_fused = false;   // its result is read only by ops that fused chains replace: skipped in whole fused runs
 };
 
 struct W4Packed {
@@ -116,6 +117,7 @@ struct Engine {
 
     // options
     int opt_fuse = 1, opt_graph = 1, trace_on = 0;
+    bool skip_dead = false;       // set for the duration of a whole fused run
     bool force_unfused = false;   // a run needed an op that the fused plan gave no memory
     const char* hook_spec = nullptr;
     wt_op_ts* ts_buf = nullptr;
@@ -144,8 +146,9 @@ void tp_p2p_shutdown();
 bool tp_p2p_add_rmsnorm(cudaStream_t st, const uint16_t* a, uint16_t* r, const uint16_t* g, const uint16_t* b,
                         uint16_t* sum_out, uint16_t* y, uint32_t rows, uint32_t width);
 // fuse.cu
-void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal);
+void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal, std::vector<uint8_t>& dead);
 void fuse_materialize(const wt_blob* b);
+bool fuse_all_materialized();
 void fuse_release();
 
 }  // namespace gehtp

@@ -206,7 +206,7 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
             }
             if (!rc) {
                 if (use_fused) p.fused(g.stream);
-                else for (PlanOp* q : pending) if (q->launch) q->launch(g.stream);
+                else for (PlanOp* q : pending) if (q->launch && !(g.skip_dead && q->dead_when_fused)) q->launch(g.stream);
             }
             if (ev1) cudaEventRecord(ev1, g.stream);
             pending.clear();
@@ -341,7 +341,9 @@ static int run_impl(const wt_blob* b, uint32_t first, uint32_t count, const void
     const unsigned long long launches0 = g_launches;
     if (capture) { if (in_host) stage_inputs(b, in_host, nullptr); }
     else if (has_in) stage_inputs(b, in_host, in_dev);
+    g.skip_dead = whole && g.opt_fuse != 0 && !hooks_active();
     rc = queue_range(first, count, g.opt_fuse != 0, timing, engine_m, op_us, err, errn);
+    g.skip_dead = false;
     if (rc == kNeedUnfused) {
         // an op inside a fused chain has to run on its own: plan again with every temp in memory
         if (capture) { cudaGraph_t gr = nullptr; cudaStreamEndCapture(g.stream, &gr); if (gr) cudaGraphDestroy(gr); cudaGetLastError(); }

@@ -368,9 +368,10 @@ const uint8_t* resolve(const wt_blob* b, uint32_t arg) {
 
 // Finds the chains. `internal[t]` is set for temp ids written only inside
 // fused chains (and not among a chain's outputs): they need no memory.
-void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal) {
+void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal, std::vector<uint8_t>& dead) {
     g_spans.clear();
     internal.assign(kMaxTemps, 0);
+    dead.assign(b->n_ops, 0);
     Graph G;
     build_graph(b, meas, G);
     std::vector<uint8_t> taken(b->n_ops, 0);
@@ -421,6 +422,34 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
             (interior[i] ? writes_in : writes_out)[id]++;
         }
     for (uint32_t t = 0; t < kMaxTemps; t++) internal[t] = writes_in[t] > 0 && writes_out[t] == 0;
+
+    // Ops outside the chains whose results only the replaced ops read (the broadcast of
+    // the scale constant, a mask expanded over heads that the kernel takes unexpanded):
+    // dead when every chain runs fused.
+    std::vector<int> span_of(b->n_ops, -1);
+    for (size_t si = 0; si < g_spans.size(); si++)
+        for (uint32_t o : g_spans[si].ops) span_of[o] = (int)si;
+    auto span_reads = [&](const Span& sp, uint32_t t) {
+        switch (sp.kind) {
+        case 0: return t == sp.qkv || t == sp.cos_q || t == sp.sin_q || t == sp.cos_k || t == sp.sin_k || t == sp.mask;
+        case 1: return t == sp.a_ref;
+        case 2: return t == sp.add_a || t == sp.add_b;
+        case 3: return t == sp.a_ref || t == sp.cos_q || t == sp.sin_q;
+        case 4: return t == sp.pq || t == sp.pk || t == sp.pv || (!sp.mask_is_slot && t == sp.mask);
+        }
+        return true;
+    };
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        if (span_of[i] >= 0 || G.users[i].empty() || meas[i].rc) continue;
+        const uint32_t opc = b->ops[i].opcode;
+        if (opc != OP_BROADCAST_F16) continue;          // pure functions of their inputs only
+        const uint32_t t = meas[i].out_id[0];
+        if (t == kNoOff || meas[i].out_id[1] != kNoOff) continue;
+        bool all_dead = true;
+        for (uint32_t u : G.users[i])
+            if (span_of[u] < 0 || span_reads(g_spans[span_of[u]], t)) { all_dead = false; break; }
+        if (all_dead) dead[i] = 1;
+    }
 }
 
 // Bakes the fused launches into the plan (after addresses are known).
@@ -554,6 +583,12 @@ void fuse_materialize(const wt_blob* b) {
         head.span = sp.count;
         g.fused_ops += sp.count;
     }
+}
+
+bool fuse_all_materialized() {
+    for (const Span& sp : g_spans)
+        if (!g.plan[sp.first].fused || g.plan[sp.first].span != sp.count) return false;
+    return true;
 }
 
 void fuse_release() {

@@ -61,6 +61,25 @@ __device__ __forceinline__ void rmsnorm_row(const uint16_t* a, const uint16_t* r
     }
     __syncthreads();
     const float rms = *s_rms;
+    if ((width & 7u) == 0 && ((((uintptr_t)g) | ((uintptr_t)b) | ((uintptr_t)y)) & 15u) == 0) {
+        // 8 outputs per thread and step: one 16-byte load of gamma (and beta), one 16-byte store
+        for (uint32_t i = threadIdx.x * 8; i < width; i += BLOCK * 8) {
+            const uint4 qg = __ldg((const uint4*)(g + i));
+            uint4 qb = make_uint4(0, 0, 0, 0);
+            if (b) qb = __ldg((const uint4*)(b + i));
+            const uint32_t wg[4] = {qg.x, qg.y, qg.z, qg.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+            uint32_t wo[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                float v0 = __fdiv_rn(row[i + 2 * k], rms), v1 = __fdiv_rn(row[i + 2 * k + 1], rms);
+                v0 = __fadd_rn(__fmul_rn(v0, h2f((uint16_t)(wg[k] & 0xffffu))), b ? h2f((uint16_t)(wb[k] & 0xffffu)) : 0.0f);
+                v1 = __fadd_rn(__fmul_rn(v1, h2f((uint16_t)(wg[k] >> 16))), b ? h2f((uint16_t)(wb[k] >> 16)) : 0.0f);
+                wo[k] = (uint32_t)f2h(v0) | ((uint32_t)f2h(v1) << 16);
+            }
+            *(uint4*)(y + i) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        }
+        return;
+    }
     for (uint32_t i = threadIdx.x; i < width; i += BLOCK) {
         float v = __fdiv_rn(row[i], rms);
         v = __fadd_rn(__fmul_rn(v, h2f(g[i])), b ? h2f(b[i]) : 0.0f);

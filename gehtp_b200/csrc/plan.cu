@@ -813,9 +813,10 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     std::vector<PlanOp> meas(b->n_ops);
     for (uint32_t i = 0; i < b->n_ops; i++) { P.opi = i; P.cur = &meas[i]; plan_op(P, b->ops[i], meas[i]); }
     const bool fusing = g.opt_fuse && !g.force_unfused;
+    std::vector<uint8_t> dead_ops;
     if (fusing) {
         std::vector<uint8_t> internal;
-        fuse_analyze(b, meas, internal);
+        fuse_analyze(b, meas, internal, dead_ops);
         for (uint32_t i = 0; i < kMaxTemps; i++) P.internal[i] = internal[i] != 0;
     }
 
@@ -878,7 +879,12 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     for (uint32_t i = 0; i < kMaxTemps; i++) g.temp_dev[i] = P.addr[i];
 
     g.fused_ops = 0;
-    if (fusing) fuse_materialize(b);
+    if (fusing) {
+        fuse_materialize(b);
+        // only when every chain really got its kernel: a chain left op-by-op still reads those results
+        if (fuse_all_materialized())
+            for (uint32_t i = 0; i < b->n_ops && i < dead_ops.size(); i++) g.plan[i].dead_when_fused = dead_ops[i] != 0;
+    }
     cudaError_t ce = cudaStreamSynchronize(g.stream);
     if (ce != cudaSuccess) { std::snprintf(err, errn, "plan upload: %s", cudaGetErrorString(ce)); return -1; }
     g.blob = b; g.blob_wbase = b->weight_base; g.blob_nops = b->n_ops; g.blob_nslots = b->n_slots;
