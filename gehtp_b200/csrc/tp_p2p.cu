@@ -33,7 +33,9 @@ constexpr int kMaxCtas = 64;
 constexpr size_t kSlotBytes = 1u << 20;                       // per source rank and bank
 constexpr size_t kDataBytes = 2 * kMaxWorld * kSlotBytes;
 constexpr size_t kFlagBytes = 2 * kMaxWorld * kMaxCtas * sizeof(uint32_t);
-constexpr size_t kBoxBytes = kDataBytes + kFlagBytes;
+constexpr size_t kLLSlotBytes = 1u << 20;                     // flag-in-data slots: 8 bytes per 4 payload bytes
+constexpr size_t kLLBytes = 2 * kMaxWorld * kLLSlotBytes;
+constexpr size_t kBoxBytes = kDataBytes + kFlagBytes + kLLBytes;
 constexpr uint32_t kSpinLimit = 4u * 1000u * 1000u;           // polls (with a short sleep) before giving up
 constexpr unsigned int kStatusTimeout = 0x80000001u;
 
@@ -57,6 +59,10 @@ __device__ __forceinline__ unsigned char* slot_ptr(unsigned char* box, uint32_t 
 }
 __device__ __forceinline__ uint32_t* flag_ptr(unsigned char* box, uint32_t bank, int src, uint32_t cta) {
     return (uint32_t*)(box + kDataBytes) + ((size_t)bank * kMaxWorld + src) * kMaxCtas + cta;
+}
+
+__device__ __forceinline__ uint2* ll_slot_ptr(unsigned char* box, uint32_t bank, int src) {
+    return (uint2*)(box + kDataBytes + kFlagBytes + ((size_t)bank * kMaxWorld + src) * kLLSlotBytes);
 }
 
 // vecs: number of 16-byte vectors of the fp16 vector.
@@ -123,11 +129,16 @@ p2p_allreduce_kernel(P2PCtx c, const uint4* in, uint4* out, uint32_t vecs) {   /
 }
 
 // All-reduce of the addend `r` fused with the residual add and the RMSNorm that
-// follow a row-parallel projection: one CTA per row pushes its row of partial
-// sums to every mailbox, waits for the peers' rows (flag index = row), adds them
-// in rank order, stores the reduced row back to `r`, and normalises
-// f16(a + r) as rmsnorm_kernel does.
-template <int BLOCK>
+// follow a row-parallel projection. One CTA per row. The exchange carries its
+// flag inside the data: every 32-bit word of the row travels as an 8-byte
+// {word, epoch} pair written with one store (8-byte stores arrive whole), into
+// slot [epoch parity][my rank] of every peer's mailbox; the receiver polls the
+// pairs of its own mailbox until each carries the epoch. No fence and no
+// separate flag round trip: the exchange costs one NVLink write latency. The
+// words are added in rank order in fp32 (every rank gets the same bits), the
+// reduced row is stored back to `r`, and f16(a + r) is normalised as in
+// rmsnorm_kernel. Polls are bounded; a peer that never writes raises the status word.
+template <int BLOCK, int WPT>
 __global__ void __launch_bounds__(BLOCK)
 p2p_add_rmsnorm_kernel(P2PCtx c, const uint16_t* a, uint16_t* r, const uint16_t* __restrict__ g,
                        const uint16_t* __restrict__ b, uint16_t* sum_out, uint16_t* y, uint32_t width) {
@@ -138,48 +149,67 @@ p2p_add_rmsnorm_kernel(P2PCtx c, const uint16_t* a, uint16_t* r, const uint16_t*
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t epoch = c.epoch[0] + 1, bank = epoch & 1u;
     const size_t base = (size_t)blockIdx.x * width;
-    const uint32_t vecs = width / 8, v0 = (uint32_t)(base / 8);
-    // push
-    for (uint32_t v = threadIdx.x; v < vecs; v += BLOCK) {
-        const uint4 x = *(const uint4*)(r + base + 8 * v);
-        for (int p = 0; p < c.world; p++) ((uint4*)slot_ptr(c.box[p], bank, c.rank))[v0 + v] = x;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < (uint32_t)c.world) {
-        uint32_t* f = flag_ptr(c.box[threadIdx.x], bank, c.rank, blockIdx.x);
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
-        // wait
-        const uint32_t* fw = flag_ptr(c.box[c.rank], bank, (int)threadIdx.x, blockIdx.x);
-        uint32_t seen = 0, it = 0;
-        for (; it < kSpinLimit; it++) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(fw) : "memory");
-            if ((int32_t)(seen - epoch) >= 0) break;
-            __nanosleep(32);
-        }
-        if (it == kSpinLimit) raise_status(c.status, kStatusTimeout);
-    }
-    __syncthreads();
-    // sum in rank order, back into r
-    for (uint32_t v = threadIdx.x; v < vecs; v += BLOCK) {
-        float acc[8];
+    const uint32_t words = width / 2;
+    const size_t w0 = (size_t)blockIdx.x * words;
+    uint32_t* rw = (uint32_t*)(r + base);
+    uint32_t mine[WPT];
+    // push this rank's words to every peer
 #pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-        for (int q = 0; q < c.world; q++) {
-            const uint4 x = __ldcg((const uint4*)slot_ptr(c.box[c.rank], bank, q) + v0 + v);
-            const __half2* h = (const __half2*)&x;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 f = __half22float2(h[i]);
-                acc[2 * i] += f.x;
-                acc[2 * i + 1] += f.y;
+    for (int j = 0; j < WPT; j++) {
+        const uint32_t w = threadIdx.x + j * BLOCK;
+        mine[j] = w < words ? rw[w] : 0u;
+        if (w < words)
+            for (int p = 0; p < c.world; p++) {
+                if (p == c.rank) continue;
+                uint2* dst = ll_slot_ptr(c.box[p], bank, c.rank) + w0 + w;
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(mine[j]), "r"(epoch) : "memory");
             }
-        }
-        uint4 o;
-        uint32_t* ow = (uint32_t*)&o;
+    }
+    // collect the peers' words: all loads of a sweep are issued before any is tested
+    uint32_t got[kMaxWorld][WPT];
+    uint32_t pending = 0;      // bit q * WPT + j
 #pragma unroll
-        for (int i = 0; i < 4; i++) ow[i] = (uint32_t)f2h(acc[2 * i]) | ((uint32_t)f2h(acc[2 * i + 1]) << 16);
-        *(uint4*)(r + base + 8 * v) = o;
+    for (int q = 0; q < kMaxWorld; q++)
+#pragma unroll
+        for (int j = 0; j < WPT; j++) {
+            got[q][j] = 0u;
+            if (q < c.world && q != c.rank && threadIdx.x + j * BLOCK < words) pending |= 1u << (q * WPT + j);
+        }
+    for (uint32_t it = 0; pending && it < kSpinLimit; it++) {
+        uint2 v[kMaxWorld][WPT];
+#pragma unroll
+        for (int q = 0; q < kMaxWorld; q++)
+#pragma unroll
+            for (int j = 0; j < WPT; j++)
+                if (pending & (1u << (q * WPT + j))) {
+                    const uint2* src = ll_slot_ptr(c.box[c.rank], bank, q) + w0 + threadIdx.x + j * BLOCK;
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[q][j].x), "=r"(v[q][j].y) : "l"(src) : "memory");
+                }
+#pragma unroll
+        for (int q = 0; q < kMaxWorld; q++)
+#pragma unroll
+            for (int j = 0; j < WPT; j++)
+                if ((pending & (1u << (q * WPT + j))) && v[q][j].y == epoch) {
+                    got[q][j] = v[q][j].x;
+                    pending &= ~(1u << (q * WPT + j));
+                }
+        if (pending && it > 64) __nanosleep(64);
+    }
+    if (pending) raise_status(c.status, kStatusTimeout);
+    // sum in rank order, back into r
+#pragma unroll
+    for (int j = 0; j < WPT; j++) {
+        const uint32_t w = threadIdx.x + j * BLOCK;
+        if (w >= words) continue;
+        float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+        for (int q = 0; q < kMaxWorld; q++) {
+            if (q >= c.world) break;
+            const uint32_t x = q == c.rank ? mine[j] : got[q][j];
+            lo += h2f((uint16_t)(x & 0xffffu));
+            hi += h2f((uint16_t)(x >> 16));
+        }
+        rw[w] = (uint32_t)f2h(lo) | ((uint32_t)f2h(hi) << 16);
     }
     __syncthreads();     // the row of r is complete (and visible to this CTA) before the norm reads it
     rmsnorm_row<BLOCK>(a + base, r + base, g, b, sum_out ? sum_out + base : nullptr, y + base, width, row, part, &s_rms);
@@ -204,9 +234,12 @@ bool tp_p2p_ready() { return p2p.ready; }
 // all-reduce and the norm as two launches).
 bool tp_p2p_add_rmsnorm(cudaStream_t st, const uint16_t* a, uint16_t* r, const uint16_t* g, const uint16_t* b,
                         uint16_t* sum_out, uint16_t* y, uint32_t rows, uint32_t width) {
-    if (!p2p.ready || !rows || rows > (uint32_t)kMaxCtas || (width & 7u) || (size_t)rows * width * 2 > kSlotBytes) return false;
+    if (!p2p.ready || !rows || (width & 7u) || (size_t)rows * width * 4 > kLLSlotBytes || width > 2 * 512 * 4) return false;
     if ((((uintptr_t)a) | ((uintptr_t)r) | ((uintptr_t)sum_out) | ((uintptr_t)y)) & 15u) return false;
-    launch_pdl(p2p_add_rmsnorm_kernel<256>, dim3(rows), dim3(256), width * sizeof(float), st, p2p.ctx, a, r, g, b, sum_out, y, width);
+    if (width <= 2 * 512 * 2)
+        launch_pdl(p2p_add_rmsnorm_kernel<512, 2>, dim3(rows), dim3(512), width * sizeof(float), st, p2p.ctx, a, r, g, b, sum_out, y, width);
+    else
+        launch_pdl(p2p_add_rmsnorm_kernel<512, 4>, dim3(rows), dim3(512), width * sizeof(float), st, p2p.ctx, a, r, g, b, sum_out, y, width);
     g_launches++;
     return true;
 }
