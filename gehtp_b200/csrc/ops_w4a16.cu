@@ -186,7 +186,7 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
 enum { WALK_ANY = 0, WALK_FULL = 1, WALK_ONE = 2 };
 
 template <int MT, int UNROLL, bool DUAL, int WALK>
-__global__ void __launch_bounds__(640)
+__global__ void __launch_bounds__(MT >= 4 ? 512 : 640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
                     const uint16_t* __restrict__ sc2, uint16_t* __restrict__ y, uint32_t M,
@@ -265,15 +265,22 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
             b[i][1] = ld_ordered(ap + 1);
         }
     };
-    load_act(bc, 0);
+    // MT <= 2: the next group's activations are requested one group ahead; wider
+    // row tiles (MT = 4) have no registers for that and load them at their use.
+    constexpr bool PRE = MT <= 2;
+    if (PRE) load_act(bc, 0);
     const uint32_t last = kg1 - kg0 - 1;
     auto batch = [&](uint32_t relb, bool more) {   // groups relb .. relb+UNROLL-1
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             if (!FULL && relb + u > last) break;
-            uint4 bn[MT][2];
-            const bool have_next = u + 1 < UNROLL || !ONE;
-            if (have_next) load_act(bn, ONE ? (uint32_t)(u + 1) : min(relb + u + 1, last));
+            uint4 bn[PRE ? MT : 1][2];
+            const bool have_next = PRE && (u + 1 < UNROLL || !ONE);
+            if (PRE) {
+                if (have_next) load_act(*(uint4(*)[MT][2])&bn, ONE ? (uint32_t)(u + 1) : min(relb + u + 1, last));
+            } else {
+                load_act(bc, ONE ? (uint32_t)u : relb + u);
+            }
             uint32_t af[4][4];
             dequant_word(wq[u].x, af[0]);
             dequant_word(wq[u].y, af[1]);
@@ -296,7 +303,7 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
             if (!ONE && more && (FULL || relb + UNROLL + u <= last)) fetch(u, relb + UNROLL + u);
             if (have_next) {
 #pragma unroll
-                for (int i = 0; i < MT; i++) {
+                for (int i = 0; i < (PRE ? MT : 1); i++) {
                     bc[i][0] = bn[i][0];
                     bc[i][1] = bn[i][1];
                 }
@@ -334,10 +341,26 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
     }
 }
 
-static uint32_t skinny_kgw(uint32_t KG) {
-    uint32_t kgw = 8;
-    while ((KG + kgw - 1) / kgw > 20) kgw += 8;
-    return kgw;
+// k groups per warp (a multiple of 8). Default 8 (one register batch per warp,
+// the widest split of K). When that many warps per CTA would leave the strips
+// unable to be resident together (a long K with few columns: register-limited
+// to one CTA per SM and more strips than SMs), warps take more batches instead,
+// so that the whole grid is one wave.
+static uint32_t skinny_kgw(uint32_t KG, uint32_t strips) {
+    uint32_t fallback = 0;
+    for (uint32_t kgw = 8; kgw <= 256; kgw += 8) {
+        const uint32_t nw = (KG + kgw - 1) / kgw;
+        if (nw > 20) continue;
+        if (!fallback) fallback = kgw;
+        const uint32_t threads = nw * 32;
+        uint32_t per_sm = 2048 / threads;
+        const uint32_t by_regs = 65536 / (80 * threads);
+        if (by_regs < per_sm) per_sm = by_regs;
+        if (per_sm > 32) per_sm = 32;
+        if (per_sm && strips <= 148 * per_sm) return kgw;
+        if (kgw >= 32) break;
+    }
+    return fallback ? fallback : 8;
 }
 
 #define SKINNY_ARGS(P1, S1, P2, S2) a, (const uint4*)(P1), S1, (const uint4*)(P2), (const uint16_t*)(S2), y, M, K, N, kgw, ep
@@ -346,21 +369,26 @@ void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, 
                     uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep) {
     if (!M || !N || !K) return;
     const uint32_t KG = K / 64;
-    const uint32_t kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    const uint32_t kgw = skinny_kgw(KG, N / 16), nwarps = (KG + kgw - 1) / kgw;
     const dim3 block(nwarps * 32);
     if (M <= 8) {
         const dim3 grid(N / 16, 1);
         const size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
         if (kgw == 8 && KG % 8 == 0)
             launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ONE>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
-        else if (kgw % 8 == 0 && KG % kgw == 0)
+        else if (kgw % 8 == 0 && KG % 8 == 0)
             launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_FULL>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
         else
             launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
-    } else {
+    } else if (M <= 16 || nwarps > 16) {
         const dim3 grid(N / 16, (M + 15) / 16);
         const size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
         launch_pdl(w4a16_skinny_kernel<2, 4, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+    } else {
+        // 32 rows per CTA: the strip is dequantised once per 32 rows instead of once per 16
+        const dim3 grid(N / 16, (M + 31) / 32);
+        const size_t smem = (size_t)nwarps * 16 * 32 * sizeof(float);
+        launch_pdl(w4a16_skinny_kernel<4, 4, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     }
     g_launches++;
 }
@@ -371,7 +399,7 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
                            uint32_t N) {
     if (!M || !N || !K) return;
     const uint32_t KG = K / 64;
-    uint32_t kgw = skinny_kgw(KG), nwarps = (KG + kgw - 1) / kgw;
+    uint32_t kgw = skinny_kgw(KG, 0xFFFFFFFFu), nwarps = (KG + kgw - 1) / kgw;
     W4Epilogue ep;
     if (M <= 8) {
         const dim3 grid(N / 16, 1);

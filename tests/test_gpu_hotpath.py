@@ -147,7 +147,7 @@ def run_decode(lib, buf, man, cfg, steps, fuse=None, graph=None, tokens=None):
     return logits, toks
 
 
-@pytest.mark.parametrize("B", [1, 3])
+@pytest.mark.parametrize("B", [1, 3, 20])      # 20 rows: the two-row-tile forms of the GEMV and of the dual SwiGLU GEMV
 def test_decode_runlist_matches_reference(cuda, ref, B):
     """A decoder decode runlist (W4A16 weights) on the GPU, fused and op-by-op,
     against the same graph with dequantised weights on the reference executor."""
