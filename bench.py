@@ -44,7 +44,7 @@ def parse_args():
                          "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "headline", "attn", "attn8", "norm", "prefill", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -345,6 +345,12 @@ def run_micro(which):
         us, _, flops = w4(8192, 2560, 9728, 2, n=8)
         out.append({"kernel": "w4a16_gemm_tcgen05", "M": 8192, "K": 2560, "N": 9728, "us": us, "TFLOPs": flops / us / 1e6,
                     "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
+    if which == "gemmtiles":   # the tile configurations of the tcgen05 GEMM side by side (path 3 / 4 / 5)
+        for (M, K, N) in ((2048, 2560, 9728), (4096, 2560, 9728), (8192, 2560, 9728), (8192, 9728, 2560), (8192, 2560, 6144)):
+            for path, name in ((3, "128x128"), (4, "256x128"), (5, "256x256")):
+                us, _, flops = w4(M, K, N, path, n=8)
+                out.append({"kernel": "w4a16_gemm_tcgen05", "tile": name, "M": M, "K": K, "N": N, "us": us,
+                            "TFLOPs": flops / us / 1e6, "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
     if which == "gemm1":    # one mid-size GEMM: a small case for profiler captures
         M, K, N = 2048, 2560, 9728
         us, _, flops = w4(M, K, N, 2, n=4)

@@ -39,9 +39,9 @@ int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y
     const uint16_t* sc = (const uint16_t*)(dslot.as<uint8_t>() + nb);
     W4Epilogue ep;
     bool done = false;
-    if (path == 2 || (path == 0 && M >= 128)) {
-        done = k_w4a16_gemm_sm100(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep);
-        if (!done && path == 2) return fail("tcgen05 GEMM does not take this shape");
+    if (path >= 2 || (path == 0 && M >= 128)) {   // 2: tile by shape; 3, 4, 5: 128x128, 256x128, 256x256 tiles
+        done = k_w4a16_gemm_sm100(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep, path >= 3 ? path - 2 : 0);
+        if (!done && path >= 2) return fail("tcgen05 GEMM does not take this shape");
     }
     if (!done) k_w4a16_skinny(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep);
     cudaMemcpyAsync(y_f16, dy.p, (size_t)M * N * 2, cudaMemcpyDeviceToHost, g.stream);
@@ -117,15 +117,16 @@ int gehtp_dev_w4_repack(const uint8_t* slot_dev, uint32_t* packed_dev, uint32_t 
     return 0;
 }
 
-// path: 0 = engine's choice by M, 1 = streaming kernel, 2 = tcgen05 GEMM
+// path: 0 = engine's choice by M, 1 = streaming kernel, 2 = tcgen05 GEMM (tile by shape), 3 / 4 / 5 = tcgen05 GEMM
+// with 128x128 / 256x128 / 256x256 tiles
 int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
                            uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N, int path) {
     if (!ensure_device(nullptr, 0)) return -1;
     if (!M || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
     W4Epilogue ep;
-    if (path == 2 || (path == 0 && M >= 128)) {
-        if (k_w4a16_gemm_sm100(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep)) return 0;
-        if (path == 2) return fail("tcgen05 GEMM does not take this shape");
+    if (path >= 2 || (path == 0 && M >= 128)) {
+        if (k_w4a16_gemm_sm100(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep, path >= 3 ? path - 2 : 0)) return 0;
+        if (path >= 2) return fail("tcgen05 GEMM does not take this shape");
     }
     k_w4a16_skinny(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep);
     return 0;

@@ -43,9 +43,10 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
                            uint32_t N);
 // tcgen05 / TMEM form for M >= 128 (w4a16_gemm_sm100.cu). Returns false when
 // the shape is outside what it handles (the caller then uses the skinny form).
+// `tile`: 0 = chosen from the shape, 1 = 128x128, 2 = 256x128, 3 = 256x256 (N % 256 == 0).
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,
                         const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
-                        const W4Epilogue& ep);
+                        const W4Epilogue& ep, int tile = 0);
 
 // CTAs of the tcgen05 GEMM that gave up on a barrier since the process started (0 in a healthy run).
 unsigned int w4a16_gemm_timeouts();

@@ -15,8 +15,8 @@
 //                scales with bulk copies into an RSTAGES-deep ring.
 //   warp 3     : owns the TMEM allocation.
 //   warps 4-7  : epilogue (tcgen05.ld -> fp16 -> 64-byte row segments).
-//   warps 8-23 : dequant, four groups of four warps; group q takes every fourth
-//                k block. A warp turns two strip units (32 columns) into fp16 with
+//   warps 8-23 : dequant, one group of four warps per operand stage (the 3-stage
+//                configuration leaves four warps idle). A warp turns its strip units into fp16 with
 //                the magic-number trick, multiplies by the group scale and stores
 //                16-byte chunks into the stage's B tile in the 128B-swizzled
 //                K-major form tcgen05.mma reads.
@@ -32,14 +32,36 @@ namespace gehtp {
 
 namespace {
 
-constexpr int BN = 128, BK = 64;
-constexpr int STAGES = 4;          // A/B operand ring
-constexpr int RSTAGES = 6;         // int4 + scale ring
-constexpr int HALF_A_BYTES = 128 * BK * 2, B_BYTES = BN * BK * 2;
-constexpr int RAW_BYTES = BN * BK / 2, RAW_SLOT = RAW_BYTES + BN * 2;   // nibbles + 128 fp16 scales
+constexpr int BK = 64;
+constexpr int MAX_STAGES = 4;      // A/B operand ring (depth per configuration below)
+constexpr int RSTAGES_MAX = 4;     // int4 + scale ring
+constexpr int HALF_A_BYTES = 128 * BK * 2;
 constexpr int NTHREADS = 768;
 constexpr int DQ_PER_STAGE = 4, EPI_WARPS = 4;   // 16 dequant warps, 4 of them per k block
 constexpr uint32_t SPIN_LIMIT = 2u * 1000u * 1000u;   // try_wait polls before a role gives up
+
+// Tile configuration: MH row halves of 128 x BN columns per tile.
+//   <1,128>: 128x128, 4 stages, two accumulator buffers   (small M, or N not a multiple of 256)
+//   <2,128>: 256x128, 4 stages, two accumulator buffers
+//   <2,256>: 256x256, 3 stages, one accumulator buffer (all 512 TMEM columns): per FLOP it reads
+//            45 % fewer operand bytes from L2 and a third fewer from shared memory than 256x128;
+//            the epilogue is not overlapped (a few % of a K >= 2048 main loop).
+template <int MH, int BN>
+struct Cfg {
+    static constexpr int STAGES = (MH == 2 && BN == 256) ? 3 : 4;
+    static constexpr int NBUF = (MH * BN == 512) ? 1 : 2;
+    // One dequant group (4 warps) per operand stage, and one int4/scale slot per group: group q only
+    // ever waits on stage q and slot q, so it sees every phase of those barriers in turn. (A parity
+    // wait is only sound when the waiter has seen the phase before the one it waits for.)
+    static constexpr int GROUPS = STAGES;
+    static constexpr int RSTAGES = STAGES;
+    static constexpr int A_BYTES = MH * HALF_A_BYTES, B_BYTES = BN * BK * 2;
+    static constexpr int RAW_BYTES = BN * BK / 2, RAW_SLOT = RAW_BYTES + BN * 2;   // nibbles + BN fp16 scales
+    static constexpr uint32_t ACC_COLS = MH * BN;             // TMEM columns of one accumulator buffer
+    static constexpr uint32_t TMEM_COLS = NBUF * ACC_COLS;    // 256 or 512: a power of two
+    // instruction descriptor, kind::f16: A,B fp16 K-major, D fp32, M128 x N = BN
+    static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -88,14 +110,11 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return d;
 }
 
-// instruction descriptor, kind::f16: A,B fp16 K-major, D fp32, M128 N128
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
         " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -124,8 +143,8 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 slo, __half2 sh
 }
 
 struct __align__(8) Barriers {
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES];
-    uint64_t raw_full[RSTAGES], raw_empty[RSTAGES];
+    uint64_t full_a[MAX_STAGES], full_b[MAX_STAGES], empty[MAX_STAGES];
+    uint64_t raw_full[RSTAGES_MAX], raw_empty[RSTAGES_MAX];
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base, abort_flag;
 };
@@ -141,14 +160,15 @@ __device__ __forceinline__ uint32_t pack_out_res(float a, float b, uint32_t res)
     return (uint32_t)f2h(__fadd_rn(h2f(f2h(a)), ra)) | ((uint32_t)f2h(__fadd_rn(h2f(f2h(b)), rb)) << 16);
 }
 
-template <int MH>
+template <int MH, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4* __restrict__ wp,
                         const uint16_t* __restrict__ sc, uint16_t* __restrict__ y, uint32_t M, uint32_t K,
                         uint32_t N, W4Epilogue ep) {
-    constexpr int A_BYTES = MH * HALF_A_BYTES;
-    constexpr uint32_t ACC_COLS = MH * 128;          // TMEM columns of one accumulator buffer
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;     // 256 or 512: a power of two
+    using C = Cfg<MH, BN>;
+    constexpr int STAGES = C::STAGES, RSTAGES = C::RSTAGES, NBUF = C::NBUF;
+    constexpr int A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES, RAW_BYTES = C::RAW_BYTES, RAW_SLOT = C::RAW_SLOT;
+    constexpr uint32_t ACC_COLS = C::ACC_COLS, TMEM_COLS = C::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t KG = K / BK, NB = N / 16;
@@ -169,7 +189,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             mbar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < RSTAGES; s++) { mbar_init(&bars->raw_full[s], 1); mbar_init(&bars->raw_empty[s], DQ_PER_STAGE); }
-        for (int s = 0; s < 2; s++) { mbar_init(&bars->tmem_full[s], 1); mbar_init(&bars->tmem_empty[s], EPI_WARPS); }
+        for (int s = 0; s < NBUF; s++) { mbar_init(&bars->tmem_full[s], 1); mbar_init(&bars->tmem_empty[s], EPI_WARPS); }
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -198,15 +218,15 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                 }
             }
             if (*abort_flag)   // copies already requested must land before the CTA may go away
-                for (uint32_t j = it > STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&bars->full_a[j % STAGES], (j / STAGES) & 1);
+                for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&bars->full_a[j % STAGES], (j / STAGES) & 1);
         }
     } else if (warp == 1) {
         // ---- MMA issue
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, t++) {
-                const uint32_t buf = t & 1;
-                if (!mbar_wait(&bars->tmem_empty[buf], ((t >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
+                const uint32_t buf = t % NBUF;
+                if (!mbar_wait(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1)) { *abort_flag = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + buf * ACC_COLS;
                 for (uint32_t kb = 0; kb < KG; kb++, it++) {
@@ -219,7 +239,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                         const uint64_t db = umma_desc(b0 + k4 * 32);
 #pragma unroll
                         for (int h = 0; h < MH; h++)
-                            umma_f16(acc + h * 128, umma_desc(a0 + h * HALF_A_BYTES + k4 * 32), db, (kb | k4) ? 1u : 0u);
+                            umma_f16(acc + h * BN, umma_desc(a0 + h * HALF_A_BYTES + k4 * 32), db, C::IDESC, (kb | k4) ? 1u : 0u);
                     }
                     umma_commit(&bars->empty[s]);
                 }
@@ -245,17 +265,17 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                 }
             }
             if (*abort_flag)
-                for (uint32_t j = it > RSTAGES ? it - RSTAGES : 0; j < it; j++) mbar_wait(&bars->raw_full[j % RSTAGES], (j / RSTAGES) & 1);
+                for (uint32_t j = it > (uint32_t)RSTAGES ? it - RSTAGES : 0; j < it; j++) mbar_wait(&bars->raw_full[j % RSTAGES], (j / RSTAGES) & 1);
         }
     } else if (warp >= 4 && warp < 8) {
         // ---- epilogue: TMEM lane = output row; a warp may touch lanes (warp % 4) * 32 .. +31
         const uint32_t lane_base = (warp & 3) * 32;
         uint32_t t = 0;
         for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, t++) {
-            const uint32_t buf = t & 1;
+            const uint32_t buf = t % NBUF;
             const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
             bool ok = !__any_sync(0xffffffffu, *abort_flag != 0);
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[buf], (t >> 1) & 1));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[buf], (t / NBUF) & 1));
             if (!ok) { *abort_flag = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -264,7 +284,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
 #pragma unroll 1
                 for (uint32_t c = 0; c < BN / 32; c++) {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem + (lane_base << 16) + buf * ACC_COLS + h * 128 + c * 32;
+                    const uint32_t taddr = tmem + (lane_base << 16) + buf * ACC_COLS + h * BN + c * 32;
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -303,59 +323,71 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             if (lane == 0) mbar_arrive(&bars->tmem_empty[buf]);
         }
     } else if (warp >= 8) {
-        // ---- dequant: 16 warps in 4 groups; group q takes the k blocks with it % 4 == q, and
-        // warp j of a group turns strip units 2j, 2j+1 (32 columns) of that block into fp16.
-        // A warp so has four k-block periods for its two units, and pays one proxy fence for both.
+        // ---- dequant: one group of 4 warps per operand stage; group q takes the k blocks with
+        // it % STAGES == q, and warp j of a group turns strip units UPW*j .. UPW*j+UPW-1 (BN/4
+        // columns) of that block into fp16, two units at a time. A warp so has STAGES k-block
+        // periods for its share, and pays one proxy fence for all of it.
+        constexpr int UPW = BN / 64;       // strip units per warp and k block: 2 or 4
+        constexpr int GROUPS = C::GROUPS;
         const uint32_t dw = warp - 8, q = dw >> 2, j = dw & 3, g = lane >> 2, t = lane & 3;
         const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t total = my_tiles * KG;
         const uint32_t sB_u32 = smem_u32(sB), sRaw_u32 = smem_u32(sRaw);
-        uint32_t off[2][4];     // byte offsets of this lane's four 16-byte chunks inside a B stage, per unit
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-            const uint32_t r0 = (2 * j + u) * 16 + g, r1 = r0 + 8;
-            // row r, 16-byte chunk c (8 k) lives at r*128 + ((c ^ (r & 7)) << 4)
-            off[u][0] = r0 * 128 + (((2 * t) ^ (r0 & 7)) << 4);
-            off[u][1] = r0 * 128 + (((2 * t + 1) ^ (r0 & 7)) << 4);
-            off[u][2] = r1 * 128 + (((2 * t) ^ (r1 & 7)) << 4);
-            off[u][3] = r1 * 128 + (((2 * t + 1) ^ (r1 & 7)) << 4);
+        // byte offsets of this lane's four 16-byte chunks inside unit 0 of a B stage; a unit is 16 rows = 2048 bytes:
+        // row r, 16-byte chunk c (8 k) lives at r*128 + ((c ^ (r & 7)) << 4), and r & 7 does not depend on the unit
+        uint32_t off[4];
+        {
+            const uint32_t r0 = g, r1 = g + 8;
+            off[0] = r0 * 128 + (((2 * t) ^ (r0 & 7)) << 4);
+            off[1] = r0 * 128 + (((2 * t + 1) ^ (r0 & 7)) << 4);
+            off[2] = r1 * 128 + (((2 * t) ^ (r1 & 7)) << 4);
+            off[3] = r1 * 128 + (((2 * t + 1) ^ (r1 & 7)) << 4);
         }
-        for (uint32_t it = q; it < total; it += 4) {
-            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-            const uint32_t r = it % RSTAGES, rph = (it / RSTAGES) & 1;
+        for (uint32_t it = q; q < (uint32_t)GROUPS && it < total; it += GROUPS) {
+            const uint32_t s = q, ph = (it / STAGES) & 1;      // it % STAGES == q
+            const uint32_t r = q, rph = ph;
             // warp-uniform decisions: every lane polls, the warp leaves together
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->raw_full[r], rph))) { *abort_flag = 1; break; }
             const uint32_t raw = sRaw_u32 + r * RAW_SLOT;
-            uint4 w[2];
-            uint16_t sl[2], sh[2];
+            uint4 w[UPW];
+            uint16_t sl[UPW], sh[UPW];
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const uint32_t unit = 2 * j + u;
+            for (int u = 0; u < UPW; u++) {
+                const uint32_t unit = UPW * j + u;
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                              : "=r"(w[u].x), "=r"(w[u].y), "=r"(w[u].z), "=r"(w[u].w) : "r"(raw + (unit * 32 + lane) * 16));
                 asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sl[u]) : "r"(raw + RAW_BYTES + (unit * 16 + g) * 2));
                 asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sh[u]) : "r"(raw + RAW_BYTES + (unit * 16 + g + 8) * 2));
             }
-            uint32_t o[2][4][4];
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const __half2 slo = __half2half2(__ushort_as_half(sl[u])), shi = __half2half2(__ushort_as_half(sh[u]));
-                dequant_word(w[u].x, slo, shi, o[u][0]);
-                dequant_word(w[u].y, slo, shi, o[u][1]);
-                dequant_word(w[u].z, slo, shi, o[u][2]);
-                dequant_word(w[u].w, slo, shi, o[u][3]);
-            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->raw_empty[r]);      // the slot has been consumed into registers
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ph ^ 1))) { *abort_flag = 1; break; }
+            bool stage_free = false;
             const uint32_t bt = sB_u32 + s * B_BYTES;
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][0]), "r"(o[u][0][0]), "r"(o[u][0][2]), "r"(o[u][1][0]), "r"(o[u][1][2]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][1]), "r"(o[u][2][0]), "r"(o[u][2][2]), "r"(o[u][3][0]), "r"(o[u][3][2]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][2]), "r"(o[u][0][1]), "r"(o[u][0][3]), "r"(o[u][1][1]), "r"(o[u][1][3]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + off[u][3]), "r"(o[u][2][1]), "r"(o[u][2][3]), "r"(o[u][3][1]), "r"(o[u][3][3]) : "memory");
+            for (int up = 0; up < UPW; up += 2) {
+                uint32_t o[2][4][4];
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const __half2 slo = __half2half2(__ushort_as_half(sl[up + u])), shi = __half2half2(__ushort_as_half(sh[up + u]));
+                    dequant_word(w[up + u].x, slo, shi, o[u][0]);
+                    dequant_word(w[up + u].y, slo, shi, o[u][1]);
+                    dequant_word(w[up + u].z, slo, shi, o[u][2]);
+                    dequant_word(w[up + u].w, slo, shi, o[u][3]);
+                }
+                if (!stage_free) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ph ^ 1))) { *abort_flag = 1; break; }
+                    stage_free = true;
+                }
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const uint32_t ub = bt + (UPW * j + up + u) * 2048;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ub + off[0]), "r"(o[u][0][0]), "r"(o[u][0][2]), "r"(o[u][1][0]), "r"(o[u][1][2]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ub + off[1]), "r"(o[u][2][0]), "r"(o[u][2][2]), "r"(o[u][3][0]), "r"(o[u][3][2]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ub + off[2]), "r"(o[u][0][1]), "r"(o[u][0][3]), "r"(o[u][1][1]), "r"(o[u][1][3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(ub + off[3]), "r"(o[u][2][1]), "r"(o[u][2][3]), "r"(o[u][3][1]), "r"(o[u][3][3]) : "memory");
+                }
             }
+            if (!stage_free) break;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->full_b[s]);
@@ -387,13 +419,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int MH>
+template <int MH, int BN>
 bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, const uint16_t* sc, uint16_t* y,
             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms) {
-    const size_t smem = 1024 + (size_t)STAGES * (MH * HALF_A_BYTES + B_BYTES) + (size_t)RSTAGES * RAW_SLOT + sizeof(Barriers) + 16;
+    using C = Cfg<MH, BN>;
+    const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + (size_t)C::RSTAGES * C::RAW_SLOT + sizeof(Barriers) + 16;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(w4a16_gemm_sm100_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(w4a16_gemm_sm100_kernel<MH, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return false;
         }
@@ -401,7 +434,7 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     }
     const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN);
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    w4a16_gemm_sm100_kernel<MH><<<grid, NTHREADS, smem, st>>>(tmap, (const uint4*)packed, sc, y, M, K, N, ep);
+    w4a16_gemm_sm100_kernel<MH, BN><<<grid, NTHREADS, smem, st>>>(tmap, (const uint4*)packed, sc, y, M, K, N, ep);
     g_launches++;
     return true;
 }
@@ -415,8 +448,8 @@ unsigned int w4a16_gemm_timeouts() {
 }
 
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
-                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep) {
-    if (!M || K % BK || N % BN) return false;
+                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile) {
+    if (!M || K % BK || N % 128) return false;
     if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)sc & 15) || ((uintptr_t)y & 15)) return false;
     if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
     EncodeTiledFn enc = encode_fn();
@@ -436,10 +469,14 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
     if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
-    // two row halves per tile when that still gives every SM a tile
-    const uint32_t tiles2 = ((M + 255) / 256) * (N / BN);
-    if (M > 128 && tiles2 >= (uint32_t)sms) return launch<2>(st, tmap, packed, sc, y, M, K, N, ep, sms);
-    return launch<1>(st, tmap, packed, sc, y, M, K, N, ep, sms);
+    // Largest tile that still gives every SM a tile.
+    const uint32_t t256 = ((M + 255) / 256) * (N / 256);
+    const uint32_t t128 = ((M + 255) / 256) * (N / 128);
+    const int force = tile;   // 0: by shape, 1: 128x128, 2: 256x128, 3: 256x256
+    if (force == 3 ? N % 256 == 0 : (force == 0 && N % 256 == 0 && M > 128 && t256 >= (uint32_t)sms))
+        return launch<2, 256>(st, tmap, packed, sc, y, M, K, N, ep, sms);
+    if (force == 2 || (force == 0 && M > 128 && t128 >= (uint32_t)sms)) return launch<2, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
+    return launch<1, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
 }
 
 }  // namespace gehtp

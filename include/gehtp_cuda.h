@@ -201,7 +201,9 @@ size_t gehtp_w4a16_slot_bytes(uint32_t K, uint32_t N);
  * tests and small tools; 0 on success, -1 otherwise (see gehtp_cuda_last_error).
  *
  * gehtp_w4a16_matmul: `w_slot` in the slot form above. `path`: 0 = engine's
- * choice by M, 1 = streaming GEMV (mma.sync), 2 = tcgen05 GEMM. */
+ * choice by M, 1 = streaming GEMV (mma.sync), 2 = tcgen05 GEMM with the tile
+ * chosen from the shape, 3 / 4 / 5 = tcgen05 GEMM with 128x128 / 256x128 /
+ * 256x256 tiles (256-wide tiles need N % 256 == 0). */
 int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y_f16,
                        uint32_t M, uint32_t K, uint32_t N, int path);
 /* Integer q-8 of every weight, read back out of the device-side packed

@@ -71,6 +71,13 @@ def test_w4a16_tcgen05_gemm_vs_oracle(cuda, orc, M, K, N):
     skinny = np.zeros((M, N), np.float16)
     assert cuda.gehtp_w4a16_matmul(ptr(a), ptr(slot), ptr(skinny), M, K, N, 1) == 0
     assert_fp16_close(got, skinny, "tcgen05 vs streaming kernel")
+    # every tile configuration gives the same bits: the k order of the accumulation does not depend on the tile
+    for path in (3, 4, 5):
+        if path == 5 and N % 256:
+            continue
+        other = np.zeros((M, N), np.float16)
+        assert cuda.gehtp_w4a16_matmul(ptr(a), ptr(slot), ptr(other), M, K, N, path) == 0, cuda.gehtp_cuda_last_error()
+        assert np.array_equal(other.view(np.uint16), got.view(np.uint16)), "tile configuration %d differs" % path
 
 
 def test_w4a16_exact_on_small_integers(cuda, orc):
