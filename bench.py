@@ -44,7 +44,7 @@ def parse_args():
                          "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -393,6 +393,42 @@ def run_micro(which):
             us = timeit(lambda i: lib.gehtp_dev_rmsnorm(x[i % 64].data_ptr(), r[i % 64].data_ptr(), gam.data_ptr(), None,
                                                         sm.data_ptr(), y.data_ptr(), rows, width))
             out.append({"kernel": "add_rmsnorm", "rows": rows, "width": width, "us": us, "GBps": 8.0 * rows * width / us / 1e3})
+    if which == "gdn":
+        # gated-delta-rule layer (config 5): in-projection, conv1d over 4096 channels, 32 chunks of 64 tokens, out-projection
+        from gehtp_b200.runlists import build_gdn_runlist
+        from gehtp_b200.wtop import Engine
+        buf, man = build_gdn_runlist()
+        eng = Engine(lib, buf)
+        h = np.random.default_rng(1005).standard_normal((man["seq"], man["hidden"])).astype(np.float16)
+        last = man["chunk_out"][-1]
+        for _ in range(3):
+            lib.wt_exec_state_reset()
+            eng.run_io(h, last, None)
+        stream = torch.cuda.ExternalStream(lib.gehtp_cuda_stream())
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+        for _ in range(reps):
+            eng.run_io(h, last, None)
+        with torch.cuda.stream(stream):
+            e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        op_ms = (ctypes.c_float * eng.blob.n_ops)()
+        err = ctypes.create_string_buffer(256)
+        assert lib.gehtp_cuda_run_profiled(ctypes.byref(eng.blob), h.ctypes.data, last, op_ms, eng.blob.n_ops, err, 256) == 0, err.value
+        from gehtp_b200.wtop import OP as _OP
+        by = {}
+        for i in range(eng.blob.n_ops):
+            by[eng.blob.ops[i].opcode] = by.get(eng.blob.ops[i].opcode, 0.0) + op_ms[i]
+        H, D, seq, C = man["H"], man["D"], man["seq"], man["C"]
+        out.append({"workload": "gated delta-rule layer, seq 2048, 16 heads x 128, conv 4096 channels, W4A16 in/out projections",
+                    "ms": ms, "tokens_per_s": seq / ms * 1e3,
+                    "conv1d_ms": by.get(_OP.CONV1D_SSM, 0.0), "conv1d_GBps": 2.0 * seq * C * 2 / max(by.get(_OP.CONV1D_SSM, 1e-9), 1e-9) / 1e6,
+                    "delta_chunks_ms": by.get(_OP.DELTA_CHUNK, 0.0), "delta_qkvy_GBps": 4.0 * H * seq * D * 2 / max(by.get(_OP.DELTA_CHUNK, 1e-9), 1e-9) / 1e6,
+                    "projections_ms": by.get(_OP.MATMUL_W4A16, 0.0)})
+        eng.shutdown()
     if which == "prefill":
         # Qwen3-0.6B-shaped causal prefill of 512 tokens, batch 1, through the engine (graph replay after warm-up)
         from gehtp_b200.runlists import QWEN3_0P6B, build_prefill_runlist

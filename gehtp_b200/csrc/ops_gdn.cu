@@ -73,9 +73,16 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
                    int c, int ntok, int D, int q_raw) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int h = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
+    // The value dimension m is split over gridDim.y CTAs per head: b, u, y and the rows of S are
+    // independent across m (every element is computed exactly as an unsplit CTA would), while the
+    // small c x c matrices L, T and QK are recomputed by each of them.
+    const int Dm = D / (int)gridDim.y, m0 = (int)blockIdx.y * Dm;
+    // Rows of kf, qf and S are padded by one float: several loops walk them with the
+    // row index on the lanes, which without the pad lands every lane in the same bank.
+    const int DP = D + 1;
     float* kf = (float*)smem;
-    float* qf = kf + (size_t)c * D;
-    float* bm = qf + (size_t)c * D;
+    float* qf = kf + (size_t)c * DP;
+    float* bm = qf + (size_t)c * DP;
     float* u = bm + (size_t)c * D;
     float* G = u + (size_t)c * D;      // [64]
     float* bj = G + 64;                // [64]
@@ -98,13 +105,16 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
         for (int t = 0; t < c; t++) { acc += h2f(gh[t]); G[t] = acc; }
     }
     for (int t = tid; t < c; t += NT) bj[t] = h2f(bh[t]);
+    const int SP = S_SMEM ? DP : D;   // row stride of S (the global copy is not padded)
+    const int ms0 = S_SMEM ? m0 : 0;  // first row held by S (the shared copy holds this CTA's rows only)
     for (int e = tid; e < c * D; e += NT) {
-        kf[e] = h2f(kh[e]);
+        const int r = e / D, n = e % D;
+        kf[r * DP + n] = h2f(kh[e]);
         bm[e] = h2f(vh[e]);
-        qf[e] = h2f(qh[e]) * scale;
+        qf[r * DP + n] = h2f(qh[e]) * scale;
     }
     if (S_SMEM)
-        for (int e = tid; e < D * D; e += NT) S[e] = Sglob[e];
+        for (int e = tid; e < Dm * D; e += NT) S[(e / D) * SP + e % D] = Sglob[(size_t)m0 * D + e];
     __syncthreads();
 
     // L[j][i] = exp(G_j - G_i) * (k_j . k_i) * beta_j for i < j, else 0 (fp16)
@@ -113,7 +123,7 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
         uint16_t r = 0;
         if (i < j) {
             float s = 0.0f;
-            for (int n = 0; n < D; n++) s += kf[j * D + n] * kf[i * D + n];
+            for (int n = 0; n < D; n++) s += kf[j * DP + n] * kf[i * DP + n];
             r = f2h(expf(G[j] - G[i]) * s * bj[j]);
         }
         Lh[j * c + i] = r;
@@ -133,23 +143,23 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
         __syncthreads();
     }
     // b_j = beta_j (v_j - e^{G_j} S0 k_j), in place over v
-    for (int e = tid; e < c * D; e += NT) {
-        int j = e / D, m = e % D;
+    for (int e = tid; e < c * Dm; e += NT) {
+        int j = e / Dm, m = m0 + e % Dm;
         float sk = 0.0f;
-        for (int n = 0; n < D; n++) sk += S[m * D + n] * kf[j * D + n];
-        bm[e] = bj[j] * (bm[e] - expf(G[j]) * sk);
+        for (int n = 0; n < D; n++) sk += S[(m - ms0) * SP + n] * kf[j * DP + n];
+        bm[j * D + m] = bj[j] * (bm[j * D + m] - expf(G[j]) * sk);
     }
     __syncthreads();
     // u = T b
-    for (int e = tid; e < c * D; e += NT) {
-        int j = e / D, m = e % D;
+    for (int e = tid; e < c * Dm; e += NT) {
+        int j = e / Dm, m = m0 + e % Dm;
         float acc = 0.0f;
         for (int i = 0; i <= j; i++) {
             float tij = h2f(T[j * c + i]);
             if (tij == 0.0f) continue;
             acc += tij * bm[i * D + m];
         }
-        u[e] = acc;
+        u[j * D + m] = acc;
     }
     __syncthreads();
     // QK[t][i] = exp(G_t - G_i) (q_t . k_i), i <= t (T and L are dead now)
@@ -157,52 +167,58 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
         int t = e / c, i = e % c;
         float qk = 0.0f;
         if (i <= t) {
-            for (int n = 0; n < D; n++) qk += qf[t * D + n] * kf[i * D + n];
+            for (int n = 0; n < D; n++) qk += qf[t * DP + n] * kf[i * DP + n];
             qk *= expf(G[t] - G[i]);
         }
         QK[e] = qk;
     }
     __syncthreads();
     // y_t = e^{G_t} (S0 q_t) + sum_{i<=t} QK[t][i] u_i
-    for (int e = tid; e < c * D; e += NT) {
-        int t = e / D, m = e % D;
+    for (int e = tid; e < c * Dm; e += NT) {
+        int t = e / Dm, m = m0 + e % Dm;
         float s = 0.0f;
-        for (int n = 0; n < D; n++) s += S[m * D + n] * qf[t * D + n];
+        for (int n = 0; n < D; n++) s += S[(m - ms0) * SP + n] * qf[t * DP + n];
         float acc = expf(G[t]) * s;
         for (int i = 0; i <= t; i++) {
             float qk = QK[t * c + i];
             if (qk == 0.0f) continue;
             acc += qk * u[i * D + m];
         }
-        yh[e] = f2h(acc);
+        yh[t * D + m] = f2h(acc);
     }
     __syncthreads();
     // S' = e^{G_c} S0 + sum_i e^{G_c - G_i} u_i k_i^T
     const float eC = expf(G[c - 1]);
-    for (int e = tid; e < D * D; e += NT) {
-        int m = e / D, n = e % D;
-        float sv = S[e] * eC;
+    for (int i = tid; i < c; i += NT) bj[i] = expf(G[c - 1] - G[i]);   // beta is dead by now: its row holds the decay of token i
+    __syncthreads();
+    for (int e = tid; e < Dm * D; e += NT) {
+        int m = m0 + e / D, n = e % D;
+        float sv = S[(m - ms0) * SP + n] * eC;
         for (int i = 0; i < c; i++) {
-            float wu = expf(G[c - 1] - G[i]) * u[i * D + m];
+            float wu = bj[i] * u[i * D + m];
             if (wu == 0.0f) continue;
-            sv += wu * kf[i * D + n];
+            sv += wu * kf[i * DP + n];
         }
-        Sglob[e] = sv;
+        Sglob[(size_t)m * D + n] = sv;
     }
 }
 
 void k_delta_chunk(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_t* q,
                    const uint16_t* beta, const uint16_t* g, uint16_t* y, float* S, uint32_t c,
                    uint32_t ntok, uint32_t H, uint32_t D, uint32_t q_raw) {
-    size_t base = (size_t)4 * c * D * 4 + 128 * 4 + 2 * 64 * 64 * 2;
-    bool s_smem = base + (size_t)D * D * 4 <= 227 * 1024;
-    size_t smem = base + (s_smem ? (size_t)D * D * 4 : 0);
+    // 4 CTAs per head when D allows: each owns D/4 value columns and D/4 rows of S
+    const uint32_t MS = (D % 4 == 0 && D >= 64) ? 4 : 1;
+    size_t base = (size_t)2 * c * D * 4 + (size_t)2 * c * (D + 1) * 4 + 128 * 4 + 2 * 64 * 64 * 2;
+    size_t s_bytes = (size_t)(D / MS) * (D + 1) * 4;
+    bool s_smem = base + s_bytes <= 227 * 1024;
+    size_t smem = base + (s_smem ? s_bytes : 0);
+    const dim3 grid(H, MS);
     if (s_smem) {
         cudaFuncSetAttribute(delta_chunk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_chunk_kernel<true><<<H, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
+        delta_chunk_kernel<true><<<grid, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
     } else {
         cudaFuncSetAttribute(delta_chunk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_chunk_kernel<false><<<H, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
+        delta_chunk_kernel<false><<<grid, 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)D, (int)q_raw);
     }
     g_launches++;
 }

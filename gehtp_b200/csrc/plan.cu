@@ -659,7 +659,7 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
         if ((a[6] & 0xE000u) != WT_REF_STATE_FLAG) FAIL("delta state_ref bad");
         uint32_t si = a[6] & 0x1FFFu;
         if (si >= g.n_states || g.st_bytes[si] < (uint64_t)H * D * D * 4u) FAIL("delta state %u too small", si);
-        if ((uint64_t)4 * c * D * 4 + 17408 > 227u * 1024u) FAIL("delta chunk c=%u D=%u exceeds shared memory", c, D);
+        if ((uint64_t)4 * c * (D + 1) * 4 + 17408 > 227u * 1024u) FAIL("delta chunk c=%u D=%u exceeds shared memory", c, D);
         float* S = (float*)g.st_buf[si];
         p.engine = WT_ENG_HVX;
         if (P.build) p.launch = [=](cudaStream_t st) { k_delta_chunk(st, k, v, q, be, gg, y, S, c, ntok, H, D, q_raw); };

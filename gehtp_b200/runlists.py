@@ -419,3 +419,60 @@ def build_prefill_runlist(cfg, seq, seed=1003, quant="w4", n_layers=None, with_l
         man["logits_temp"] = e.linear(hn, *rand_w4(rng, H, V), seq)
     man["n_ops"] = len(e.b.ops)
     return e.b.build(), man
+
+
+def build_gdn_runlist(seq=2048, hidden=1024, C=4096, k_conv=4, H=16, D=128, chunk=64, seed=1005, quant="w4"):
+    """One gated-delta-rule linear-attention layer over `seq` tokens, batch 1
+    (baseline config 5): W4A16 in-projection hidden -> C channels, causal
+    depthwise conv1d (OP_CONV1D_SSM), the delta rule chunk by chunk
+    (OP_DELTA_CHUNK, fp32 state [H, D, D] carried in persistent state 0) on
+    independent synthetic q/k/v/beta/g slots, and a W4A16 out-projection
+    H*D -> hidden of every chunk's output. Input face: h fp16 [seq, hidden].
+
+    Returns (blob, manifest); manifest["chunk_out"] lists the temps holding
+    the out-projection of each chunk ([chunk, hidden] fp16)."""
+    rng = np.random.default_rng(seed)
+    assert seq % chunk == 0 and chunk <= 64
+    e = Emitter(quant)
+    face = e.b.add_ext_in(seq * hidden * 2)
+    e.b.add_states([H * D * D * 4])
+    xin = e.linear(S(face), *rand_w4(rng, hidden, C), seq)
+    conv_w = e.b.add_slot(rng.normal(0.0, 0.5, (k_conv, C)).astype(np.float16))
+    conv = e.fresh()
+    e.b.add_op(OP.CONV1D_SSM, [xin, conv_w, conv, seq, C, k_conv])
+    kk = rng.standard_normal((H, seq, D)).astype(np.float32)
+    kk = (kk / np.linalg.norm(kk, axis=-1, keepdims=True)).astype(np.float16)
+    vv = rng.standard_normal((H, seq, D)).astype(np.float16)
+    qq = rng.standard_normal((H, seq, D)).astype(np.float16)
+    beta = (1.0 / (1.0 + np.exp(-rng.standard_normal((H, seq))))).astype(np.float16)
+    gg = np.log(1.0 / (1.0 + np.exp(-rng.standard_normal((H, seq))))).astype(np.float16)
+    sk, sv, sq, sb, sg = (S(e.b.add_slot(a)) for a in (kk, vv, qq, beta, gg))
+    nib_o, sc_o = rand_w4(rng, H * D, hidden)
+    if quant == "w4":
+        w_out = S(e.b.add_slot(np.concatenate([nib_o.reshape(-1), sc_o.view(np.uint8).reshape(-1)]), count=H * D * hidden))
+    else:
+        w_out = S(e.b.add_slot(dequant_f16(nib_o, sc_o)))
+    outs = []
+    for ci in range(seq // chunk):
+        t0, t1 = ci * chunk, (ci + 1) * chunk
+        parts = []
+        for src in (sk, sv, sq):
+            y = e.fresh()
+            e.b.add_op(OP.SLICE, [src, y, H * chunk * D, 3, 0, t0, 0, H, t1, D, 1, 1, 1, H, seq, D])
+            parts.append(y)
+        for src in (sb, sg):
+            y = e.fresh()
+            e.b.add_op(OP.SLICE, [src, y, H * chunk, 2, 0, t0, 0, H, t1, 0, 1, 1, 1, H, seq, 1])
+            parts.append(y)
+        yc = e.fresh()
+        e.b.add_op(OP.DELTA_CHUNK, parts + [yc, ST(0), chunk, chunk, H, D, 0])
+        yt = e.transpose3(yc, (H, chunk, D), (1, 0, 2))            # [chunk, H*D]
+        yo = e.fresh()
+        if quant == "w4":
+            e.b.add_op(OP.MATMUL_W4A16, [yt, w_out, yo, chunk, H * D, hidden])
+        else:
+            e.b.add_op(OP.MATMUL_F16, [yt, w_out, yo, chunk, H * D, hidden, 0])
+        outs.append(yo)
+    man = dict(seq=seq, hidden=hidden, C=C, H=H, D=D, chunk=chunk, conv_temp=conv, chunk_out=outs,
+               input_slot=face, quant=quant, n_ops=len(e.b.ops))
+    return e.b.build(), man

@@ -252,6 +252,27 @@ def test_prefill_runlist_matches_reference(cuda, ref, seq):
     assert_fp16_close(outs[0], unfused, "fused vs op-by-op prefill")
 
 
+def test_gdn_layer_runlist_matches_reference(cuda, ref):
+    """Config 5 in small: W4A16 in-projection, causal conv1d, four delta-rule chunks carrying the
+    fp32 state, out-projection per chunk; against the reference executor with dequantised weights."""
+    from gehtp_b200.runlists import build_gdn_runlist
+    kw = dict(seq=128, hidden=128, C=256, H=2, D=128, chunk=32, seed=5)
+    buf_w4, man = build_gdn_runlist(quant="w4", **kw)
+    buf_f16, man2 = build_gdn_runlist(quant="f16", **kw)
+    h = np.random.default_rng(3).standard_normal((kw["seq"], kw["hidden"])).astype(np.float16)
+    res = []
+    for lib, buf, m in ((cuda, buf_w4, man), (ref, buf_f16, man2)):
+        lib.wt_exec_state_reset()
+        eng = Engine(lib, buf)
+        eng.run_io(h, m["chunk_out"][-1], None)
+        res.append([eng.temp(m["conv_temp"]).copy()] + [eng.temp(t).copy() for t in m["chunk_out"]])
+        eng.shutdown()
+        lib.wt_exec_state_reset()
+    assert_fp16_close(res[0][0], res[1][0], "conv1d over the in-projection")
+    for i in range(1, len(res[0])):
+        assert_fp16_close(res[0][i], res[1][i], "delta-rule chunk %d after the out-projection" % (i - 1))
+
+
 def test_static_offset_table_and_alias_hazard(cuda, ref):
     """A TEMPOFF table whose offsets are sound is honoured; one that maps two
     simultaneously live temps to the same bytes (what the reference's emitter
