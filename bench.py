@@ -457,7 +457,16 @@ def run_micro(which):
         nh, kvh, hd = cfg.n_heads, cfg.kv_heads, cfg.head_dim
         lin = 2.0 * seq * (H * (nh + 2 * kvh) * hd + nh * hd * H + 3 * H * F) * L + 2.0 * seq * H * V
         att = 4.0 * nh * seq * seq * hd / 2 * L
+        op_ms = (ctypes.c_float * eng.blob.n_ops)()
+        perr = ctypes.create_string_buffer(256)
+        by = {}
+        if lib.gehtp_cuda_run_profiled(ctypes.byref(eng.blob), ids.ctypes.data, man["hidden_temp"], op_ms, eng.blob.n_ops, perr, 256) == 0:
+            for i in range(eng.blob.n_ops):
+                if op_ms[i] > 0:
+                    k = int(eng.blob.ops[i].opcode)
+                    by[k] = [by.get(k, [0, 0.0])[0] + 1, by.get(k, [0, 0.0])[1] + op_ms[i]]
         out.append({"workload": "qwen3-0.6b-shape prefill, 512 tokens, batch 1, 28 layers + lm_head", "ms": ms,
+                    "units_ms_by_first_opcode": {str(k): [v[0], round(v[1], 3)] for k, v in sorted(by.items(), key=lambda kv: -kv[1][1])},
                     "tokens_per_s": seq / ms * 1e3, "TFLOPs": (lin + att) / ms / 1e9, "fused_ops": int(lib.gehtp_cuda_fused_ops()),
                     "frac_of_measured_bf16_peak": (lin + att) / ms / 1e9 / peak_tf})
         eng.shutdown()
