@@ -114,6 +114,8 @@ struct Engine {
     struct ProfEvent { uint32_t op; cudaEvent_t e0, e1; };
     float* prof_ms = nullptr;
     std::vector<ProfEvent> prof_events;
+    float prof_attn_ms = 0.0f;      // decode attention kernel alone, last profiled run
+    uint32_t prof_attn_n = 0;
 
     // options
     int opt_fuse = 1, opt_graph = 1, trace_on = 0;

@@ -12,6 +12,7 @@
 #include <cstring>
 #include <thread>
 #include "engine.h"
+#include "launchers_attn.h"
 
 namespace gehtp {
 
@@ -576,6 +577,7 @@ int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_
     // The stream is held back by a host node until every launch of the pass is
     // queued (bounded: 200 ms), so the event pairs measure kernels running back
     // to back, not the host's launch pace.
+    attn_prof_begin();
     static std::atomic<int> go;
     go.store(0);
     cudaLaunchHostFunc(g.stream, [](void* p) {
@@ -587,6 +589,7 @@ int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_
     if (rc == 0) rc = finish_run(err, errn);
     else cudaStreamSynchronize(g.stream);
     g.prof_ms = nullptr;
+    attn_prof_end(&g.prof_attn_ms, &g.prof_attn_n);
     for (auto& e : g.prof_events) {
         float ms = 0.0f;
         if (rc == 0 && e.op < cap && cudaEventElapsedTime(&ms, e.e0, e.e1) == cudaSuccess) op_ms[e.op] = ms;
@@ -594,6 +597,13 @@ int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_
     }
     g.prof_events.clear();
     return rc;
+}
+
+// Summed device time and launch count of the decode attention kernel alone in the last
+// gehtp_cuda_run_profiled (its launch unit also holds the rotary/append and merge kernels).
+void gehtp_cuda_profiled_attn(float* total_ms, uint32_t* launches) {
+    if (total_ms) *total_ms = g.prof_attn_ms;
+    if (launches) *launches = g.prof_attn_n;
 }
 
 // Loads `bytes` of a persistent state from host or device memory and, for a KV

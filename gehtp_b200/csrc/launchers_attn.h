@@ -26,6 +26,12 @@ struct AttnDecodeArgs {
     int no_cache;              // 1: keep no host-side record of this ring (its tensor map is built per call)
 };
 
+// Timing probe for profiled runs: between begin and end every launch of the grouped attention kernel
+// is bracketed by a CUDA event pair on its stream; end waits for nothing (the caller has synchronised)
+// and returns the summed kernel time and the number of launches.
+void attn_prof_begin();
+void attn_prof_end(float* total_ms, uint32_t* launches);
+
 uint32_t attn_decode_nsplit(uint32_t kv_heads_total, uint32_t max_positions, uint32_t rep, uint32_t hd, size_t max_floats);
 size_t attn_decode_scratch_floats(uint32_t kv_heads_total, uint32_t rep, uint32_t hd, uint32_t nsplit);
 // false: shape not handled (rep > 16 or head_dim not 64/128); nothing launched

@@ -23,6 +23,8 @@
 // small kernel merges the chunks in chunk order.
 #include <cstdio>
 #include <map>
+#include <utility>
+#include <vector>
 #include <tuple>
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -830,6 +832,32 @@ const CUtensorMap* ring_tensor_map(const uint16_t* ring, uint32_t nslots, uint32
 }
 }  // namespace
 
+namespace {
+bool g_attn_prof = false;
+std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_attn_prof_events;
+}  // namespace
+
+void attn_prof_begin() {
+    g_attn_prof_events.clear();
+    g_attn_prof = true;
+}
+
+void attn_prof_end(float* total_ms, uint32_t* launches) {
+    g_attn_prof = false;
+    float tot = 0.0f;
+    uint32_t n = 0;
+    for (auto& e : g_attn_prof_events) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) { tot += ms; n++; }
+        cudaEventDestroy(e.first);
+        cudaEventDestroy(e.second);
+    }
+    cudaGetLastError();
+    g_attn_prof_events.clear();
+    if (total_ms) *total_ms = tot;
+    if (launches) *launches = n;
+}
+
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out, uint32_t kv_heads_total) {
     if (a.rep == 0 || a.rep > 16 || (hd != 128 && hd != 64)) return false;
     if (!a.nsplit) return false;
@@ -838,7 +866,10 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
             const size_t tsmem = 1024 + (size_t)TMA_STAGES * TMA_STAGE_B + 2 * TMA_STAGES * sizeof(uint64_t);
             static bool tattr = false;
             if (!tattr) { cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem); tattr = true; }
+            cudaEvent_t pe0 = nullptr, pe1 = nullptr;
+            if (g_attn_prof) { cudaEventCreate(&pe0); cudaEventCreate(&pe1); cudaEventRecord(pe0, st); }
             launch_pdl(attn_decode_tma_kernel, dim3((kv_heads_total / 4) * a.nsplit), dim3((TMA_NW + 1) * 32), tsmem, st, *tm, a, kv_heads_total);
+            if (g_attn_prof) { cudaEventRecord(pe1, st); g_attn_prof_events.emplace_back(pe0, pe1); }
             launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
                        (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, 16u);
             g_launches += 2;

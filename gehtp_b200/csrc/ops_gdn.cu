@@ -130,15 +130,17 @@ delta_chunk_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ 
     }
     __syncthreads();
     // T = (I + L)^-1 by rows; each row needs the rows above it
+    // Four lanes share a column j and split the sum over i (the rows are a dependency chain of c
+    // steps, so the step itself has to be short); the four partial sums are added pairwise.
     for (int r = 0; r < c; r++) {
-        for (int j = tid; j < c; j += NT) {
-            uint16_t out = 0;
-            if (j <= r) {
-                float s = (r == j) ? 1.0f : 0.0f;
-                for (int i = j; i < r; i++) s -= h2f(Lh[r * c + i]) * h2f(T[i * c + j]);
-                out = f2h(s);
-            }
-            T[r * c + j] = out;
+        for (int base = 0; base < c * 4; base += NT) {        // every thread runs the body: the shuffles need whole warps
+            const int jj = base + tid, j = jj >> 2, part = jj & 3;
+            float s = 0.0f;
+            if (j < r && j < c)
+                for (int i = j + part; i < r; i += 4) s -= h2f(Lh[r * c + i]) * h2f(T[i * c + j]);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (part == 0 && j < c) T[r * c + j] = j <= r ? f2h((r == j ? 1.0f : 0.0f) + s) : (uint16_t)0;
         }
         __syncthreads();
     }

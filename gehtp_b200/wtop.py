@@ -190,6 +190,8 @@ def bind(lib):
         lib.gehtp_cuda_set_graph.argtypes = [c.c_int]
         lib.gehtp_cuda_run_dev.argtypes = [P(WtBlob), c.c_void_p, c.c_void_p, c.c_uint32, c.c_char_p, c.c_size_t]
         lib.gehtp_cuda_run_profiled.argtypes = [P(WtBlob), c.c_void_p, c.c_uint32, P(c.c_float), c.c_uint32, c.c_char_p, c.c_size_t]
+        lib.gehtp_cuda_profiled_attn.argtypes = [P(c.c_float), P(c.c_uint32)]
+        lib.gehtp_cuda_profiled_attn.restype = None
         lib.gehtp_cuda_state_load.argtypes = [P(WtBlob), c.c_uint32, c.c_void_p, c.c_size_t, c.c_int, c.c_uint32, c.c_uint32, c.c_char_p, c.c_size_t]
         lib.gehtp_cuda_state_set_count.argtypes = [c.c_uint32, c.c_uint32]
         lib.gehtp_cuda_state_read.argtypes = [c.c_uint32, c.c_void_p, c.c_size_t]

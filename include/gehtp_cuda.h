@@ -163,6 +163,9 @@ int gehtp_cuda_run_dev(const struct wt_blob* b, const void* in_dev, void* out_de
  * ops absorbed into a fused unit. `in_ptr` is host memory as in wt_exec_run_io. */
 int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_t out_temp,
                             float* op_ms, uint32_t cap, char* err, size_t errn);
+/* Device time (summed, ms) and launch count of the decode attention kernel alone in the last
+ * gehtp_cuda_run_profiled: its launch unit also holds the rotary/append and merge kernels. */
+void gehtp_cuda_profiled_attn(float* total_ms, uint32_t* launches);
 
 /* Persistent-state image exchange (the reference keeps states inside its
  * engine and can only fill them by running append ops; its host golden saves
