@@ -133,7 +133,11 @@ def classify_units(blob, op_ms, man, n_kv):
         if ms <= 0.0:
             i += 1
             continue
-        if op.opcode == OP.MATMUL_W4A16:
+        if op.opcode == OP.MATMUL_W4A16 and i + 1 < n and blob.ops[i + 1].opcode == OP.SPLIT and op_ms[i + 1] <= 0.0:
+            # the q|k|v projection heads the attention unit (rotary + append in its epilogue, then attention + merge);
+            # the unit is filed under attention, whose KV bytes dominate it
+            add("attn_decode", ms, 2 * n_kv * man["kv_elems"] * 2 + 4 * man["q_elems"])
+        elif op.opcode == OP.MATMUL_W4A16:
             M, K, N = op.args[3], op.args[4], op.args[5]
             nb = w4_bytes(M, K, N)
             dual = (i + 3 < n and blob.ops[i + 1].opcode == OP.UNARY and blob.ops[i + 3].opcode == OP.MATMUL_W4A16
@@ -632,7 +636,7 @@ def run_main(args):
     achieved = dbytes / (dms * 1e-3) / 1e9
     dom_kernel, dom_us = dom, dms * 1e3 / dn
     if dom == "attn_decode" and r.get("attn_kernel_us"):
-        # the unit holds three kernels (rotary/append, attention, merge); the roofline is the attention kernel's,
+        # the unit holds three kernels (q|k|v projection with rotary/append, attention, merge); the roofline is the attention kernel's,
         # timed by its own event pair inside the same profiled steps
         dom_kernel, dom_us = "attn_decode_tma_kernel", r["attn_kernel_us"]
         achieved = (dbytes / dn) / (dom_us * 1e-6) / 1e9
@@ -644,7 +648,7 @@ def run_main(args):
             "gpu_launches": r["launches"],
             "roofline": {"bound": "hbm", "kernel": dom_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC.get((dom, B, args.ctx, world)), "peak_source": peak_src,
-                         "bytes_per_launch": dbytes / dn, "avg_launch_us": dom_us, "unit_of_three_kernels_us": dms * 1e3 / dn},
+                         "bytes_per_launch": dbytes / dn, "avg_launch_us": dom_us, "launch_unit_us": dms * 1e3 / dn},
             "kernels": kernels, "fused_ops": r["fused_ops"], "setup_s": r["setup_s"]}
     if world == 1 and args.shard_of <= 1:
         # the kernel halves of the headline metric: streaming GEMV (vocabulary projection, M = 1) and prefill GEMM

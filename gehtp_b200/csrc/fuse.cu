@@ -22,6 +22,7 @@
 #include <utility>
 #include "engine.h"
 #include "launchers_attn.h"
+#include "launchers_w4.h"
 
 namespace gehtp {
 
@@ -136,6 +137,9 @@ struct Span {
     // rotary on its own (kind 3): x, cos_q, sin_q, y, rows = M, hd
     // prefill attention (kind 4): q/k/v inputs, mask operand (+ constant mask slot when known), ctx, seq_q = M, seq_k = N
     uint32_t pq, pk, pv, mask_slot; bool mask_is_slot;
+    // decode attention: index of the W4A16 q|k|v projection when it sits right before the chain and
+    // nothing but the chain reads its output (its epilogue can then do the rotary + append), else -1
+    int qkv_lin = -1;
 };
 
 bool contiguous(std::vector<uint32_t>& ops, uint32_t& first) {
@@ -235,6 +239,15 @@ bool match_attention(const Graph& G, uint32_t ia, Span& sp) {
     if (!contiguous(ops, first)) return false;
     if (!closed(G, ops, {j + 4})) return false;
     sp.kind = 0; sp.first = first; sp.count = (uint32_t)ops.size(); sp.ops = ops;
+    {
+        const int lp = G.producer_of_arg[0][rk.src_op];
+        sp.qkv_lin = -1;
+        if (lp >= 0 && (uint32_t)lp + 1 == first && b->ops[lp].opcode == OP_MATMUL_W4A16 && b->ops[lp].args[2] == ks.args[0]) {
+            bool only_chain = true;
+            for (uint32_t u : G.users[lp]) only_chain = only_chain && std::binary_search(ops.begin(), ops.end(), u);
+            if (only_chain) sp.qkv_lin = lp;
+        }
+    }
     sp.qkv = ks.args[0]; sp.cos_q = rq.cos_b; sp.sin_q = rq.sin_b; sp.cos_k = rk.cos_b; sp.sin_k = rk.sin_b;
     sp.q_out = b->ops[rq.out_op].args[2]; sp.mask = ad.args[1]; sp.ctx = pv.args[2]; sp.state = si;
     sp.B = B; sp.nh = nh; sp.kvh = kvh; sp.hd = hd; sp.nslots = nslots; sp.pos = ap.args[3];
@@ -492,6 +505,35 @@ void fuse_materialize(const wt_blob* b) {
                 k_rope_kv_append(st, qkv, cq, sq, ck, sk, q_out, ring, posmap, ctr, B, nh, kvh, hd, nslots, pos);
                 k_attn_decode(st, a, hd, ctx, B * kvh);
             };
+            // The q|k|v projection right before the chain takes the rotary embedding and the append into
+            // its epilogue (one launch less per layer); the projection op becomes the head of the span.
+            if (sp.qkv_lin >= 0 && hd == 128 && B <= 8) {
+                PlanOp& lin = g.plan[sp.qkv_lin];
+                const wt_op& lo = b->ops[sp.qkv_lin];
+                const uint32_t K = lo.args[4], N = lo.args[5];
+                const bool reduced = g.tp_world > 1 && (uint32_t)sp.qkv_lin < g_allreduce_after.size() && g_allreduce_after[sp.qkv_lin];
+                uint64_t key = (uint64_t)(lo.args[1] & 0x7FFFu) | ((uint64_t)K << 16) | ((uint64_t)N << 40);
+                auto it = g.w4.find(key);
+                const uint16_t* act = (const uint16_t*)resolve(b, lo.args[0]);
+                if (it != g.w4.end() && act && !lin.fused && !lin.rc && lin.launch && !lin.uses_internal && !reduced &&
+                    lo.args[3] == B && N == (nh + 2 * kvh) * hd && K % 512 == 0 && K / 512 <= 10 &&
+                    N / 32 >= 148) {     // one CTA per pair of strips: worth it only while every SM still gets one
+                    W4Epilogue ep;
+                    ep.mode = 2;
+                    ep.cos_q = cq; ep.sin_q = sq; ep.cos_k = ck; ep.sin_k = sk; ep.q_out = q_out; ep.ring = ring;
+                    ep.posmap = posmap; ep.counter = ctr; ep.nh = nh; ep.kvh = kvh; ep.nslots = nslots; ep.pos_const = pos;
+                    const uint32_t* pk = it->second.packed;
+                    const uint16_t* sc = it->second.scales;
+                    const uint32_t wm = lin.w4_m;
+                    (void)wm;
+                    lin.fused = [=](cudaStream_t st) {
+                        k_w4a16_skinny_qkv_rope(st, act, pk, sc, B, K, N, ep);
+                        k_attn_decode(st, a, hd, ctx, B * kvh);
+                    };
+                    lin.span = 1 + sp.count;
+                    g.fused_ops += 1;
+                }
+            }
         } else if (sp.kind == 1) {
             const uint16_t* act = (const uint16_t*)resolve(b, sp.a_ref);
             uint16_t* y = (uint16_t*)resolve(b, sp.y);

@@ -9,9 +9,20 @@ namespace gehtp {
 //   mode 0: y = f16(acc)
 //   mode 1: y = f16( f16(acc) + res )          (matmul followed by a residual ADD op;
 //           both fp16 roundings of the two-op form are kept)
+//   mode 2: the matmul is the fused q|k|v projection of a decode step (head_dim 128): the rotary
+//           embedding is applied to the q and k heads with the rounding points of the op chain
+//           (matmul output -> fp16, x*cos -> fp16, rot(x)*sin -> fp16, sum -> fp16), q goes to
+//           q_out, k and v go straight into the KV ring slot of the position (SPLIT x3 + rotary
+//           chain x2 + KV_APPEND of the runlist). Streaming kernel only, M <= 8.
 struct W4Epilogue {
     int mode = 0;
     const uint16_t* res = nullptr;
+    // mode 2
+    const uint16_t *cos_q = nullptr, *sin_q = nullptr, *cos_k = nullptr, *sin_k = nullptr;   // [M*heads][hd]
+    uint16_t *q_out = nullptr, *ring = nullptr;
+    uint32_t* posmap = nullptr;
+    const uint32_t* counter = nullptr;
+    uint32_t nh = 0, kvh = 0, nslots = 0, pos_const = 0;
 };
 
 #ifdef __CUDACC__
@@ -37,6 +48,10 @@ void k_w4_unpack_i8(cudaStream_t st, const uint32_t* packed, int8_t* out, uint32
 // from L2 once per 16 rows).
 void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
                     uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep);
+// The q|k|v projection with rotary embedding and KV append in the epilogue (ep.mode == 2, head_dim 128).
+// false: shape not handled (M > 8, K not a multiple of 512 or above 5120, N != (nh + 2 kvh) * 128).
+bool k_w4a16_skinny_qkv_rope(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
+                             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep);
 // Gate and up projections with the SwiGLU product in the epilogue (one pass over both matrices).
 void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* pg, const uint16_t* sg,
                            const uint32_t* pu, const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K,

@@ -185,7 +185,7 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
 //   WALK_ANY  : ragged tail; per-group bounds tests.
 enum { WALK_ANY = 0, WALK_FULL = 1, WALK_ONE = 2 };
 
-template <int MT, int UNROLL, bool DUAL, int WALK>
+template <int MT, int UNROLL, bool DUAL, int WALK, bool ROPE = false>
 __global__ void __launch_bounds__(MT >= 4 ? 512 : 640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
@@ -200,10 +200,15 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t nb = blockIdx.x, NB = N / 16, KG = K / 64;
+    // ROPE: a CTA owns two strips of one head that are half a head (64 columns) apart, so that it
+    // holds both members of every rotary pair; the first half of its warps walks K for the first
+    // strip, the second half for the second.
+    const uint32_t nwk = ROPE ? nwarps / 2 : nwarps;            // warps along K
+    const uint32_t which = ROPE ? warp / nwk : 0, kwarp = ROPE ? warp % nwk : warp;
+    const uint32_t nb = ROPE ? (blockIdx.x / 4) * 8 + blockIdx.x % 4 + which * 4 : blockIdx.x, NB = N / 16, KG = K / 64;
     const uint32_t m0 = blockIdx.y * (8 * MT);
     const uint32_t n_lo = nb * 16 + g;
-    const uint32_t kg0 = warp * (ONE ? (uint32_t)UNROLL : kgw);
+    const uint32_t kg0 = kwarp * (ONE ? (uint32_t)UNROLL : kgw);
     const uint32_t kg1 = ONE ? kg0 + UNROLL : min(kg0 + kgw, KG);
 
     float acc[MT][4], acc2[DUAL ? MT : 1][4];
@@ -324,6 +329,46 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
             if (DUAL) red[(warp * NACC + MT * 4 + i * 4 + c) * 32 + lane] = acc2[i][c];
         }
     __syncthreads();
+    if (ROPE) {
+        // one thread per (row m, column d of the first half): it owns d and d + 64 of its head
+        const uint32_t hd = 128, hidx = blockIdx.x / 4, d0 = (blockIdx.x % 4) * 16;
+        const uint32_t pos = ep.pos_const == 0xFFFFFFFAu ? *ep.counter : ep.pos_const;
+        const uint32_t slot = pos % ep.nslots;
+        const uint32_t kv_elems = M * ep.kvh * hd;
+        uint16_t* kf = ep.ring + (size_t)slot * kv_elems * 2;
+        uint16_t* vf = kf + kv_elems;
+        for (uint32_t idx = threadIdx.x; idx < 4 * 32; idx += blockDim.x) {
+            float sa = 0.0f, sb = 0.0f;
+            for (uint32_t w = 0; w < nwk; w++) {
+                sa += red[w * NACC * 32 + idx];
+                sb += red[(nwk + w) * NACC * 32 + idx];
+            }
+            const uint32_t ln = idx & 31, c = idx >> 5;
+            const uint32_t d = d0 + (ln >> 2) + ((c & 2) ? 8 : 0);
+            const uint32_t m = (ln & 3) * 2 + (c & 1);
+            if (m >= M) continue;
+            const uint16_t xa = f2h(sa), xb = f2h(sb);          // the matmul's own fp16 outputs
+            if (hidx >= ep.nh + ep.kvh) {                        // v head: plain copy into the ring
+                const size_t o = ((size_t)m * ep.kvh + (hidx - ep.nh - ep.kvh)) * hd + d;
+                vf[o] = xa;
+                vf[o + 64] = xb;
+                continue;
+            }
+            const bool is_q = hidx < ep.nh;
+            const size_t o = is_q ? ((size_t)m * ep.nh + hidx) * hd + d : ((size_t)m * ep.kvh + (hidx - ep.nh)) * hd + d;
+            const uint16_t* ct = is_q ? ep.cos_q : ep.cos_k;
+            const uint16_t* st = is_q ? ep.sin_q : ep.sin_k;
+            uint16_t* dst = is_q ? ep.q_out : kf;
+            const float fa = h2f(xa), fb = h2f(xb);
+            // out[d] = x[d] cos - x[d+64] sin ; out[d+64] = x[d+64] cos + x[d] sin, each product rounded to fp16
+            const float lo = __fadd_rn(h2f(f2h(__fmul_rn(fa, h2f(ct[o])))), h2f(f2h(__fmul_rn(-fb, h2f(st[o])))));
+            const float hi = __fadd_rn(h2f(f2h(__fmul_rn(fb, h2f(ct[o + 64])))), h2f(f2h(__fmul_rn(fa, h2f(st[o + 64])))));
+            dst[o] = f2h(lo);
+            dst[o + 64] = f2h(hi);
+        }
+        if (blockIdx.x == 0 && threadIdx.x == 0) ep.posmap[slot] = pos;
+        return;
+    }
     for (uint32_t idx = threadIdx.x; idx < MT * 4 * 32; idx += blockDim.x) {
         float s = 0.0f, s2 = 0.0f;
         for (uint32_t w = 0; w < nwarps; w++) {
@@ -391,6 +436,19 @@ void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, 
         launch_pdl(w4a16_skinny_kernel<4, 4, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     }
     g_launches++;
+}
+
+bool k_w4a16_skinny_qkv_rope(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
+                             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep) {
+    const uint32_t KG = K / 64;
+    if (!M || M > 8 || K % 512 || KG / 8 > 10 || ep.mode != 2 || N != (ep.nh + 2 * ep.kvh) * 128u) return false;
+    const uint32_t kgw = 8, nwk = KG / 8;
+    uint16_t* y = nullptr;
+    const dim3 grid(N / 32, 1), block(2 * nwk * 32);
+    const size_t smem = (size_t)2 * nwk * 4 * 32 * sizeof(float);
+    launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ONE, true>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+    g_launches++;
+    return true;
 }
 
 // y = swiglu(a.Wg, a.Wu): two weight matrices of the same shape in one pass.
