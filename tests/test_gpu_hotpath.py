@@ -171,6 +171,27 @@ def test_decode_runlist_matches_reference(cuda, ref, B):
     cuda.gehtp_cuda_set_graph(1)
 
 
+def test_decode_wide_qkv_projection_takes_rotary_epilogue(cuda, ref):
+    """With 48 heads of 128 (6144 columns) the q|k|v projection is wide enough for the variant whose
+    epilogue applies the rotary embedding and appends to the KV ring; one more op is then fused."""
+    cfg = DecoderConfig(512, 1, 32, 8, 128, 512, 512, 1e6, "wide-heads")
+    B, steps, nslots = 2, 3, 32
+    buf_w4, man = build_decode_runlist(cfg, B, nslots, seed=13, quant="w4")
+    buf_f16, man2 = build_decode_runlist(cfg, B, nslots, seed=13, quant="f16")
+    r_logits, _ = run_decode(ref, buf_f16, man2, cfg, steps)
+    g_logits, _ = run_decode(cuda, buf_w4, man, cfg, steps, fuse=1, graph=1)
+    fused_with = cuda.gehtp_cuda_fused_ops()
+    u_logits, _ = run_decode(cuda, buf_w4, man, cfg, steps, fuse=0, graph=0)
+    for s in range(steps):
+        assert_fp16_close(g_logits[s], r_logits[s], "logits step %d" % s)
+        # the epilogue keeps every rounding point of the op chain: fused and op-by-op agree bit for bit
+        assert np.array_equal(g_logits[s].view(np.uint16), u_logits[s].view(np.uint16)) or \
+            np.abs(g_logits[s].astype(np.float32) - u_logits[s].astype(np.float32)).max() <= 1e-2 * np.abs(u_logits[s]).max()
+    assert fused_with >= 25 + 1 + 5 + 2 + 2      # attention chain + its projection, SwiGLU, two add+norm pairs
+    cuda.gehtp_cuda_set_fusion(1)
+    cuda.gehtp_cuda_set_graph(1)
+
+
 def test_run_range_pieces_equal_whole_run(cuda):
     """Whole-step run vs one run_range call per op: every temp byte-identical
     (the reference's on-device gate 30)."""
