@@ -524,8 +524,6 @@ void fuse_materialize(const wt_blob* b) {
                     ep.posmap = posmap; ep.counter = ctr; ep.nh = nh; ep.kvh = kvh; ep.nslots = nslots; ep.pos_const = pos;
                     const uint32_t* pk = it->second.packed;
                     const uint16_t* sc = it->second.scales;
-                    const uint32_t wm = lin.w4_m;
-                    (void)wm;
                     lin.fused = [=](cudaStream_t st) {
                         k_w4a16_skinny_qkv_rope(st, act, pk, sc, B, K, N, ep);
                         k_attn_decode(st, a, hd, ctx, B * kvh);
