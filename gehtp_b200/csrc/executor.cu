@@ -2,6 +2,7 @@
 // list, host<->device I/O staging, per-op timing / hooks / traces, whole-run
 // CUDA graphs. Mirrors the calling contract of the reference engine
 // (kernels/src/runtime/oplist_exec.c:2499-2602; kernels/include/oplist_exec.h).
+#include <cuda_fp16.h>
 #include <fcntl.h>
 #include <unistd.h>
 #include <chrono>
@@ -655,6 +656,133 @@ int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes) {
     cudaSetDevice(g.device);
     cudaStreamSynchronize(g.stream);
     return cudaMemcpy(dst, g.st_buf[idx], bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+
+// ---- state files in the layout of the reference's host golden ("HDS1") ----
+// compiler/src/ops/host_decode_state.cpp:14-62 writes
+//   "HDS1", u32 n = 42, u32 kv_count[6], f32 kv_k[6][64][512], f32 kv_v[6][64][512],
+//   f32 conv_win[18][3 * 6144], f32 delta_s[18][16 * 128 * 128]
+// (dimensions: compiler/include/hnnx/host_decode_state.hpp:17-27); the device state table
+// numbers them kv 0..5, conv 6..23, delta 24..41 (compiler/tools/wtop_ops/wtop_ops.hpp:478-492).
+// A KV state here is a ring of fp16 slots [K face | V face]; the file holds positions
+// 0..count-1 as fp32 (every fp16 value is exact in fp32, and a file written by the host
+// golden from fp16 inputs rounds back without loss).
+namespace {
+constexpr uint32_t kHdsKv = 6, kHdsConv = 18, kHdsDelta = 18, kHdsKvElems = 512, kHdsKvMax = 64;
+constexpr uint32_t kHdsConvBytes = 3u * 6144u * 4u, kHdsDeltaBytes = 16u * 128u * 128u * 4u;
+constexpr uint32_t kHdsSlotBytes = kHdsKvElems * 4u;   // fp16 K face + fp16 V face
+
+int hds_check_table(char* err, size_t errn) {
+    if (g.n_states != kHdsKv + kHdsConv + kHdsDelta) { set_err(err, errn, "state file: state table does not hold 42 states"); return -1; }
+    for (uint32_t i = 0; i < g.n_states; i++) {
+        bool ok = i < kHdsKv ? (g.st_bytes[i] >= kHdsSlotBytes && g.st_bytes[i] % kHdsSlotBytes == 0 &&
+                                (!g.kv[i].ready || g.kv[i].slot_bytes == kHdsSlotBytes))
+                : i < kHdsKv + kHdsConv ? g.st_bytes[i] == kHdsConvBytes
+                                        : g.st_bytes[i] == kHdsDeltaBytes;
+        if (!ok) {
+            char m[96]; std::snprintf(m, sizeof m, "state file: state %u has %u bytes, not the file's shape", i, g.st_bytes[i]);
+            set_err(err, errn, m); return -1;
+        }
+    }
+    return 0;
+}
+}  // namespace
+
+int gehtp_cuda_state_save_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn) {
+    if (!path) { set_err(err, errn, "null argument"); return -1; }
+    if (!ensure_device(err, errn)) return -1;
+    if (b && ensure_plan(b, err, errn) != 0) return -1;
+    if (hds_check_table(err, errn) != 0) return -1;
+    cudaStreamSynchronize(g.stream);
+    uint32_t counts[WT_MAX_STATES];
+    if (cudaMemcpy(counts, g.d_st_count, sizeof(uint32_t) * g.n_states, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        set_err(err, errn, "state file: counter read failed"); return -1;
+    }
+    std::vector<float> kf((size_t)kHdsKv * kHdsKvMax * kHdsKvElems, 0.0f), vf(kf.size(), 0.0f);
+    uint32_t kv_count[kHdsKv];
+    for (uint32_t i = 0; i < kHdsKv; i++) {
+        kv_count[i] = 0;
+        if (!g.kv[i].ready) continue;
+        const uint32_t nslots = g.kv[i].nslots;
+        std::vector<uint32_t> pm(nslots);
+        std::vector<uint16_t> ring((size_t)g.st_bytes[i] / 2);
+        if (cudaMemcpy(pm.data(), g.kv[i].posmap, (size_t)nslots * 4, cudaMemcpyDeviceToHost) != cudaSuccess ||
+            cudaMemcpy(ring.data(), g.st_buf[i], g.st_bytes[i], cudaMemcpyDeviceToHost) != cudaSuccess) {
+            set_err(err, errn, "state file: KV read failed"); return -1;
+        }
+        // appends at explicit positions leave the AUTO counter at 0: the count is then the run of
+        // resident positions from 0
+        uint32_t n = counts[i];
+        if (!n) while (n < nslots && pm[n] == n) n++;
+        if (n > kHdsKvMax) { set_err(err, errn, "state file: a KV state holds more than 64 positions"); return -1; }
+        kv_count[i] = n;
+        for (uint32_t p = 0; p < n; p++) {
+            const uint32_t s = p % nslots;
+            if (pm[s] != p) { set_err(err, errn, "state file: a KV position below the counter is not resident"); return -1; }
+            const uint16_t* slot = ring.data() + (size_t)s * kHdsKvElems * 2;
+            float* kd = kf.data() + ((size_t)i * kHdsKvMax + p) * kHdsKvElems;
+            float* vd = vf.data() + ((size_t)i * kHdsKvMax + p) * kHdsKvElems;
+            for (uint32_t e = 0; e < kHdsKvElems; e++) {
+                kd[e] = __half2float(__ushort_as_half(slot[e]));
+                vd[e] = __half2float(__ushort_as_half(slot[kHdsKvElems + e]));
+            }
+        }
+    }
+    FILE* f = std::fopen(path, "wb");
+    if (!f) { set_err(err, errn, "state file: cannot open for writing"); return -1; }
+    const uint32_t n = g.n_states;
+    bool ok = std::fwrite("HDS1", 1, 4, f) == 4 && std::fwrite(&n, 4, 1, f) == 1 &&
+              std::fwrite(kv_count, 4, kHdsKv, f) == kHdsKv &&
+              std::fwrite(kf.data(), 4, kf.size(), f) == kf.size() && std::fwrite(vf.data(), 4, vf.size(), f) == vf.size();
+    std::vector<uint8_t> img(kHdsDeltaBytes);
+    for (uint32_t i = kHdsKv; ok && i < n; i++) {
+        ok = cudaMemcpy(img.data(), g.st_buf[i], g.st_bytes[i], cudaMemcpyDeviceToHost) == cudaSuccess &&
+             std::fwrite(img.data(), 1, g.st_bytes[i], f) == g.st_bytes[i];
+    }
+    ok = (std::fclose(f) == 0) && ok;
+    if (!ok) { set_err(err, errn, "state file: write failed"); return -1; }
+    return 0;
+}
+
+// 0 = loaded, 1 = no such file (states untouched), -1 = bad file or a state table of another shape
+// (states untouched), as host_decode_state_load reports them.
+int gehtp_cuda_state_load_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn) {
+    if (!path) { set_err(err, errn, "null argument"); return -1; }
+    if (!ensure_device(err, errn)) return -1;
+    if (b && ensure_plan(b, err, errn) != 0) return -1;
+    if (hds_check_table(err, errn) != 0) return -1;
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return 1;
+    char magic[4];
+    uint32_t n = 0, kv_count[kHdsKv];
+    std::vector<float> kf((size_t)kHdsKv * kHdsKvMax * kHdsKvElems), vf(kf.size());
+    std::vector<uint8_t> rest((size_t)kHdsConv * kHdsConvBytes + (size_t)kHdsDelta * kHdsDeltaBytes);
+    bool ok = std::fread(magic, 1, 4, f) == 4 && !std::memcmp(magic, "HDS1", 4) && std::fread(&n, 4, 1, f) == 1 &&
+              n == g.n_states && std::fread(kv_count, 4, kHdsKv, f) == kHdsKv &&
+              std::fread(kf.data(), 4, kf.size(), f) == kf.size() && std::fread(vf.data(), 4, vf.size(), f) == vf.size() &&
+              std::fread(rest.data(), 1, rest.size(), f) == rest.size();
+    std::fclose(f);
+    for (uint32_t i = 0; ok && i < kHdsKv; i++) ok = kv_count[i] <= kHdsKvMax && kv_count[i] <= g.st_bytes[i] / kHdsSlotBytes;
+    if (!ok) { set_err(err, errn, "state file: bad magic, size or counts"); return -1; }
+    for (uint32_t i = 0; i < kHdsKv; i++) {
+        std::vector<uint16_t> ring((size_t)g.st_bytes[i] / 2, 0);
+        for (uint32_t p = 0; p < kv_count[i]; p++) {
+            uint16_t* slot = ring.data() + (size_t)p * kHdsKvElems * 2;
+            const float* ks = kf.data() + ((size_t)i * kHdsKvMax + p) * kHdsKvElems;
+            const float* vs = vf.data() + ((size_t)i * kHdsKvMax + p) * kHdsKvElems;
+            for (uint32_t e = 0; e < kHdsKvElems; e++) {
+                slot[e] = __half_as_ushort(__float2half_rn(ks[e]));
+                slot[kHdsKvElems + e] = __half_as_ushort(__float2half_rn(vs[e]));
+            }
+        }
+        if (gehtp_cuda_state_load(nullptr, i, ring.data(), g.st_bytes[i], 0, kHdsKvElems, kv_count[i], err, errn) != 0) return -1;
+    }
+    const uint8_t* src = rest.data();
+    for (uint32_t i = kHdsKv; i < n; i++) {
+        if (gehtp_cuda_state_load(nullptr, i, src, g.st_bytes[i], 0, 0, 0, err, errn) != 0) return -1;
+        src += g.st_bytes[i];
+    }
+    return 0;
 }
 
 // Capture whatever the caller queues on the engine stream between begin and

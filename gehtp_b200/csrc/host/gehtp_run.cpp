@@ -8,8 +8,10 @@
 // job.txt holds "key value" lines.
 //   job  : blob, input, output, out_temp; optional trace (0/1), hook (dump spec), steps (n > 1: inputs
 //          are <input>.<i>, outputs <output>.<i>), weights_size, op_ts (path of the per-op timestamp file,
-//          default <output>.op_ts.bin). External weights are looked for beside the blob:
-//          <blob minus ".wtop">.weights.bin.
+//          default <output>.op_ts.bin), state_file (an "HDS1" decode-state file: loaded before the
+//          first run when it exists, written after the last one, the way the reference's host golden
+//          uses GEHTP_HOST_STATE, compiler/src/ir/graph_prepare.cpp:720,1155). External weights are
+//          looked for beside the blob: <blob minus ".wtop">.weights.bin.
 //   serve: blob, req, resp, out, out_temp, in_bytes; optional idle_exit_s, weights_size, trace.
 //          A request file is a 4-byte big-endian header length, a JSON header
 //          {"op": "run|reset|ping|shutdown", "want_out": 0|1, ...} and, for run, the input body; it is
@@ -140,6 +142,23 @@ int run_step(const wt_blob* b, const std::string& in_path, const std::string& ou
     return 0;
 }
 
+// "first load, last save" of the decode states through an HDS1 file
+bool state_file_load(const wt_blob* b, const char* path) {
+    if (!path) return true;
+    char err[160] = {0};
+    int rc = gehtp_cuda_state_load_hds1(b, path, err, sizeof err);
+    if (rc < 0) { logf("[FAIL] state file %s: %s", path, err); return false; }
+    logf(rc == 0 ? "[state] loaded %s" : "[state] %s absent, states start at zero", path);
+    return true;
+}
+bool state_file_save(const wt_blob* b, const char* path) {
+    if (!path) return true;
+    char err[160] = {0};
+    if (gehtp_cuda_state_save_hds1(b, path, err, sizeof err) != 0) { logf("[FAIL] state file %s: %s", path, err); return false; }
+    logf("[state] saved %s", path);
+    return true;
+}
+
 int mode_job(const std::string& job_path) {
     Job job;
     if (!job.load(job_path)) { logf("[FAIL] read %s", job_path.c_str()); return 1; }
@@ -150,6 +169,8 @@ int mode_job(const std::string& job_path) {
     Loaded L;
     if (!load_blob(job, L)) return 1;
     if (const char* hook = job.get("hook")) { wt_exec_set_hook(hook); logf("[hook] tensor dump spec: %s", hook); }
+    const char* state_p = job.get("state_file");
+    if (!state_file_load(L.blob, state_p)) { wt_exec_shutdown(); return 1; }
     const int64_t t_read1 = now_us();
     const long steps = job.num("steps", 1);
     if (steps > 1) {
@@ -163,6 +184,7 @@ int mode_job(const std::string& job_path) {
             bad = r != 0;
         }
         logf("[decode-loop] total us=%lld%s", (long long)(now_us() - t0), bad ? " (FAIL)" : "");
+        if (!bad && !state_file_save(L.blob, state_p)) bad = 1;
         wt_exec_shutdown();
         logf(bad ? "[FAIL] gehtp_run overall" : "[PASS] gehtp_run overall");
         return bad;
@@ -212,6 +234,7 @@ int mode_job(const std::string& job_path) {
     logf("[run] seg_us read=%lld exec=%lld write=%lld", (long long)(t_read1 - t_read0), (long long)wall, (long long)(now_us() - t_w0));
     if (!ok) logf("[FAIL] out temp %u empty or %s unwritable", out_temp, out_p);
     else logf("[out] %u bytes -> %s", wt_exec_temp_last_bytes(out_temp), out_p);
+    if (ok && !state_file_save(L.blob, state_p)) ok = false;
     wt_exec_shutdown();
     logf(ok ? "[PASS] gehtp_run overall" : "[FAIL] gehtp_run overall");
     return ok ? 0 : 1;

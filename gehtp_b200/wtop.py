@@ -195,6 +195,8 @@ def bind(lib):
         lib.gehtp_cuda_state_load.argtypes = [P(WtBlob), c.c_uint32, c.c_void_p, c.c_size_t, c.c_int, c.c_uint32, c.c_uint32, c.c_char_p, c.c_size_t]
         lib.gehtp_cuda_state_set_count.argtypes = [c.c_uint32, c.c_uint32]
         lib.gehtp_cuda_state_read.argtypes = [c.c_uint32, c.c_void_p, c.c_size_t]
+        lib.gehtp_cuda_state_save_hds1.argtypes = [P(WtBlob), c.c_char_p, c.c_char_p, c.c_size_t]
+        lib.gehtp_cuda_state_load_hds1.argtypes = [P(WtBlob), c.c_char_p, c.c_char_p, c.c_size_t]
         lib.gehtp_cuda_tp_init.argtypes = [c.c_int, c.c_int, c.c_void_p, c.c_size_t]
         lib.gehtp_cuda_tp_unique_id.argtypes = [c.c_void_p, c.c_size_t]
         lib.gehtp_cuda_tp_allreduce_after.argtypes = [P(c.c_uint32), c.c_uint32]
@@ -275,3 +277,15 @@ class Engine:
 
     def state_reset(self):
         self.lib.wt_exec_state_reset()
+
+    def state_save_hds1(self, path):
+        """Writes the 42-state decode table as an "HDS1" file (compiler/src/ops/host_decode_state.cpp:41-62)."""
+        if self.lib.gehtp_cuda_state_save_hds1(ctypes.byref(self.blob), str(path).encode(), self._err, 256) != 0:
+            raise EngineError(-1, self._err.value.decode(errors="replace"))
+
+    def state_load_hds1(self, path):
+        """Returns 0 (loaded) or 1 (no such file); raises on a bad file or a state table of another shape."""
+        rc = self.lib.gehtp_cuda_state_load_hds1(ctypes.byref(self.blob), str(path).encode(), self._err, 256)
+        if rc < 0:
+            raise EngineError(-1, self._err.value.decode(errors="replace"))
+        return rc

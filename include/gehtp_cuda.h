@@ -181,6 +181,19 @@ int gehtp_cuda_state_load(const struct wt_blob* b, uint32_t idx, const void* src
 int gehtp_cuda_state_set_count(uint32_t idx, uint32_t n_positions);
 int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes);
 
+/* State file in the layout of the reference's host golden (magic "HDS1";
+ * host_decode_state_save / _load, compiler/src/ops/host_decode_state.cpp:14-62):
+ *   "HDS1", u32 n = 42, u32 kv_count[6], f32 kv_k[6][64][512], f32 kv_v[6][64][512],
+ *   f32 conv_win[18][3*6144], f32 delta_s[18][16*128*128]
+ * (compiler/include/hnnx/host_decode_state.hpp:17-27). The blob's state table must be the
+ * 42-state decode table: KV rings 0..5 with 512 values per face, conv windows 6..23, delta
+ * states 24..41 (decode_state_gid, compiler/tools/wtop_ops/wtop_ops.hpp:478-492). KV faces
+ * are fp16 on the device and fp32 in the file; positions 0..count-1 are exchanged.
+ * save: 0 or -1. load: 0 loaded, 1 no such file, -1 bad file or table (states untouched),
+ * the return values of host_decode_state_load. */
+int gehtp_cuda_state_save_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn);
+int gehtp_cuda_state_load_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn);
+
 /* ------------------------------------------------------- W4A16 group-64
  * Weight slot form accepted by opcode 1 on this executor (the reference's
  * opcode 1 is an HMX-specific integer contract found by slot size,
