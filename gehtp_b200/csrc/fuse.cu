@@ -124,7 +124,8 @@ Rope match_rope(const Graph& G, int add_op) {
 }
 
 struct Span {
-    int kind;                // 0 decode attention, 1 swiglu, 2 add+norm, 3 rotary, 4 prefill attention
+    int kind;                // 0 decode attention, 1 swiglu, 2 add+norm, 3 rotary, 4 prefill attention,
+                             // 5 prefill split + rotary of q|k|v, 6 swiglu tail behind two GEMMs
     uint32_t first, count;
     std::vector<uint32_t> ops;
     // attention
@@ -140,6 +141,10 @@ struct Span {
     // decode attention: index of the W4A16 q|k|v projection when it sits right before the chain and
     // nothing but the chain reads its output (its epilogue can then do the rotary + append), else -1
     int qkv_lin = -1;
+    // kind 5, split + rotary of a prefill block: qkv in, q_out / k_out / v_out, B = tokens
+    // kind 6, SwiGLU around two GEMMs: ops gate_op and up_op keep their launches, a_ref/y as kind 1, n values
+    uint32_t k_out, v_out, gate_op, up_op, gate_t, up_t;
+    std::vector<uint32_t> keep;   // ops inside the span whose outputs stay materialised (besides the last)
 };
 
 bool contiguous(std::vector<uint32_t>& ops, uint32_t& first) {
@@ -349,6 +354,64 @@ bool match_swiglu(const Graph& G, uint32_t ip, Span& sp) {
     return true;
 }
 
+// SPLIT(qkv, 0) -> rotary chain, SPLIT(qkv, 1) -> rotary chain, SPLIT(qkv, 2): the 17 consecutive
+// ops between the q|k|v projection and the attention chain of a prefill block. `i` is the first SPLIT.
+bool match_qkv_split_rope(const Graph& G, const std::vector<PlanOp>& meas, uint32_t i, Span& sp) {
+    const wt_blob* b = G.b;
+    if (i + 17 > b->n_ops) return false;
+    const wt_op &s0 = b->ops[i], &s1 = b->ops[i + 8], &s2 = b->ops[i + 16];
+    auto split_ok = [&](const wt_op& s, uint32_t idx) {
+        return s.opcode == OP_SPLIT_F16 && s.args[0] == s0.args[0] && s.args[10] == 3 && s.args[15] == idx &&
+               s.args[11] == s0.args[11] && s.args[12] == s0.args[12] && s.args[13] == s0.args[13];
+    };
+    if (!split_ok(s0, 0) || !split_ok(s1, 1) || !split_ok(s2, 2) || !is_temp_ref(s0.args[0])) return false;
+    Rope ra = match_rope(G, (int)i + 7), rb = match_rope(G, (int)i + 15);
+    if (!ra.ok || !rb.ok || ra.hd != rb.hd || (ra.hd & 3u)) return false;
+    const uint32_t hd = ra.hd, wq = s0.args[11], wk = s0.args[12];
+    if (s0.args[13] != wk || wq % hd || wk % hd || !wk || !wq) return false;
+    if (ra.x != s0.args[1] || rb.x != s1.args[1] || ra.src_op != (int)i || rb.src_op != (int)i + 8) return false;
+    if (meas[i].out_bytes[0] % (wq * 2u)) return false;
+    const uint32_t tokens = meas[i].out_bytes[0] / (wq * 2u);
+    if (!tokens || ra.rows != tokens * (wq / hd) || rb.rows != tokens * (wk / hd) ||
+        meas[i + 8].out_bytes[0] != tokens * wk * 2u || meas[i + 16].out_bytes[0] != tokens * wk * 2u) return false;
+    std::vector<uint32_t> ops = {i, i + 8, i + 16};
+    ops.insert(ops.end(), ra.ops.begin(), ra.ops.end());
+    ops.insert(ops.end(), rb.ops.begin(), rb.ops.end());
+    uint32_t first;
+    if (!contiguous(ops, first) || ops.size() != 17 || first != i || !closed(G, ops, {i + 7, i + 15, i + 16})) return false;
+    sp.kind = 5; sp.first = i; sp.count = 17; sp.ops = ops; sp.keep = {i + 7, i + 15};
+    sp.qkv = s0.args[0]; sp.cos_q = ra.cos_b; sp.sin_q = ra.sin_b; sp.cos_k = rb.cos_b; sp.sin_k = rb.sin_b;
+    sp.q_out = b->ops[i + 7].args[2]; sp.k_out = b->ops[i + 15].args[2]; sp.v_out = s2.args[1];
+    sp.B = tokens; sp.nh = wq / hd; sp.kvh = wk / hd; sp.hd = hd;
+    return true;
+}
+
+// The SwiGLU chain of match_swiglu with more rows than the fused GEMV form takes: the two
+// projections keep their own launches (GEMMs) and the three elementwise ops become one kernel.
+bool match_swiglu_tail(const Graph& G, uint32_t ip, Span& sp) {
+    const wt_blob* b = G.b;
+    const wt_op& pr = b->ops[ip];
+    if (pr.opcode != OP_BINARY_F16 || pr.args[4] != 2) return false;
+    int act = G.producer_of_arg[0][ip], up = G.producer_of_arg[1][ip];
+    if (act < 0 || up < 0 || b->ops[act].opcode != OP_BINARY_F16 || b->ops[act].args[4] != 2 || b->ops[up].opcode != OP_MATMUL_W4A16) return false;
+    int gate = G.producer_of_arg[0][act], sig = G.producer_of_arg[1][act];
+    if (gate < 0 || sig < 0 || b->ops[gate].opcode != OP_MATMUL_W4A16 || b->ops[sig].opcode != OP_UNARY_F16 || b->ops[sig].args[3] != 8) return false;
+    if (G.producer_of_arg[0][sig] != gate) return false;
+    const wt_op &gt = b->ops[gate], &u = b->ops[up];
+    if (gt.args[3] != u.args[3] || gt.args[5] != u.args[5]) return false;
+    const uint64_t n64 = (uint64_t)gt.args[3] * gt.args[5];
+    const uint32_t n = (uint32_t)n64;
+    if (n64 > 0xFFFFFFFFull || gt.args[3] <= 64 || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
+    if (!is_temp_ref(gt.args[2]) || !is_temp_ref(u.args[2]) || !is_temp_ref(pr.args[2])) return false;
+    std::vector<uint32_t> ops = {(uint32_t)gate, (uint32_t)sig, (uint32_t)act, (uint32_t)up, ip};
+    uint32_t first;
+    if (!contiguous(ops, first) || !closed(G, ops, {ip})) return false;
+    sp.kind = 6; sp.first = first; sp.count = 5; sp.ops = ops; sp.keep = {(uint32_t)gate, (uint32_t)up};
+    sp.gate_op = (uint32_t)gate; sp.up_op = (uint32_t)up; sp.gate_t = gt.args[2]; sp.up_t = u.args[2];
+    sp.a_ref = gt.args[0]; sp.y = pr.args[2]; sp.n = n;
+    return true;
+}
+
 bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
     const wt_blob* b = G.b;
     if (i + 1 >= b->n_ops) return false;
@@ -407,11 +470,15 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
     }
     for (uint32_t i = 0; i < b->n_ops; i++) {
         Span sp{};
+        if (!taken[i] && b->ops[i].opcode == OP_SPLIT_F16 && match_qkv_split_rope(G, meas, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        Span sp{};
         if (!taken[i] && b->ops[i].opcode == OP_ADD_F16 && match_rope_span(G, i, sp)) claim(sp);
     }
     for (uint32_t i = 0; i < b->n_ops; i++) {
         Span sp{};
-        if (!taken[i] && b->ops[i].opcode == OP_BINARY_F16 && match_swiglu(G, i, sp)) claim(sp);
+        if (!taken[i] && b->ops[i].opcode == OP_BINARY_F16 && (match_swiglu(G, i, sp) || match_swiglu_tail(G, i, sp))) claim(sp);
     }
     for (uint32_t i = 0; i + 1 < b->n_ops; i++) {
         Span sp{};
@@ -427,6 +494,7 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
         if (sp.kind == 0)                                   // the rotated q is kept as the attention kernel's input
             for (uint32_t o : sp.ops)
                 if (meas[o].out_id[0] == sp.q_out) interior[o] = 0;
+        for (uint32_t o : sp.keep) interior[o] = 0;
     }
     for (uint32_t i = 0; i < b->n_ops; i++)
         for (int k = 0; k < 2; k++) {
@@ -449,6 +517,8 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
         case 2: return t == sp.add_a || t == sp.add_b;
         case 3: return t == sp.a_ref || t == sp.cos_q || t == sp.sin_q;
         case 4: return t == sp.pq || t == sp.pk || t == sp.pv || (!sp.mask_is_slot && t == sp.mask);
+        case 5: return t == sp.qkv || t == sp.cos_q || t == sp.sin_q || t == sp.cos_k || t == sp.sin_k;
+        case 6: return t == sp.a_ref;
         }
         return true;
     };
@@ -553,6 +623,25 @@ void fuse_materialize(const wt_blob* b) {
             if (!x || !ct || !stb || !y || ((((uintptr_t)x) | ((uintptr_t)ct) | ((uintptr_t)stb) | ((uintptr_t)y)) & 3u)) continue;
             uint32_t rows = sp.M, hd = sp.hd;
             head.fused = [=](cudaStream_t st) { k_rope(st, x, ct, stb, y, rows, hd); };
+        } else if (sp.kind == 5) {
+            const uint16_t* qkv = (const uint16_t*)resolve(b, sp.qkv);
+            const uint16_t *cq = (const uint16_t*)resolve(b, sp.cos_q), *sq = (const uint16_t*)resolve(b, sp.sin_q);
+            const uint16_t *ck = (const uint16_t*)resolve(b, sp.cos_k), *sk = (const uint16_t*)resolve(b, sp.sin_k);
+            uint16_t *qo = (uint16_t*)resolve(b, sp.q_out), *ko = (uint16_t*)resolve(b, sp.k_out), *vo = (uint16_t*)resolve(b, sp.v_out);
+            if (!qkv || !cq || !sq || !ck || !sk || !qo || !ko || !vo) continue;
+            if ((((uintptr_t)qkv) | ((uintptr_t)cq) | ((uintptr_t)sq) | ((uintptr_t)ck) | ((uintptr_t)sk) | ((uintptr_t)qo) |
+                 ((uintptr_t)ko) | ((uintptr_t)vo)) & 3u) continue;
+            uint32_t tokens = sp.B, nh = sp.nh, kvh = sp.kvh, hd = sp.hd;
+            head.fused = [=](cudaStream_t st) { k_qkv_split_rope(st, qkv, cq, sq, ck, sk, qo, ko, vo, tokens, nh, kvh, hd); };
+        } else if (sp.kind == 6) {
+            const PlanOp &pg = g.plan[sp.gate_op], &pu = g.plan[sp.up_op];
+            const uint16_t *gt = (const uint16_t*)resolve(b, sp.gate_t), *up = (const uint16_t*)resolve(b, sp.up_t);
+            uint16_t* y = (uint16_t*)resolve(b, sp.y);
+            if (!pg.launch || !pu.launch || pg.rc || pu.rc || !gt || !up || !y) continue;
+            if ((((uintptr_t)gt) | ((uintptr_t)up) | ((uintptr_t)y)) & 15u) continue;
+            auto lg = pg.launch, lu = pu.launch;
+            size_t n = sp.n;
+            head.fused = [=](cudaStream_t st) { lg(st); lu(st); k_swiglu_tail(st, gt, up, y, n); };
         } else if (sp.kind == 4) {
             const uint16_t *q = (const uint16_t*)resolve(b, sp.pq), *k = (const uint16_t*)resolve(b, sp.pk),
                            *v = (const uint16_t*)resolve(b, sp.pv);

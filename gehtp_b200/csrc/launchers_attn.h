@@ -55,4 +55,13 @@ uint32_t attn_prefill_tile();
 void k_rope(cudaStream_t st, const uint16_t* x, const uint16_t* cos_t, const uint16_t* sin_t, uint16_t* out,
             uint32_t rows, uint32_t hd);
 
+// SPLIT q / rotary / SPLIT k / rotary / SPLIT v of a prefill block in one pass: qkv is [tokens][q | k | v],
+// the tables are [tokens * heads][hd]; q_out [tokens][nh*hd], k_out and v_out [tokens][kvh*hd].
+void k_qkv_split_rope(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_q, const uint16_t* sin_q,
+                      const uint16_t* cos_k, const uint16_t* sin_k, uint16_t* q_out, uint16_t* k_out, uint16_t* v_out,
+                      uint32_t tokens, uint32_t nh, uint32_t kvh, uint32_t hd);
+// y = fp16(fp16(gate * fp16(sigmoid(gate))) * up), elementwise over n values (16-byte aligned operands).
+void k_swiglu_tail(cudaStream_t st, const uint16_t* gate, const uint16_t* up, uint16_t* y, size_t n);
+
+
 }  // namespace gehtp

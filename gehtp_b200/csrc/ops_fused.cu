@@ -103,4 +103,88 @@ void k_rope(cudaStream_t st, const uint16_t* x, const uint16_t* cos_t, const uin
     g_launches++;
 }
 
+// Prefill form of the head of the attention block: SPLIT q, rotary chain on q, SPLIT k, rotary
+// chain on k, SPLIT v (17 ops) in one pass over the projection's [tokens][q | k | v] rows.
+// cos/sin tables are [tokens * heads][hd], as the chain's BINARY mul ops take them.
+__global__ void qkv_split_rope_kernel(const uint16_t* qkv, const uint16_t* __restrict__ cos_q,
+                                      const uint16_t* __restrict__ sin_q, const uint16_t* __restrict__ cos_k,
+                                      const uint16_t* __restrict__ sin_k, uint16_t* __restrict__ q_out,
+                                      uint16_t* __restrict__ k_out, uint16_t* __restrict__ v_out, uint32_t tokens,
+                                      uint32_t nh, uint32_t kvh, uint32_t hd) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t h = hd / 2, wq = nh * hd, wk = kvh * hd, W = wq + 2 * wk;
+    const size_t n = (size_t)tokens * W;
+    for (size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2; e < n; e += (size_t)gridDim.x * blockDim.x * 2) {
+        const uint32_t t = (uint32_t)(e / W), c = (uint32_t)(e % W);
+        const uint32_t xv = *(const uint32_t*)(qkv + e);
+        if (c >= wq + wk) {
+            *(uint32_t*)(v_out + (size_t)t * wk + (c - wq - wk)) = xv;
+            continue;
+        }
+        const bool is_q = c < wq;
+        const uint32_t cc = is_q ? c : c - wq, d = cc % hd;
+        const size_t o = (size_t)t * (is_q ? wq : wk) + cc;
+        const uint32_t pv = *(const uint32_t*)(qkv + (d < h ? e + h : e - h));
+        const uint32_t cv = *(const uint32_t*)((is_q ? cos_q : cos_k) + o), sv = *(const uint32_t*)((is_q ? sin_q : sin_k) + o);
+        uint16_t r[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const float xf = h2f((uint16_t)(xv >> (16 * k))), pf = h2f((uint16_t)(pv >> (16 * k)));
+            const float rot = d < h ? -pf : pf;
+            const float xc = h2f(f2h(__fmul_rn(xf, h2f((uint16_t)(cv >> (16 * k))))));
+            const float xs = h2f(f2h(__fmul_rn(rot, h2f((uint16_t)(sv >> (16 * k))))));
+            r[k] = f2h(__fadd_rn(xc, xs));
+        }
+        *(uint32_t*)((is_q ? q_out : k_out) + o) = (uint32_t)r[0] | ((uint32_t)r[1] << 16);
+    }
+}
+
+void k_qkv_split_rope(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_q, const uint16_t* sin_q,
+                      const uint16_t* cos_k, const uint16_t* sin_k, uint16_t* q_out, uint16_t* k_out, uint16_t* v_out,
+                      uint32_t tokens, uint32_t nh, uint32_t kvh, uint32_t hd) {
+    const size_t n = (size_t)tokens * (nh + 2 * kvh) * hd;
+    if (!n) return;
+    size_t grid = (n / 2 + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    launch_pdl(qkv_split_rope_kernel, dim3((unsigned)grid), dim3(256), 0, st, qkv, cos_q, sin_q, cos_k, sin_k, q_out, k_out, v_out,
+               tokens, nh, kvh, hd);
+    g_launches++;
+}
+
+// Elementwise tail of a SwiGLU whose projections run as GEMMs (more rows than the fused
+// GEMV form takes): UNARY sigmoid of the gate, BINARY mul gate * sigmoid, BINARY mul by the
+// up projection, each rounded to fp16 as the three ops round.
+__global__ void swiglu_tail_kernel(const uint16_t* gate, const uint16_t* up, uint16_t* __restrict__ y, size_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    auto one = [](uint16_t gh, uint16_t uh) {
+        const float gt = h2f(gh);
+        const float sg = h2f(f2h(1.0f / (1.0f + expf(-gt))));
+        const float act = h2f(f2h(__fmul_rn(gt, sg)));
+        return f2h(__fmul_rn(act, h2f(uh)));
+    };
+    const size_t n8 = n / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 gv = *((const uint4*)gate + i), uv = *((const uint4*)up + i);
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            r[k] = (uint32_t)one((uint16_t)gw[k], (uint16_t)uw[k]) | ((uint32_t)one((uint16_t)(gw[k] >> 16), (uint16_t)(uw[k] >> 16)) << 16);
+        *((uint4*)y + i) = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    if (blockIdx.x == 0)
+        for (size_t i = n8 * 8 + threadIdx.x; i < n; i += blockDim.x) y[i] = one(gate[i], up[i]);
+}
+
+void k_swiglu_tail(cudaStream_t st, const uint16_t* gate, const uint16_t* up, uint16_t* y, size_t n) {
+    if (!n) return;
+    size_t grid = (n / 8 + 255) / 256;
+    if (grid < 1) grid = 1;
+    if (grid > 148 * 16) grid = 148 * 16;
+    launch_pdl(swiglu_tail_kernel, dim3((unsigned)grid), dim3(256), 0, st, gate, up, y, n);
+    g_launches++;
+}
+
 }  // namespace gehtp

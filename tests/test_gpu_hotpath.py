@@ -261,8 +261,9 @@ def test_prefill_runlist_matches_reference(cuda, ref, seq):
         eng.shutdown()
     assert_fp16_close(outs[0], outs[1], "prefill logits")
     assert (outs[0].argmax(1) == outs[1].argmax(1)).mean() > 0.9
-    # 2 layers x (2 rotary chains of 7 ops + 1 attention chain of 9 ops) must have been replaced
-    assert cuda.gehtp_cuda_fused_ops() >= 2 * (2 * 7 + 9)
+    # 2 layers x (3 splits + 2 rotary chains of 7 ops in one kernel, the attention chain of 9 ops, the 5-op
+    # SwiGLU: one GEMV up to 64 rows, two GEMMs + one elementwise kernel beyond) must have been replaced
+    assert cuda.gehtp_cuda_fused_ops() >= 2 * (17 + 9 + 5)
     # and the op-by-op plan gives the same answer within the same gate
     cuda.gehtp_cuda_set_fusion(0)
     eng = Engine(cuda, buf_w4)
@@ -271,6 +272,41 @@ def test_prefill_runlist_matches_reference(cuda, ref, seq):
     eng.shutdown()
     cuda.gehtp_cuda_set_fusion(1)
     assert_fp16_close(outs[0], unfused, "fused vs op-by-op prefill")
+
+
+@pytest.mark.parametrize("tokens", [70, 133])
+def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens):
+    """The head of a prefill block (3 SPLITs + 2 rotary chains, 17 ops, one kernel) and a SwiGLU over
+    more than 64 rows (two GEMMs + one elementwise kernel for the 3 elementwise ops) keep every fp16
+    rounding point of the ops they replace: fused and op-by-op plans agree bit for bit."""
+    from gehtp_b200.runlists import Emitter, rand_w4, rope_tables
+    rng = np.random.default_rng(31)
+    H, nh, kvh, hd, F = 256, 4, 2, 128, 512
+    e = Emitter("w4")
+    face = e.b.add_ext_in(tokens * H * 2)
+    cos, sin = rope_tables(hd, np.arange(tokens), 1e6)
+    cq, sq = (S(e.b.add_slot(np.repeat(t, nh, axis=0))) for t in (cos, sin))
+    ck, sk = (S(e.b.add_slot(np.repeat(t, kvh, axis=0))) for t in (cos, sin))
+    qkv = e.linear(S(face), *rand_w4(rng, H, (nh + 2 * kvh) * hd), tokens)
+    sizes = [nh * hd, kvh * hd, kvh * hd]
+    q = e.rope(e.split(qkv, sizes, 0), tokens * nh, hd, cq, sq)
+    k = e.rope(e.split(qkv, sizes, 1), tokens * kvh, hd, ck, sk)
+    v = e.split(qkv, sizes, 2)
+    d = e.swiglu(S(face), tokens, rand_w4(rng, H, F), rand_w4(rng, H, F), rand_w4(rng, F, H))
+    buf = e.b.build()
+    x = rng.standard_normal((tokens, H)).astype(np.float16)
+    res = []
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        eng.run_io(x, d, None)
+        res.append([eng.temp(t, np.uint16).copy() for t in (q, k, v, d)])
+        if fusion:
+            assert cuda.gehtp_cuda_fused_ops() == 17 + 5
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    for a, b2, name in zip(res[0], res[1], "qkvd"):
+        assert a.size and np.array_equal(a, b2), name
 
 
 def test_gdn_layer_runlist_matches_reference(cuda, ref):
