@@ -178,6 +178,10 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     Barriers* bars = (Barriers*)(sRaw + RSTAGES * RAW_SLOT);
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
+    // Programmatic dependent launch: the set-up below, the weight copies and the dequantisation
+    // of the first k blocks (constants, independent of the predecessor) run while the predecessor
+    // drains; only the A loads and the epilogue's global accesses order themselves after it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (M + 128 * MH - 1) / (128 * MH), n_tiles = N / BN;
     const uint32_t tiles = m_tiles * n_tiles;
@@ -205,6 +209,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     if (warp == 0) {
         // ---- A tiles by TMA
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // A is the predecessor's output
             uint32_t it = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
                 const uint32_t m0 = (tile % m_tiles) * (128 * MH);
@@ -271,6 +276,8 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         // ---- epilogue: TMEM lane = output row; a warp may touch lanes (warp % 4) * 32 .. +31
         const uint32_t lane_base = (warp & 3) * 32;
         uint32_t t = 0;
+        // y (and the residual) may be memory the predecessor still reads or writes
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, t++) {
             const uint32_t buf = t % NBUF;
             const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
@@ -434,7 +441,10 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     }
     const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN);
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    w4a16_gemm_sm100_kernel<MH, BN><<<grid, NTHREADS, smem, st>>>(tmap, (const uint4*)packed, sc, y, M, K, N, ep);
+    if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc, y, M, K, N, ep) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
     g_launches++;
     return true;
 }
