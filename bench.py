@@ -44,7 +44,7 @@ def parse_args():
                          "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "gemm512", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -366,6 +366,12 @@ def run_micro(which):
         us, _, flops = w4(M, K, N, 2, n=4)
         out.append({"kernel": "w4a16_gemm_tcgen05", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
                     "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
+    if which == "gemm512":  # one prefill-size GEMM (512 tokens, q|k|v of the 0.6B shape) per tile configuration that takes it
+        M, K, N = 512, 1024, 4096
+        for path, name in ((3, "128x128"), (4, "256x128")):
+            us, _, flops = w4(M, K, N, path, n=4)
+            out.append({"kernel": "w4a16_gemm_tcgen05", "tile": name, "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
+                        "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
     if which == "lmhead":   # the vocabulary projection alone: a small case for profiler captures
         for M in (1, 8):
             us, nbytes, _ = w4(M, 2560, 151936, 1, False, n=8)
