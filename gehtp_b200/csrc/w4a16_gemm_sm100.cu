@@ -143,7 +143,9 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 slo, __half2 sh
 }
 
 struct __align__(8) Barriers {
-    uint64_t full_a[MAX_STAGES], full_b[MAX_STAGES], empty[MAX_STAGES];
+    // full: one phase per k block, completed by the TMA bytes of the A tile (one expect_tx arrival) and the
+    // arrivals of the four dequant warps that wrote the B tile - the MMA lane polls a single barrier per k block
+    uint64_t full[MAX_STAGES], empty[MAX_STAGES];
     uint64_t raw_full[RSTAGES_MAX], raw_empty[RSTAGES_MAX];
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base, abort_flag;
@@ -188,8 +190,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&bars->full_a[s], 1);
-            mbar_init(&bars->full_b[s], DQ_PER_STAGE);
+            mbar_init(&bars->full[s], 1 + DQ_PER_STAGE);
             mbar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < RSTAGES; s++) { mbar_init(&bars->raw_full[s], 1); mbar_init(&bars->raw_empty[s], DQ_PER_STAGE); }
@@ -216,19 +217,20 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                 for (uint32_t kb = 0; kb < KG; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->empty[s], ph ^ 1)) { *abort_flag = 1; break; }
-                    mbar_expect_tx(&bars->full_a[s], A_BYTES);
+                    mbar_expect_tx(&bars->full[s], A_BYTES);
 #pragma unroll
                     for (int h = 0; h < MH; h++)
-                        tma_load_2d(sA + s * A_BYTES + h * HALF_A_BYTES, &tmap_a, (int)(kb * BK), (int)(m0 + h * 128), &bars->full_a[s]);
+                        tma_load_2d(sA + s * A_BYTES + h * HALF_A_BYTES, &tmap_a, (int)(kb * BK), (int)(m0 + h * 128), &bars->full[s]);
                 }
             }
             if (*abort_flag)   // copies already requested must land before the CTA may go away
-                for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&bars->full_a[j % STAGES], (j / STAGES) & 1);
+                for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&bars->full[j % STAGES], (j / STAGES) & 1);
         }
     } else if (warp == 1) {
         // ---- MMA issue
         if (lane == 0) {
             uint32_t it = 0, t = 0;
+            const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
             for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, t++) {
                 const uint32_t buf = t % NBUF;
                 if (!mbar_wait(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1)) { *abort_flag = 1; break; }
@@ -236,15 +238,17 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                 const uint32_t acc = tmem + buf * ACC_COLS;
                 for (uint32_t kb = 0; kb < KG; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (*abort_flag || !mbar_wait(&bars->full_a[s], ph) || !mbar_wait(&bars->full_b[s], ph)) { *abort_flag = 1; break; }
+                    if (*abort_flag || !mbar_wait(&bars->full[s], ph)) { *abort_flag = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a0 = smem_u32(sA + s * A_BYTES), b0 = smem_u32(sB + s * B_BYTES);
+                    // descriptors of the stage's first K16 slice; the next slices start 32 bytes further
+                    // (the start-address field counts 16-byte units), the second row half HALF_A_BYTES further
+                    const uint64_t da0 = umma_desc(a_base + s * A_BYTES), db0 = umma_desc(b_base + s * B_BYTES);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; k4++) {
-                        const uint64_t db = umma_desc(b0 + k4 * 32);
 #pragma unroll
                         for (int h = 0; h < MH; h++)
-                            umma_f16(acc + h * BN, umma_desc(a0 + h * HALF_A_BYTES + k4 * 32), db, C::IDESC, (kb | k4) ? 1u : 0u);
+                            umma_f16(acc + h * BN, da0 + (uint64_t)(h * (HALF_A_BYTES >> 4) + k4 * 2), db0 + (uint64_t)(k4 * 2), C::IDESC,
+                                     (kb | k4) ? 1u : 0u);
                     }
                     umma_commit(&bars->empty[s]);
                 }
@@ -397,7 +401,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             if (!stage_free) break;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->full_b[s]);
+            if (lane == 0) mbar_arrive(&bars->full[s]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
