@@ -324,4 +324,10 @@ int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int worl
     return 0;
 }
 
+void gehtp_cuda_tp_p2p_disable(void) {
+    if (!p2p.ready) return;
+    p2p.ready = false;
+    if (g.planned) drop_plan(true);
+}
+
 }  // extern "C"

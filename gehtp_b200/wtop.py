@@ -202,6 +202,7 @@ def bind(lib):
         lib.gehtp_cuda_tp_allreduce_after.argtypes = [P(c.c_uint32), c.c_uint32]
         lib.gehtp_cuda_tp_p2p_export.argtypes = [c.c_void_p, c.c_size_t]
         lib.gehtp_cuda_tp_p2p_import.argtypes = [c.c_void_p, c.c_size_t, c.c_int]
+        lib.gehtp_cuda_tp_p2p_disable.restype = None
         lib.gehtp_w4a16_slot_bytes.argtypes = [c.c_uint32, c.c_uint32]
         lib.gehtp_w4a16_slot_bytes.restype = c.c_size_t
         lib.gehtp_w4a16_matmul.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32, c.c_uint32, c.c_int]

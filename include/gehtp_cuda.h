@@ -139,6 +139,9 @@ int gehtp_cuda_tp_allreduce_after(const uint32_t* op_idx, uint32_t n);
  * never arrives makes the run return an error instead of hanging. */
 int gehtp_cuda_tp_p2p_export(void* handle_out, size_t handle_bytes);
 int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int world);
+/* Back to NCCL for every all-reduce (all ranks must agree: call it on every rank when the
+ * export or import failed on any of them). */
+void gehtp_cuda_tp_p2p_disable(void);
 
 /* Kernels launched by the engine since the process started. */
 uint64_t gehtp_cuda_launch_count(void);
