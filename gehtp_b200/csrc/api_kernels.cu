@@ -38,6 +38,7 @@ int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y
     k_w4_repack(g.stream, dslot.as<uint8_t>(), dpk.as<uint32_t>(), K, N);
     const uint16_t* sc = (const uint16_t*)(dslot.as<uint8_t>() + nb);
     W4Epilogue ep;
+    ep.status = g.d_status;
     bool done = false;
     if (path >= 2 || (path == 0 && M >= 128)) {   // 2: tile by shape; 3, 4, 5: 128x128, 256x128, 256x256 tiles
         done = k_w4a16_gemm_sm100(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep, path >= 3 ? path - 2 : 0);
@@ -46,8 +47,7 @@ int gehtp_w4a16_matmul(const uint16_t* a_f16, const uint8_t* w_slot, uint16_t* y
     if (!done) k_w4a16_skinny(g.stream, da.as<uint16_t>(), dpk.as<uint32_t>(), sc, dy.as<uint16_t>(), M, K, N, ep);
     cudaMemcpyAsync(y_f16, dy.p, (size_t)M * N * 2, cudaMemcpyDeviceToHost, g.stream);
     if (finish("w4a16 matmul")) return -1;
-    if (done && w4a16_gemm_timeouts()) return fail("tcgen05 GEMM: a barrier wait ran out");
-    return 0;
+    return read_status(nullptr, 0) ? -1 : 0;
 }
 
 int gehtp_w4a16_unpack(const uint8_t* w_slot, int8_t* out_i8, uint32_t K, uint32_t N) {
@@ -100,7 +100,8 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
     a.part_ml = a.part_o + (size_t)kv_heads * nsplit * rep * head_dim;
     if (!k_attn_decode(g.stream, a, head_dim, dout.as<uint16_t>(), kv_heads)) return fail("attn shape not handled by the fused kernel");
     cudaMemcpyAsync(out, dout.p, q_b, cudaMemcpyDeviceToHost, g.stream);
-    return finish("attn decode");
+    if (finish("attn decode")) return -1;
+    return read_status(nullptr, 0) ? -1 : 0;
 }
 
 }  // extern "C"
@@ -124,6 +125,7 @@ int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, co
     if (!ensure_device(nullptr, 0)) return -1;
     if (!M || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
     W4Epilogue ep;
+    ep.status = g.d_status;
     if (path >= 2 || (path == 0 && M >= 128)) {
         if (k_w4a16_gemm_sm100(g.stream, a_dev, packed_dev, scales_dev, y_dev, M, K, N, ep, path >= 3 ? path - 2 : 0)) return 0;
         if (path >= 2) return fail("tcgen05 GEMM does not take this shape");

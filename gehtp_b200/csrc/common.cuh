@@ -31,9 +31,32 @@ __device__ __forceinline__ double warp_sum_d(double v) {
     return v;
 }
 
+// Codes a kernel leaves in the engine's status word when one of its bounded waits
+// runs out (bit 31 set); any other non-zero value is the 1-based index of an op
+// whose KV gather found a ring slot that holds another position. The host turns
+// the word into the run's error return (status_message, executor.cu).
+constexpr unsigned int kStatusAllReduceTimeout = 0x80000001u;   // peer-memory all-reduce: a rank never wrote
+constexpr unsigned int kStatusAttnTimeout = 0x80000002u;        // decode attention: a K/V tile copy never arrived
+constexpr unsigned int kStatusGemmTimeout = 0x80000003u;        // tcgen05 GEMM: a pipeline barrier never completed
+
 // Device status word: first failing op (1-based) wins.
 __device__ __forceinline__ void raise_status(unsigned int* status, unsigned int code) {
     if (status) atomicCAS(status, 0u, code);
+}
+
+// cudaFuncSetAttribute is per device: remembers, per device ordinal, the largest
+// dynamic shared-memory size a kernel has been opted into, and raises it when needed.
+template <typename K>
+inline bool ensure_dyn_smem(K kernel, size_t bytes, int (&have)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if ((size_t)have[dev] >= bytes) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    have[dev] = (int)bytes;
+    return true;
 }
 
 // Launch with programmatic dependent launch allowed: the grid may start while

@@ -135,6 +135,8 @@ extern Engine g;
 
 // executor.cu
 bool ensure_device(char* err, size_t errn);
+int status_message(unsigned int code, char* msg, size_t msg_bytes);
+int read_status(char* err, size_t errn);   // after a stream sync: 0, or the failed run's return value with last_error set
 // plan.cu
 int build_plan(const wt_blob* b, char* err, size_t errn);
 void drop_plan(bool keep_states);

@@ -12,6 +12,7 @@
 #include <chrono>
 #include <cstring>
 #include <thread>
+#include "common.cuh"
 #include "engine.h"
 #include "launchers_attn.h"
 
@@ -103,12 +104,31 @@ static void hook_dump(uint32_t ii) {
 }
 
 static FILE* g_trace_fp = nullptr;
-static void trace_line(const char* fmt, unsigned a, unsigned b, int c, long long d) {
-    if (!g_trace_fp) {
-        const char* fn = std::getenv("GEHTP_TRACE_FILE");
-        g_trace_fp = std::fopen(fn ? fn : "/tmp/gehtp_optrace.txt", "a");
+// Per-op trace lines in the reference's format (oplist_exec.c:2521-2561):
+//   pre<ii> code=<opcode> a=<arg0>,<arg1>,<arg2>,<arg3> pool=<bytes>     before the op
+//   op<ii> code=<opcode> rc=<rc> us=<host microseconds, -1 without op_us>  after it
+// appended to $GEHTP_TRACE_FILE (default /tmp/gehtp_optrace.txt). The file is reopened when the
+// variable changes.
+static std::string g_trace_name;
+static FILE* trace_file() {
+    const char* fn = std::getenv("GEHTP_TRACE_FILE");
+    const std::string want = fn ? fn : "/tmp/gehtp_optrace.txt";
+    if (g_trace_fp && want != g_trace_name) { std::fclose(g_trace_fp); g_trace_fp = nullptr; }
+    if (!g_trace_fp) { g_trace_fp = std::fopen(want.c_str(), "a"); g_trace_name = want; }
+    return g_trace_fp;
+}
+static void trace_pre(uint32_t ii, const wt_op& op) {
+    if (FILE* f = trace_file()) {
+        std::fprintf(f, "pre%u code=%u a=%u,%u,%u,%u pool=%u\n", ii, (unsigned)op.opcode, op.args[0], op.args[1], op.args[2],
+                     op.args[3], (unsigned)g.arena_bytes);
+        std::fflush(f);
     }
-    if (g_trace_fp) { std::fprintf(g_trace_fp, fmt, a, b, c, d); std::fflush(g_trace_fp); }
+}
+static void trace_post(uint32_t ii, const wt_op& op, int rc, long long us) {
+    if (FILE* f = trace_file()) {
+        std::fprintf(f, "op%u code=%u rc=%d us=%lld\n", ii, (unsigned)op.opcode, rc, us);
+        std::fflush(f);
+    }
 }
 
 static bool hooks_active() {
@@ -187,7 +207,7 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
         const int64_t t0 = now_us();
         int rc = 0;
         uint32_t fail = i;
-        if (g.trace_on) trace_line("pre%u code=%u fused=%d pool=%lld\n", ii, g.blob->ops[i].opcode, use_fused ? 1 : 0, (long long)g.arena_bytes);
+        if (g.trace_on) for (uint32_t k = 0; k < span; k++) trace_pre(ii + k, g.blob->ops[i + k]);
         for (uint32_t k = 0; k < span && !rc; k++) {
             PlanOp& q = g.plan[i + k];
             if (!use_fused && q.uses_internal) return kNeedUnfused;
@@ -230,11 +250,35 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
                 ts.engine = g.plan[i + k].engine;
             }
         }
-        if (g.trace_on) trace_line("op%u code=%u rc=%d us=%lld\n", ii, g.blob->ops[i].opcode, rc, (long long)(t1 - t0));
+        if (g.trace_on)
+            for (uint32_t k = 0; k < span && i + k <= fail; k++)
+                trace_post(ii + k, g.blob->ops[i + k], (rc && i + k == fail) ? rc : 0, op_us ? (long long)op_us[ii + k] : -1);
         if (rc) return (int)fail + 1;
         ii += span;
     }
     return 0;
+}
+
+// Device status word -> error string and return value. A KV gather that found another
+// position in its ring slot leaves the 1-based index of its op, which is also the run's
+// return value (oplist_exec.c:2562); a bounded wait that ran out inside a kernel cannot be
+// pinned on one op and returns -1, the reference's value for engine-level failures (:2504-2506).
+int status_message(unsigned int code, char* m, size_t mn) {
+    switch (code) {
+    case kStatusAllReduceTimeout:
+        std::snprintf(m, mn, "tensor-parallel all-reduce timed out waiting for a peer rank");
+        return -1;
+    case kStatusAttnTimeout:
+        std::snprintf(m, mn, "decode attention timed out waiting for a K/V tile copy");
+        return -1;
+    case kStatusGemmTimeout:
+        std::snprintf(m, mn, "tcgen05 GEMM timed out on a pipeline barrier (output incomplete)");
+        return -1;
+    default:
+        if (code & 0x80000000u) { std::snprintf(m, mn, "device status 0x%08x", code); return -1; }
+        std::snprintf(m, mn, "kv gather miss (state bug) at op %u", code - 1);
+        return (int)code;
+    }
 }
 
 // Ends a run: waits for the stream and turns a device-raised status into the
@@ -247,13 +291,23 @@ static int finish_run(char* err, size_t errn) {
         unsigned int code = *g.h_status;
         *g.h_status = 0;
         cudaMemsetAsync(g.d_status, 0, sizeof(unsigned int), g.stream);
-        char m[96];
-        if (code & 0x80000000u) std::snprintf(m, sizeof m, "tensor-parallel all-reduce timed out waiting for a peer rank");
-        else std::snprintf(m, sizeof m, "kv gather miss (state bug) at op %u", code - 1);
+        char m[128];
+        const int rc = status_message(code, m, sizeof m);
         set_err(err, errn, m);
-        return (int)code;
+        return rc;
     }
     return 0;
+}
+
+int read_status(char* err, size_t errn) {
+    unsigned int code = 0;
+    if (!g.d_status || cudaMemcpy(&code, g.d_status, sizeof code, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (!code) return 0;
+    cudaMemset(g.d_status, 0, sizeof code);
+    char m[128];
+    const int rc = status_message(code, m, sizeof m);
+    set_err(err, errn, m);
+    return rc;
 }
 
 static void stage_inputs(const wt_blob* b, const void* in_host, const void* in_dev) {
@@ -558,6 +612,7 @@ void gehtp_cuda_set_graph(int on) {
 }
 uint64_t gehtp_cuda_launch_count(void) { return g_launches; }
 uint32_t gehtp_cuda_fused_ops(void) { return g.fused_ops; }
+uint32_t gehtp_cuda_demoted_temps(void) { return g.demoted_temps; }
 void* gehtp_cuda_stream(void) { return ensure_device(nullptr, 0) ? (void*)g.stream : nullptr; }
 void* gehtp_cuda_temp_dev(uint32_t id) { return (id < kMaxTemps && g.temp_cap[id]) ? g.temp_dev[id] : nullptr; }
 int gehtp_cuda_sync(void) {
@@ -566,6 +621,12 @@ int gehtp_cuda_sync(void) {
     return (int)cudaStreamSynchronize(g.stream);
 }
 const char* gehtp_cuda_last_error(void) { return g.last_error.c_str(); }
+int gehtp_cuda_status_message(uint32_t code, char* msg, size_t msg_bytes) {
+    char m[128];
+    const int rc = status_message(code, m, sizeof m);
+    if (msg && msg_bytes) std::snprintf(msg, msg_bytes, "%s", m);
+    return rc;
+}
 // Eager run with a CUDA event pair around every launch unit; op_ms[i] gets the
 // device time of the unit that starts at op i (0 for ops inside a fused unit).
 int gehtp_cuda_run_profiled(const struct wt_blob* b, const void* in_ptr, uint32_t out_temp, float* op_ms,

@@ -17,6 +17,7 @@ namespace gehtp {
 struct W4Epilogue {
     int mode = 0;
     const uint16_t* res = nullptr;
+    unsigned int* status = nullptr;   // engine status word: the tcgen05 GEMM reports a barrier wait that ran out here
     // mode 2
     const uint16_t *cos_q = nullptr, *sin_q = nullptr, *cos_k = nullptr, *sin_k = nullptr;   // [M*heads][hd]
     uint16_t *q_out = nullptr, *ring = nullptr;
@@ -62,8 +63,5 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,
                         const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
                         const W4Epilogue& ep, int tile = 0);
-
-// CTAs of the tcgen05 GEMM that gave up on a barrier since the process started (0 in a healthy run).
-unsigned int w4a16_gemm_timeouts();
 
 }  // namespace gehtp

@@ -482,7 +482,6 @@ constexpr int TMA_NW = 4;
 constexpr int TMA_STAGE_B = 2 * TMA_NW * 2 * TMA_BOX_B;   // K,V x heads x halves = 32 KB
 constexpr int TMA_STAGES = 3;
 constexpr uint32_t TMA_SPIN = 4u * 1000u * 1000u;
-constexpr unsigned int kStatusAttnTimeout = 0x80000002u;
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
@@ -861,44 +860,39 @@ void attn_prof_end(float* total_ms, uint32_t* launches) {
 bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16_t* out, uint32_t kv_heads_total) {
     if (a.rep == 0 || a.rep > 16 || (hd != 128 && hd != 64)) return false;
     if (!a.nsplit) return false;
+    // the opt-in to large dynamic shared memory is per device: one record per device ordinal
+    static int have_tma[64] = {}, have_group[64] = {}, have_s128[64] = {}, have_s64[64] = {};
+    bool ok = true;
+    const uint32_t merge_tile = (hd == 128 && kv_heads_total % 4 == 0) ? 16u : (uint32_t)TILE;
     if (hd == 128 && kv_heads_total % 4 == 0) {
-        if (const CUtensorMap* tm = ring_tensor_map(a.ring, a.nslots, a.kv_heads * hd, a.no_cache != 0)) {
-            const size_t tsmem = 1024 + (size_t)TMA_STAGES * TMA_STAGE_B + 2 * TMA_STAGES * sizeof(uint64_t);
-            static bool tattr = false;
-            if (!tattr) { cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem); tattr = true; }
+        const CUtensorMap* tm = ring_tensor_map(a.ring, a.nslots, a.kv_heads * hd, a.no_cache != 0);
+        const size_t tsmem = 1024 + (size_t)TMA_STAGES * TMA_STAGE_B + 2 * TMA_STAGES * sizeof(uint64_t);
+        if (tm && ensure_dyn_smem(attn_decode_tma_kernel, tsmem, have_tma)) {
             cudaEvent_t pe0 = nullptr, pe1 = nullptr;
             if (g_attn_prof) { cudaEventCreate(&pe0); cudaEventCreate(&pe1); cudaEventRecord(pe0, st); }
-            launch_pdl(attn_decode_tma_kernel, dim3((kv_heads_total / 4) * a.nsplit), dim3((TMA_NW + 1) * 32), tsmem, st, *tm, a, kv_heads_total);
+            ok = launch_pdl(attn_decode_tma_kernel, dim3((kv_heads_total / 4) * a.nsplit), dim3((TMA_NW + 1) * 32), tsmem, st, *tm, a, kv_heads_total) == cudaSuccess;
             if (g_attn_prof) { cudaEventRecord(pe1, st); g_attn_prof_events.emplace_back(pe0, pe1); }
-            launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
-                       (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, 16u);
-            g_launches += 2;
-            return true;
+        } else {
+            const size_t gsmem = (size_t)3 * 2 * 4 * 16 * hd * 2;
+            if (!ensure_dyn_smem(attn_decode_group_kernel<128, 4>, gsmem, have_group)) return false;
+            ok = launch_pdl(attn_decode_group_kernel<128, 4>, dim3((kv_heads_total / 4) * a.nsplit), dim3(128), gsmem, st, a, kv_heads_total) == cudaSuccess;
         }
-        size_t gsmem = (size_t)3 * 2 * 4 * 16 * hd * 2;
-        uint32_t ggrid = (kv_heads_total / 4) * a.nsplit;
-        static bool gattr = false;
-        if (!gattr) { cudaFuncSetAttribute(attn_decode_group_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsmem); gattr = true; }
-        launch_pdl(attn_decode_group_kernel<128, 4>, dim3(ggrid), dim3(128), gsmem, st, a, kv_heads_total);
-        launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
-                   (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, 16u);
-        g_launches += 2;
-        return true;
-    }
-    size_t smem = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)NWARP * a.rep * (hd + 2) * sizeof(float);
-    uint32_t items = kv_heads_total * a.nsplit;
-    uint32_t grid = items < 2 * 148 ? items : 2 * 148;
-    if (hd == 128) {
-        static size_t attr = 0;
-        if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
-        launch_pdl(attn_decode_split_kernel<128>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total);
     } else {
-        static size_t attr = 0;
-        if (attr < smem) { cudaFuncSetAttribute(attn_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = smem; }
-        launch_pdl(attn_decode_split_kernel<64>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total);
+        const size_t smem = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)NWARP * a.rep * (hd + 2) * sizeof(float);
+        const uint32_t items = kv_heads_total * a.nsplit;
+        const uint32_t grid = items < 2 * 148 ? items : 2 * 148;
+        if (hd == 128) {
+            if (!ensure_dyn_smem(attn_decode_split_kernel<128>, smem, have_s128)) return false;
+            ok = launch_pdl(attn_decode_split_kernel<128>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total) == cudaSuccess;
+        } else {
+            if (!ensure_dyn_smem(attn_decode_split_kernel<64>, smem, have_s64)) return false;
+            ok = launch_pdl(attn_decode_split_kernel<64>, dim3(grid), dim3(NWARP * 32), smem, st, a, kv_heads_total) == cudaSuccess;
+        }
     }
-    launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
-               (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, (uint32_t)TILE);
+    if (!ok) { cudaGetLastError(); return false; }
+    ok = launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
+                    (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, merge_tile) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); return false; }
     g_launches += 2;
     return true;
 }
@@ -924,6 +918,9 @@ namespace gehtp {
 // at zero: each call writes every partial it later reads.
 constexpr size_t kNoAllocFloats = GEHTP_NOALLOC_SCRATCH_BYTES / sizeof(float);
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+// Status word of the calls below: the kernel's bounded waits report here (kStatusAttnTimeout),
+// read and cleared by gehtp_attn_decode_noalloc_status.
+static __device__ unsigned int g_noalloc_status;
 
 }  // namespace gehtp
 
@@ -947,13 +944,18 @@ extern "C" int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* 
     // The array's name is only a host-side handle; the kernel needs its device
     // address, looked up once per device with that device current.
     static float* scratch_of_device[64] = {};
+    static unsigned int* status_of_device[64] = {};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail("attn noalloc: no current CUDA device");
     if (!scratch_of_device[dev]) {
         float* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
         if (e != cudaSuccess || !p) { cudaGetLastError(); return fail("attn noalloc: cudaGetSymbolAddress failed"); }
+        unsigned int* sp = nullptr;
+        e = cudaGetSymbolAddress((void**)&sp, g_noalloc_status);
+        if (e != cudaSuccess || !sp) { cudaGetLastError(); return fail("attn noalloc: cudaGetSymbolAddress failed"); }
         scratch_of_device[dev] = p;
+        status_of_device[dev] = sp;
     }
     AttnDecodeArgs a{};
     a.q = q_dev; a.ring = ring_dev; a.counter = nullptr; a.n_kv = n_kv; a.n_kv_add = 0; a.bump_counter = nullptr;
@@ -962,8 +964,23 @@ extern "C" int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* 
     a.part_o = scratch_of_device[dev];
     a.part_ml = a.part_o + (size_t)kv_heads * nsplit * rep * head_dim;
     a.no_cache = 1;
+    a.status = status_of_device[dev];
     if (!k_attn_decode((cudaStream_t)stream, a, head_dim, out_dev, kv_heads)) return fail("attn noalloc: launch refused");
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     return 0;
+}
+
+// 0 when no bounded wait of the allocation-free calls on the current device has run out since the last
+// query, else the code it left (and the word is cleared). Copies one word from the device without
+// allocating; call it after the stream the calls were queued on has been synchronised.
+extern "C" int gehtp_attn_decode_noalloc_status(void) {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, gehtp::g_noalloc_status, sizeof v) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (v) {
+        const unsigned int zero = 0;
+        cudaMemcpyToSymbol(gehtp::g_noalloc_status, &zero, sizeof zero);
+        gehtp::g.last_error = "attn noalloc: a K/V tile copy never arrived (bounded wait ran out); the output is incomplete";
+    }
+    return (int)(v & 0x7fffffffu);
 }

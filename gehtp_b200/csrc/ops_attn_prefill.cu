@@ -255,12 +255,12 @@ bool k_attn_prefill(cudaStream_t st, const uint16_t* q, const uint16_t* k, const
     const dim3 grid((seq_q + PF_BQ - 1) / PF_BQ, nh);
     const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * hd * 2;
     if (hd == 128) {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
+        static int have[64] = {};
+        if (!ensure_dyn_smem(attn_prefill_kernel<128>, smem, have)) return false;
         launch_pdl(attn_prefill_kernel<128>, grid, dim3(PF_WARPS * 32), smem, st, a);
     } else {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
+        static int have[64] = {};
+        if (!ensure_dyn_smem(attn_prefill_kernel<64>, smem, have)) return false;
         launch_pdl(attn_prefill_kernel<64>, grid, dim3(PF_WARPS * 32), smem, st, a);
     }
     g_launches++;

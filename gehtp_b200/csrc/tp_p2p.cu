@@ -37,13 +37,13 @@ constexpr size_t kLLSlotBytes = 1u << 20;                     // flag-in-data sl
 constexpr size_t kLLBytes = 2 * kMaxWorld * kLLSlotBytes;
 constexpr size_t kBoxBytes = kDataBytes + kFlagBytes + kLLBytes;
 constexpr uint32_t kSpinLimit = 4u * 1000u * 1000u;           // polls (with a short sleep) before giving up
-constexpr unsigned int kStatusTimeout = 0x80000001u;
 
 struct P2PCtx {
     unsigned char* box[kMaxWorld];   // mailbox of every rank as mapped in this process (own one included)
     uint32_t* epoch;                 // [0] epoch of the last finished all-reduce, [1] CTAs done in this launch
     unsigned int* status;
     int rank, world;
+    uint32_t spin_limit;             // polls before a wait gives up
 };
 
 struct P2PState {
@@ -52,6 +52,8 @@ struct P2PState {
     uint32_t* epoch = nullptr;
     P2PCtx ctx{};
     bool ready = false;
+    unsigned char* loop_box[kMaxWorld] = {};   // loopback bring-up: stand-ins for the peers' mailboxes
+    uint32_t spin_limit = kSpinLimit;
 } p2p;
 
 __device__ __forceinline__ unsigned char* slot_ptr(unsigned char* box, uint32_t bank, int src) {
@@ -87,12 +89,12 @@ p2p_allreduce_kernel(P2PCtx c, const uint4* in, uint4* out, uint32_t vecs) {   /
     if (threadIdx.x < (uint32_t)c.world) {
         const uint32_t* f = flag_ptr(c.box[c.rank], bank, (int)threadIdx.x, blockIdx.x);
         uint32_t seen = 0, it = 0;
-        for (; it < kSpinLimit; it++) {
+        for (; it < c.spin_limit; it++) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
             if ((int32_t)(seen - epoch) >= 0) break;
             __nanosleep(64);
         }
-        if (it == kSpinLimit) raise_status(c.status, kStatusTimeout);
+        if (it == c.spin_limit) raise_status(c.status, kStatusAllReduceTimeout);
     }
     __syncthreads();
     // sum, rank order
@@ -175,7 +177,7 @@ p2p_add_rmsnorm_kernel(P2PCtx c, const uint16_t* a, uint16_t* r, const uint16_t*
             got[q][j] = 0u;
             if (q < c.world && q != c.rank && threadIdx.x + j * BLOCK < words) pending |= 1u << (q * WPT + j);
         }
-    for (uint32_t it = 0; pending && it < kSpinLimit; it++) {
+    for (uint32_t it = 0; pending && it < c.spin_limit; it++) {
         uint2 v[kMaxWorld][WPT];
 #pragma unroll
         for (int q = 0; q < kMaxWorld; q++)
@@ -195,7 +197,7 @@ p2p_add_rmsnorm_kernel(P2PCtx c, const uint16_t* a, uint16_t* r, const uint16_t*
                 }
         if (pending && it > 64) __nanosleep(64);
     }
-    if (pending) raise_status(c.status, kStatusTimeout);
+    if (pending) raise_status(c.status, kStatusAllReduceTimeout);
     // sum in rank order, back into r
 #pragma unroll
     for (int j = 0; j < WPT; j++) {
@@ -262,11 +264,15 @@ bool tp_p2p_allreduce_f16(cudaStream_t st, void* buf, size_t elems) {
 void tp_p2p_shutdown() {
     if (!p2p.my_box) return;
     cudaDeviceSynchronize();
-    for (int r = 0; r < kMaxWorld; r++)
+    for (int r = 0; r < kMaxWorld; r++) {
         if (p2p.peer_base[r]) { cudaIpcCloseMemHandle(p2p.peer_base[r]); p2p.peer_base[r] = nullptr; }
+        if (p2p.loop_box[r]) { cudaFree(p2p.loop_box[r]); p2p.loop_box[r] = nullptr; }
+    }
+    const uint32_t keep_limit = p2p.spin_limit;
     cudaFree(p2p.my_box);
     cudaFree(p2p.epoch);
     p2p = P2PState();
+    p2p.spin_limit = keep_limit;
 }
 
 }  // namespace gehtp
@@ -304,7 +310,7 @@ int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int worl
         return -1;
     }
     P2PCtx c{};
-    c.rank = g.tp_rank; c.world = world; c.epoch = p2p.epoch; c.status = g.d_status;
+    c.rank = g.tp_rank; c.world = world; c.epoch = p2p.epoch; c.status = g.d_status; c.spin_limit = p2p.spin_limit;
     for (int r = 0; r < world; r++) {
         if (r == g.tp_rank) { c.box[r] = p2p.my_box; continue; }
         cudaIpcMemHandle_t h;
@@ -318,6 +324,34 @@ int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int worl
         p2p.peer_base[r] = p;
         c.box[r] = (unsigned char*)p;
     }
+    p2p.ctx = c;
+    p2p.ready = true;
+    if (g.planned) drop_plan(true);
+    return 0;
+}
+
+void gehtp_cuda_set_wait_limit(uint32_t polls) {
+    p2p.spin_limit = polls ? polls : kSpinLimit;
+    p2p.ctx.spin_limit = p2p.spin_limit;
+    if (g.planned) drop_plan(true);   // launches (and a captured graph) carry the limit by value
+}
+
+int gehtp_cuda_tp_p2p_loopback(int world) {
+    if (world < 2 || world > kMaxWorld) { g.last_error = "tp p2p loopback: world must be 2..8"; return -1; }
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (g.nccl_comm || p2p.ready) { g.last_error = "tp p2p loopback: tensor parallelism is already set up"; return -1; }
+    cudaIpcMemHandle_t unused;
+    if (gehtp_cuda_tp_p2p_export(&unused, sizeof unused) != 0) return -1;   // allocates this rank's own mailbox
+    P2PCtx c{};
+    c.rank = 0; c.world = world; c.epoch = p2p.epoch; c.status = g.d_status; c.spin_limit = p2p.spin_limit;
+    c.box[0] = p2p.my_box;
+    for (int r = 1; r < world; r++) {
+        if (cudaMalloc(&p2p.loop_box[r], kBoxBytes) != cudaSuccess) { cudaGetLastError(); g.last_error = "tp p2p loopback: allocation failed"; return -1; }
+        cudaMemset(p2p.loop_box[r], 0, kBoxBytes);
+        c.box[r] = p2p.loop_box[r];
+    }
+    cudaDeviceSynchronize();
+    g.tp_rank = 0; g.tp_world = world;
     p2p.ctx = c;
     p2p.ready = true;
     if (g.planned) drop_plan(true);

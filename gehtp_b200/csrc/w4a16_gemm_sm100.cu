@@ -151,8 +151,6 @@ struct __align__(8) Barriers {
     uint32_t tmem_base, abort_flag;
 };
 
-__device__ unsigned int g_w4gemm_timeouts = 0;   // CTAs that gave up on a barrier
-
 // fp32 pair -> packed fp16 pair with the executor's NaN rule (NaN -> signed infinity)
 __device__ __forceinline__ uint32_t pack_out(float a, float b) {
     return (uint32_t)f2h(a) | ((uint32_t)f2h(b) << 16);
@@ -408,7 +406,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     __syncthreads();
     if (warp == 3) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-        if (lane == 0 && *abort_flag) atomicAdd(&g_w4gemm_timeouts, 1u);
+        if (lane == 0 && *abort_flag) raise_status(ep.status, kStatusGemmTimeout);
     }
 }
 
@@ -435,14 +433,8 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms) {
     using C = Cfg<MH, BN>;
     const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + (size_t)C::RSTAGES * C::RAW_SLOT + sizeof(Barriers) + 16;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(w4a16_gemm_sm100_kernel<MH, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            cudaGetLastError();
-            return false;
-        }
-        attr_set = true;
-    }
+    static int have[64] = {};
+    if (!ensure_dyn_smem(w4a16_gemm_sm100_kernel<MH, BN>, smem, have)) return false;
     const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN);
     const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
     if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc, y, M, K, N, ep) != cudaSuccess) {
@@ -455,12 +447,6 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
 
 }  // namespace
 
-unsigned int w4a16_gemm_timeouts() {
-    unsigned int v = 0;
-    cudaMemcpyFromSymbol(&v, g_w4gemm_timeouts, sizeof v);
-    return v;
-}
-
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
                         uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile) {
     if (!M || K % BK || N % 128) return false;
@@ -468,10 +454,11 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
     if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
-    static int sms = 0;
+    static int sms_of[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int& sms = sms_of[dev & 63];
     if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }

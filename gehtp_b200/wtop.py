@@ -29,6 +29,21 @@ ARITY = {0: 0, 1: 6, 2: 4, 3: 1, 4: 3, 5: 15, 6: 13, 7: 4, 8: 4, 9: 4, 10: 6, 11
          26: 12, 27: 8, 28: 14, 29: 6, 30: 12, 33: 8, 34: 7, 35: 9}
 
 
+# argument positions that name the temp(s) an op writes
+_OUT_ARGS = {1: (2,), 4: (1,), 7: (2,), 10: (1,), 11: (1,), 12: (2,), 13: (1,), 14: (8,), 15: (1,), 16: (1,),
+             17: (1,), 18: (1,), 19: (2,), 20: (2,), 21: (1,), 23: (1, 2), 24: (2,), 25: (3,), 26: (1,),
+             27: (1,), 28: (3,), 29: (2,), 30: (5,), 34: (1,), 35: (2,)}
+
+
+def op_out_temps(op):
+    """Temp ids an op record writes (a parsed `WtOp` or an (opcode, args) pair)."""
+    opcode, args = (op.opcode, list(op.args)) if hasattr(op, "opcode") else op
+    pos = _OUT_ARGS.get(opcode, ())
+    if opcode == OP.BINARY and args[4] == 8:      # SELECT form [cond, a, b, out, 8]
+        pos = (3,)
+    return [args[i] & 0x3FFF for i in pos if not (opcode == OP.KV_GATHER and args[i] == 0)]
+
+
 def S(slot):
     """Reference to a slot in an op argument."""
     return 0x8000 | slot
@@ -181,6 +196,7 @@ def bind(lib):
     if hasattr(lib, "gehtp_cuda_launch_count"):
         lib.gehtp_cuda_launch_count.restype = c.c_uint64
         lib.gehtp_cuda_fused_ops.restype = c.c_uint32
+        lib.gehtp_cuda_demoted_temps.restype = c.c_uint32
         lib.gehtp_cuda_stream.restype = c.c_void_p
         lib.gehtp_cuda_temp_dev.argtypes = [c.c_uint32]
         lib.gehtp_cuda_temp_dev.restype = c.c_void_p
@@ -203,6 +219,11 @@ def bind(lib):
         lib.gehtp_cuda_tp_p2p_export.argtypes = [c.c_void_p, c.c_size_t]
         lib.gehtp_cuda_tp_p2p_import.argtypes = [c.c_void_p, c.c_size_t, c.c_int]
         lib.gehtp_cuda_tp_p2p_disable.restype = None
+        lib.gehtp_cuda_status_message.argtypes = [c.c_uint32, c.c_char_p, c.c_size_t]
+        lib.gehtp_cuda_set_wait_limit.argtypes = [c.c_uint32]
+        lib.gehtp_cuda_set_wait_limit.restype = None
+        lib.gehtp_cuda_tp_p2p_loopback.argtypes = [c.c_int]
+        lib.gehtp_attn_decode_noalloc_status.restype = c.c_int
         lib.gehtp_w4a16_slot_bytes.argtypes = [c.c_uint32, c.c_uint32]
         lib.gehtp_w4a16_slot_bytes.restype = c.c_size_t
         lib.gehtp_w4a16_matmul.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_uint32, c.c_uint32, c.c_uint32, c.c_int]

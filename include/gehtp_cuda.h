@@ -142,11 +142,26 @@ int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int worl
 /* Back to NCCL for every all-reduce (all ranks must agree: call it on every rank when the
  * export or import failed on any of them). */
 void gehtp_cuda_tp_p2p_disable(void);
+/* Number of polls a device-side wait of the peer-memory exchange makes before it gives up,
+ * leaves a code in the engine's status word and lets the run return "all-reduce timed out"
+ * (0 = the default, a few seconds). Every such wait is bounded; this only moves the bound. */
+void gehtp_cuda_set_wait_limit(uint32_t polls);
+/* Bring-up aid for the peer-memory exchange on ONE GPU: this process becomes rank 0 of
+ * `world`, and the other ranks' mailboxes are private buffers on the same GPU that nobody
+ * ever writes. Every exchange therefore runs into its wait limit and the run reports the
+ * timeout: the way to see the failure path of a lost peer without losing one. Undone by
+ * gehtp_cuda_tp_shutdown. Returns 0 or -1. */
+int gehtp_cuda_tp_p2p_loopback(int world);
 
 /* Kernels launched by the engine since the process started. */
 uint64_t gehtp_cuda_launch_count(void);
 /* Number of ops of the current plan replaced by fused launches. */
 uint32_t gehtp_cuda_fused_ops(void);
+/* Number of TEMPOFF entries of the current plan that were moved out of the
+ * static pool because their byte ranges overlap another entry's while both
+ * tensors are live (the emitter binds plan offsets to recycled temp ids,
+ * compiler/tools/wtop_ops/wtop_ops.hpp:143-167). 0 for a sound table. */
+uint32_t gehtp_cuda_demoted_temps(void);
 /* Device pointer / stream the engine uses (so a host that owns device memory,
  * e.g. a bench, can time on the right stream). */
 void* gehtp_cuda_stream(void);
@@ -154,6 +169,12 @@ void* gehtp_cuda_temp_dev(uint32_t id);
 /* Wait for every queued op. Returns 0 or the CUDA error code. */
 int gehtp_cuda_sync(void);
 const char* gehtp_cuda_last_error(void);
+/* How a run reports the word a kernel leaves when it cannot finish: the message that
+ * wt_exec_run* puts into `err` and the value it returns for device status `code` (a 1-based op
+ * index for a KV gather that found another position in its ring slot; -1 with its own message
+ * for each bounded wait that ran out: peer-memory all-reduce 0x80000001, decode-attention tile
+ * copy 0x80000002, tcgen05 GEMM pipeline barrier 0x80000003). Pure host function. */
+int gehtp_cuda_status_message(uint32_t code, char* msg, size_t msg_bytes);
 
 /* Device-resident I/O for hosts that keep buffers on the GPU: like
  * wt_exec_run_io but `in_dev` / `out_dev` are device pointers and nothing is
@@ -287,6 +308,13 @@ int gehtp_cuda_capture_end_replay(int reps, float* ms_per_replay);
 int gehtp_attn_decode_noalloc(const uint16_t* q_dev, const uint16_t* ring_dev, const uint16_t* mask_dev,
                               uint16_t* out_dev, uint32_t n_heads, uint32_t kv_heads, uint32_t head_dim,
                               uint32_t n_kv, uint32_t nslots, float scale, void* stream);
+/* No counterpart in the reference. The kernel behind gehtp_attn_decode_noalloc waits for
+ * its K/V tile copies with a bounded poll; a wait that runs out leaves a code in a status
+ * word that also lives in the library's device image. This reads and clears that word for
+ * the current device (one 4-byte device-to-host copy, no allocation): 0 = every call since
+ * the last query completed, > 0 = a wait ran out and that call's output is incomplete,
+ * -1 = the copy failed. Call it after synchronising the stream the calls were queued on. */
+int gehtp_attn_decode_noalloc_status(void);
 
 #ifdef __cplusplus
 }

@@ -15,9 +15,17 @@ def pytest_configure(config):
 
 
 def _make_oracle():
-    if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")) or (
-            os.path.isdir("/root/reference") and not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libgehtp_ref.so"))):
-        subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, capture_output=True)
+    """Builds the CPU checkers when they are missing. The reference executor can only be built
+    where the reference tree is; its location comes from $GEHTP_REFERENCE_DIR (passed to the
+    Makefile as REF), else the Makefile's own default is tried."""
+    have_orc = os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so"))
+    have_ref = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libgehtp_ref.so"))
+    if have_orc and have_ref:
+        return
+    cmd = ["make", "-C", os.path.join(ROOT, "oracle")]
+    if os.environ.get("GEHTP_REFERENCE_DIR"):
+        cmd.append("REF=" + os.environ["GEHTP_REFERENCE_DIR"])
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 @pytest.fixture(scope="session")
