@@ -104,12 +104,18 @@ def test_pool_init_static_offsets(cuda, ref):
     offs[1], offs[2] = 2048, 0
     want3 = ((-x).astype(np.float16) * x).astype(np.float16)
 
-    pool = np.zeros(1 << 16, np.uint8)
-    ref.wt_exec_pool_init(pool.ctypes.data, pool.size, 4096, offs.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)))
+    # The reference frees the pool in wt_exec_shutdown and only a shutdown initialises its
+    # on-chip offset array when no TEMPOFF slot did: shutdown first, pool from the C allocator.
+    libc = ctypes.CDLL(None)
+    libc.memalign.restype = ctypes.c_void_p
+    libc.memalign.argtypes = [ctypes.c_size_t, ctypes.c_size_t]
+    pool = libc.memalign(128, 1 << 16)
+    ref.wt_exec_shutdown()
+    ref.wt_exec_pool_init(pool, 1 << 16, 4096, offs.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)))
     eng = Engine(ref, buf)
     eng.run()
-    assert ref.wt_exec_temp(1) == pool.ctypes.data + 2048 and ref.wt_exec_temp(2) == pool.ctypes.data
-    assert ref.wt_exec_temp(3) >= pool.ctypes.data + 4096
+    assert ref.wt_exec_temp(1) == pool + 2048 and ref.wt_exec_temp(2) == pool
+    assert ref.wt_exec_temp(3) >= pool + 4096
     assert np.array_equal(eng.temp(3), want3)
     eng.shutdown()
 
