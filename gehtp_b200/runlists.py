@@ -197,13 +197,33 @@ class Emitter:
 
 
 def synth_embedding(rng, V, H):
-    """fp16 ~ N(0, 0.02) [V, H]. Large tables are tiled from a 1024-row block:
-    converting hundreds of millions of floats on the host takes longer than the
-    whole benchmark, and a decode step reads only one row per sequence."""
-    if V <= 4096:
-        return (rng.standard_normal((V, H), dtype=np.float32) * 0.02).astype(np.float16)
-    block = (rng.standard_normal((1024, H), dtype=np.float32) * 0.02).astype(np.float16)
+    """fp16 ~ N(0, 0.02) [V, H]. Tables of more than 1024 rows are tiled from a
+    1024-row block: converting hundreds of millions of floats on the host takes
+    longer than the whole benchmark, and a decode step reads only one row per
+    sequence. Row r is block[r % 1024] whatever V is, so models that differ only
+    in their vocabulary size embed the same id (below 1024) the same way."""
+    block = (rng.standard_normal((min(V, 1024), H), dtype=np.float32) * 0.02).astype(np.float16)
+    if V <= 1024:
+        return block
     return np.tile(block, ((V + 1023) // 1024, 1))[:V]
+
+
+def part_rng(seed, part):
+    """Independent generator per model part (layer index, or a name's number), so that a
+    one-layer or small-vocabulary cut of a model carries the same weights as the whole."""
+    return np.random.default_rng([int(seed), int(part)])
+
+
+EMB_PART, HEAD_PART = 100000, 100001
+
+
+def synth_head(rng, H, V):
+    """Vocabulary projection [H, V] in W4 form. The first 2048 columns are drawn first, the rest
+    after them, so a 2048-column cut of a model is the head of the whole model's projection."""
+    first = rand_w4(rng, H, min(V, 2048))
+    if V <= 2048:
+        return first
+    return hcat(first, rand_w4(rng, H, V - 2048))
 
 
 def cols(w, c0, c1):
@@ -263,7 +283,6 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
     Returns (blob bytes as uint8 array, manifest dict).
     Input face, in fp16-sized units: ids (int32 x B) | cos[hd] | sin[hd] | mask[nslots].
     """
-    rng = np.random.default_rng(seed)
     L = cfg.layers if n_layers is None else n_layers
     V = cfg.vocab if vocab is None else vocab
     H, hd = cfg.hidden, cfg.head_dim
@@ -273,7 +292,7 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
     face_total = ids_u16 + 2 * hd + nslots
     face = e.b.add_ext_in(face_total * 2)
     e.b.add_states([B * kvh * hd * 4 * nslots] * L)
-    emb_s = e.b.add_slot(synth_embedding(rng, V, H))
+    emb_s = e.b.add_slot(synth_embedding(part_rng(seed, EMB_PART), V, H))
 
     ids = e.face(S(face), 0, 2 * B, face_total)
     cos = e.face(S(face), ids_u16, hd, face_total)
@@ -289,8 +308,9 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
     sc = float(np.sqrt(hd)) if scale_div else float(1.0 / np.sqrt(hd))
     scale_b = e.broadcast(e.const_f16(sc), (1, 1, 1, 1), (1, 1, 1, B * nh * nslots))
 
+    layer_out = []
     for li in range(L):
-        w = synth_layer(rng, cfg, tp, rank)
+        w = synth_layer(part_rng(seed, li), cfg, tp, rank)
         h1 = e.rmsnorm(x, w["g1"], B * H)
         qkv = e.linear(h1, *w["qkv"], B)
         sizes = [nh * hd, kvh * hd, kvh * hd]
@@ -313,15 +333,18 @@ def build_decode_runlist(cfg, B, nslots, seed=1004, quant="w4", n_layers=None, w
         h2 = e.rmsnorm(x, w["g2"], B * H)
         d = e.swiglu(h2, B, w["gate"], w["up"], w["down"])
         x = e.binary(x, d, B * H, 0)
+        layer_out.append(x)
 
+    rng = part_rng(seed, HEAD_PART)
     gf = rng.normal(1.0, 0.1, H).astype(np.float16)
     hn = e.rmsnorm(x, gf, B * H)
     man = dict(config=cfg.name, B=B, nslots=nslots, layers=L, hidden=H, face_u16=face_total, ids_u16=ids_u16,
                cos_off=ids_u16, sin_off=ids_u16 + hd, mask_off=ids_u16 + 2 * hd, hidden_temp=hn,
-               input_slot=face, quant=quant, tp=tp, rank=rank)
+               input_slot=face, quant=quant, tp=tp, rank=rank, layer_out=layer_out)
     if with_lm_head:
         Vs = V // tp
-        logits = e.linear(hn, *cols(rand_w4(rng, H, V), rank * Vs, (rank + 1) * Vs), B)
+        # column c of the vocabulary projection is the same whatever V is (drawn in blocks of 2048 columns)
+        logits = e.linear(hn, *cols(synth_head(rng, H, V), rank * Vs, (rank + 1) * Vs), B)
         toks = []
         for bi in range(B):
             row = e.slice2(logits, B, Vs, 0, Vs) if B == 1 else e.fresh()
@@ -371,14 +394,13 @@ def build_prefill_runlist(cfg, seq, seed=1003, quant="w4", n_layers=None, with_l
     """Causal prefill of `seq` tokens, batch 1. Input face: ids int32 x seq.
     cos/sin tables and the causal mask are baked constant slots, as in the
     reference's prefill graphs."""
-    rng = np.random.default_rng(seed)
     L = cfg.layers if n_layers is None else n_layers
     V = cfg.vocab if vocab is None else vocab
     H, hd, nh, kvh = cfg.hidden, cfg.head_dim, cfg.n_heads, cfg.kv_heads
     rep = nh // kvh
     e = Emitter(quant)
     face = e.b.add_ext_in(seq * 4)
-    emb_s = e.b.add_slot(synth_embedding(rng, V, H))
+    emb_s = e.b.add_slot(synth_embedding(part_rng(seed, EMB_PART), V, H))
     cos, sin = rope_tables(hd, np.arange(seq), cfg.rope_theta)
     # rows of q are (token, head): the table row of a (token, head) pair is the token's
     cos_q = S(e.b.add_slot(np.repeat(cos, nh, axis=0)))
@@ -391,8 +413,9 @@ def build_prefill_runlist(cfg, seq, seed=1003, quant="w4", n_layers=None, with_l
     e.b.add_op(OP.GATHER, [S(emb_s), S(face), x, seq * H, 0 | 1 << 8 | 2 << 16, V, H, 1, 1, 1, seq, 1, 1, 1, 1])
     mask_b = e.broadcast(mask_s, (1, 1, seq, seq), (1, nh, seq, seq))
     scale_b = e.broadcast(e.const_f16(1.0 / np.sqrt(hd)), (1, 1, 1, 1), (1, 1, 1, nh * seq * seq))
+    layer_out = []
     for li in range(L):
-        w = synth_layer(rng, cfg)
+        w = synth_layer(part_rng(seed, li), cfg)
         h1 = e.rmsnorm(x, w["g1"], seq * H)
         qkv = e.linear(h1, *w["qkv"], seq)
         sizes = [nh * hd, kvh * hd, kvh * hd]
@@ -413,10 +436,12 @@ def build_prefill_runlist(cfg, seq, seed=1003, quant="w4", n_layers=None, with_l
         h2 = e.rmsnorm(x, w["g2"], seq * H)
         d = e.swiglu(h2, seq, w["gate"], w["up"], w["down"])
         x = e.binary(x, d, seq * H, 0)
+        layer_out.append(x)
+    rng = part_rng(seed, HEAD_PART)
     hn = e.rmsnorm(x, rng.normal(1.0, 0.1, H).astype(np.float16), seq * H)
-    man = dict(config=cfg.name, seq=seq, layers=L, hidden_temp=hn, input_slot=face, quant=quant)
+    man = dict(config=cfg.name, seq=seq, layers=L, hidden_temp=hn, input_slot=face, quant=quant, layer_out=layer_out)
     if with_lm_head:
-        man["logits_temp"] = e.linear(hn, *rand_w4(rng, H, V), seq)
+        man["logits_temp"] = e.linear(hn, *synth_head(rng, H, V), seq)
     man["n_ops"] = len(e.b.ops)
     return e.b.build(), man
 
@@ -430,24 +455,29 @@ def build_gdn_runlist(seq=2048, hidden=1024, C=4096, k_conv=4, H=16, D=128, chun
     H*D -> hidden of every chunk's output. Input face: h fp16 [seq, hidden].
 
     Returns (blob, manifest); manifest["chunk_out"] lists the temps holding
-    the out-projection of each chunk ([chunk, hidden] fp16)."""
-    rng = np.random.default_rng(seed)
+    the out-projection of each chunk ([chunk, hidden] fp16). Weights and the
+    per-chunk q/k/v/beta/g are drawn from one generator per part, so a layer
+    built with a shorter `seq` is the prefix of the longer one."""
     assert seq % chunk == 0 and chunk <= 64
     e = Emitter(quant)
     face = e.b.add_ext_in(seq * hidden * 2)
     e.b.add_states([H * D * D * 4])
-    xin = e.linear(S(face), *rand_w4(rng, hidden, C), seq)
-    conv_w = e.b.add_slot(rng.normal(0.0, 0.5, (k_conv, C)).astype(np.float16))
+    xin = e.linear(S(face), *rand_w4(part_rng(seed, 0), hidden, C), seq)
+    conv_w = e.b.add_slot(part_rng(seed, 1).normal(0.0, 0.5, (k_conv, C)).astype(np.float16))
     conv = e.fresh()
     e.b.add_op(OP.CONV1D_SSM, [xin, conv_w, conv, seq, C, k_conv])
-    kk = rng.standard_normal((H, seq, D)).astype(np.float32)
-    kk = (kk / np.linalg.norm(kk, axis=-1, keepdims=True)).astype(np.float16)
-    vv = rng.standard_normal((H, seq, D)).astype(np.float16)
-    qq = rng.standard_normal((H, seq, D)).astype(np.float16)
-    beta = (1.0 / (1.0 + np.exp(-rng.standard_normal((H, seq))))).astype(np.float16)
-    gg = np.log(1.0 / (1.0 + np.exp(-rng.standard_normal((H, seq))))).astype(np.float16)
+    parts = [[], [], [], [], []]
+    for ci in range(seq // chunk):
+        rng = part_rng(seed, 10 + ci)
+        kc = rng.standard_normal((H, chunk, D)).astype(np.float32)
+        parts[0].append((kc / np.linalg.norm(kc, axis=-1, keepdims=True)).astype(np.float16))
+        parts[1].append(rng.standard_normal((H, chunk, D)).astype(np.float16))
+        parts[2].append(rng.standard_normal((H, chunk, D)).astype(np.float16))
+        parts[3].append((1.0 / (1.0 + np.exp(-rng.standard_normal((H, chunk))))).astype(np.float16))
+        parts[4].append(np.log(1.0 / (1.0 + np.exp(-rng.standard_normal((H, chunk))))).astype(np.float16))
+    kk, vv, qq, beta, gg = (np.ascontiguousarray(np.concatenate(p, axis=1)) for p in parts)
     sk, sv, sq, sb, sg = (S(e.b.add_slot(a)) for a in (kk, vv, qq, beta, gg))
-    nib_o, sc_o = rand_w4(rng, H * D, hidden)
+    nib_o, sc_o = rand_w4(part_rng(seed, 2), H * D, hidden)
     if quant == "w4":
         w_out = S(e.b.add_slot(np.concatenate([nib_o.reshape(-1), sc_o.view(np.uint8).reshape(-1)]), count=H * D * hidden))
     else:
