@@ -691,8 +691,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, AttnDecodeArgs 
 // loads are independent, so they overlap), lanes split head_dim; the four warp
 // sums are added in warp order.
 __global__ void __launch_bounds__(128)
-attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                         uint16_t* __restrict__ out, uint32_t rep, uint32_t hd, uint32_t nsplit,
+attn_decode_merge_kernel(const float* part_o, const float* part_ml,
+                         uint16_t* out, uint32_t rep, uint32_t hd, uint32_t nsplit,
                          const uint32_t* counter, uint32_t n_kv_add, uint32_t n_kv_const,
                          uint32_t* bump_counter, uint32_t round_to) {
     __shared__ float s_acc[4][256];
@@ -701,16 +701,22 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     const uint32_t h = blockIdx.x;           // query head, = kvh * rep + r
     const uint32_t kvh = h / rep, r = h % rep;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // The kernels behind this one start their weight loads as soon as they are allowed on an SM. They are
+    // released only once the split-KV kernel has finished. Released at entry (measured on B200, batch 8,
+    // context 8192), they came up beside that kernel's last CTAs, and with their loads in flight the P.V
+    // sums of single (KV head, slice) pairs came out off by about one tile of V in some runs (maxima and
+    // exp sums unchanged): results differed from run to run by ~1 % in a few heads. With the release
+    // placed here, 24 of 24 repeated steps were bit-identical.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t n_kv = counter ? *counter + n_kv_add : n_kv_const;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t n_kv = counter ? __ldcg(counter) + n_kv_add : n_kv_const;
     uint32_t per = (n_kv + nsplit - 1) / nsplit;
     per = (per + round_to - 1) / round_to * round_to;
     const uint32_t n_chunks = (n_kv + per - 1) / per;          // slices that hold positions
     const size_t row0 = ((size_t)kvh * nsplit) * rep + r;     // chunk s is at row0 + s*rep
     // global maximum over the chunks
     float mt = -INFINITY;
-    for (uint32_t s = threadIdx.x; s < n_chunks; s += 128) mt = fmaxf(mt, part_ml[(row0 + (size_t)s * rep) * 2]);
+    for (uint32_t s = threadIdx.x; s < n_chunks; s += 128) mt = fmaxf(mt, __ldcg(part_ml + (row0 + (size_t)s * rep) * 2));
     mt = warp_max(mt);
     if (lane == 0) s_m[warp] = mt;
     __syncthreads();
@@ -726,14 +732,14 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
             const uint32_t s = s0 + 4 * u;
             const bool ok = s < n_chunks;
             const size_t base = row0 + (size_t)(ok ? s : s0) * rep;
-            ms[u] = ok ? part_ml[base * 2] : -INFINITY;
-            ls[u] = ok ? part_ml[base * 2 + 1] : 0.0f;
+            ms[u] = ok ? __ldcg(part_ml + base * 2) : -INFINITY;
+            ls[u] = ok ? __ldcg(part_ml + base * 2 + 1) : 0.0f;
             const float* po = part_o + base * hd + lane * per_lane;
             if (per_lane == 4) {
-                float4 v = *(const float4*)po;
+                float4 v = __ldcg((const float4*)po);
                 ov[u][0] = v.x; ov[u][1] = v.y; ov[u][2] = v.z; ov[u][3] = v.w;
             } else {
-                float2 v = *(const float2*)po;
+                float2 v = __ldcg((const float2*)po);
                 ov[u][0] = v.x; ov[u][1] = v.y; ov[u][2] = 0.0f; ov[u][3] = 0.0f;
             }
         }
