@@ -44,18 +44,36 @@ def parse_args():
                          "all-reduces (shapes and timing of one rank; the numbers it prints are not bench values)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", type=int, default=None, choices=[1, 2, 3, 5],
+                    help="one line for another baseline configuration (1: single W4A16 matmul, 2: RMSNorm + decode attention, "
+                         "3: 0.6B-shape prefill, 5: gated delta-rule layer) with its roofline and the reference's CPU time")
     ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "gemm512", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (keyed by kernel group, batch, context, GPUs); None for other workloads.
-NCU_TRAFFIC = {
-    # attn_decode_tma_kernel, batch 8, ctx 8192, 1 GPU: 268.56 MB read + 4.31 MB written per launch
-    # (profiles/attn_decode_tma_b8_ctx8192.md); the rotary/append and merge kernels of the unit are not included
-    ("attn_decode", 8, 8192, 1): 268555264 + 4312320,
-}
+# roofline.traffic = dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel. It is not
+# measured by this program (no profiler runs inside a bench): it is read from the ncu summary under profiles/
+# that covers the workload, whose "bench-traffic" line records the byte count and the sha256 of the kernel's
+# source file at capture time. A summary taken from another version of the kernel is not quoted.
+TRAFFIC_PROFILES = {("attn_decode", 8, 8192, 1): "profiles/attn_decode_tma_b8_ctx8192.md"}
+
+
+def profile_traffic(key):
+    """(bytes per launch or None, provenance dict) for a workload key (kernel group, batch, context, GPUs)."""
+    import hashlib
+    import re
+    rel = TRAFFIC_PROFILES.get(key)
+    if not rel or not os.path.exists(os.path.join(ROOT, rel)):
+        return None, {"traffic_source": None}
+    m = re.search(r"bench-traffic:\s*bytes_per_launch=(\d+)\s+source=(\S+)\s+sha256=([0-9a-f]{64})", open(os.path.join(ROOT, rel)).read())
+    if not m:
+        return None, {"traffic_source": rel, "traffic_note": "summary has no bench-traffic line"}
+    src = os.path.join(ROOT, m.group(2))
+    now = hashlib.sha256(open(src, "rb").read()).hexdigest() if os.path.exists(src) else ""
+    if now != m.group(3):
+        return None, {"traffic_source": rel, "traffic_note": "summary was captured from another version of %s" % m.group(2)}
+    return int(m.group(1)), {"traffic_source": rel, "traffic_kernel_sha256": now[:16]}
 
 
 def load_peaks():
@@ -188,10 +206,14 @@ def run_ours(args, rank, world):
 
     # KV rings ~ N(0,1) for positions [0, ctx), generated on the device
     ring_elems = ctx * 2 * man["kv_elems"]
+    check = None
     for li in range(man["layers"]):
         kv = torch.randn(ring_elems, device="cuda", dtype=torch.float16)
         rc = lib.gehtp_cuda_state_load(ctypes.byref(eng.blob), li, kv.data_ptr(), ring_elems * 2, 1, man["kv_elems"], p0, err, 256)
         assert rc == 0, err.value
+        if li == 0 and world == 1 and args.shard_of <= 1 and not args.no_cpu_baseline:
+            # kept for the self-check: the reference runs layer 0 of step 0 on the same ring
+            check = {"ring": kv.cpu().numpy().view(np.float16).reshape(ctx, 2 * man["kv_elems"]).copy(), "p0": p0}
         del kv
     torch.cuda.synchronize()
     setup_s = time.time() - t0
@@ -239,6 +261,9 @@ def run_ours(args, rank, world):
     reset_positions()
     for s in range(2):
         eng.run_io(faces[s], tok_temp, out_host)
+        if s == 0 and check is not None:
+            check["face"] = faces[0].copy()
+            check["layer_out"] = eng.temp(man["layer_out"][0]).copy()
 
     # ---- e2e: host face in, tokens out, through wt_exec_run_io
     def step_e2e(s):
@@ -290,7 +315,7 @@ def run_ours(args, rank, world):
     eng.shutdown()
     attn_kernel_us = attn_ms * 1e3 / attn_n if attn_n else None
     return dict(attn_kernel_us=attn_kernel_us, e2e_ms=e2e_ms, dev_ms=dev_ms, launches=int(launches_dev), launches_e2e=int(launches_e2e), clocks=clocks,
-                groups=groups, man=man, face_bytes=int(faces[0].nbytes), out_bytes=int(out_host.nbytes),
+                groups=groups, man=man, face_bytes=int(faces[0].nbytes), out_bytes=int(out_host.nbytes), check=check,
                 setup_s=setup_s, fused_ops=fused_ops, blob_bytes=int(buf.size))
 
 
@@ -489,13 +514,333 @@ def run_micro(which):
     return out
 
 
-def reference_sample(args, reps):
+def _time_graph(lib, torch, fn, n=16, warm=3):
+    """Mean microseconds of one call of fn(i), n calls captured into a CUDA graph and replayed."""
+    for i in range(warm):
+        fn(i)
+    lib.gehtp_cuda_sync()
+    torch.cuda.synchronize()
+    assert lib.gehtp_cuda_capture_begin() == 0
+    for i in range(n):
+        fn(i + warm)
+    ms = ctypes.c_float()
+    assert lib.gehtp_cuda_capture_end_replay(5, ctypes.byref(ms)) == 0, lib.gehtp_cuda_last_error()
+    return ms.value * 1e3 / n
+
+
+def _ref_op_us(ref, buf, inp, reps=1):
+    """Per-op microseconds of the reference executor on one blob (its own op_us clock), last of `reps` runs."""
+    from gehtp_b200.wtop import Engine
+    eng = Engine(ref, buf)
+    op_us = (ctypes.c_int64 * eng.blob.n_ops)()
+    err = ctypes.create_string_buffer(256)
+    keep = np.ascontiguousarray(inp) if inp is not None else None
+    for _ in range(reps):
+        rc = ref.wt_exec_run_io(ctypes.byref(eng.blob), keep.ctypes.data if keep is not None else None, None, 0, None, op_us, err, 256)
+        assert rc == 0, err.value
+    us = np.array(op_us[:], dtype=np.float64)
+    ops = [(int(eng.blob.ops[i].opcode), list(eng.blob.ops[i].args)) for i in range(eng.blob.n_ops)]
+    return us, ops, eng
+
+
+def run_config(args):
+    """Baseline configurations 1, 2, 3 and 5: the same contract as the decode line (value = device-resident
+    figure by graph replay or CUDA events, e2e = through the C ABI with host buffers, roofline against the
+    measured peaks, cpu_baseline = the reference's executor on this box's host cores, one thread, on a
+    bounded sample that `sample` describes)."""
+    import tempfile
+    import torch
+    import gehtp_b200
+    from gehtp_b200.runlists import QWEN3_0P6B, build_gdn_runlist, build_prefill_runlist, dequant_f16, rand_w4
+    from gehtp_b200.wtop import KV_POS_AUTO, OP, S, ST, BlobBuilder, Engine
+    from oracle.refexec import orc_lib, ptr, ref_lib
+    lib = gehtp_b200.lib()
+    assert lib.gehtp_cuda_set_device(0) == 0, "no CUDA device"
+    peak_hbm, peak_src = load_peaks()
+    pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak_tf = float(pk.get("bf16_tflops", 1590.0))
+    ref = None if args.no_cpu_baseline else ref_lib(private_dir=tempfile.mkdtemp())
+    sampler = ClockSampler(0)
+    sampler.start()
+    stream = torch.cuda.ExternalStream(lib.gehtp_cuda_stream())
+
+    def events(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        lib.gehtp_cuda_sync()
+        with torch.cuda.stream(stream):
+            e0.record()
+        for i in range(reps):
+            fn(i)
+        with torch.cuda.stream(stream):
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    line = {"n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic"}
+    c = args.config
+    if c == 1:
+        # ---- single W4A16 matmul, M128 K1024 N3072 (GEMM) and the same weights at M = 1 (GEMV)
+        M, K, N = 128, 1024, 3072
+        rng = np.random.default_rng(1001)
+        a = rng.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+        nib, sc = rand_w4(rng, K, N)
+        slot = np.concatenate([nib.reshape(-1), sc.view(np.uint8).reshape(-1)])
+        copies = 128            # 208 MB of weights in rotation: larger than L2
+        packed = torch.randint(0, 2 ** 31 - 1, (copies, K * N // 8), dtype=torch.int32, device="cuda")
+        scales = (torch.rand(copies, K // 64, N, device="cuda") * 0.015 + 0.005).half()
+        da = torch.from_numpy(a.view(np.int16)).cuda()
+        dy = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+        res = {}
+        for name, m, path in (("gemm", M, 2), ("gemv", 1, 1)):
+            us = _time_graph(lib, torch, lambda i: lib.gehtp_dev_w4a16_matmul(da.data_ptr(), packed[i % copies].data_ptr(), scales[i % copies].data_ptr(),
+                                                                              dy.data_ptr(), m, K, N, path), n=32)
+            res[name] = us
+        got = np.zeros((M, N), np.float16)
+        e2e_ms = events(lambda i: lib.gehtp_w4a16_matmul(ptr(a), ptr(slot), ptr(got), M, K, N, 0), max(args.steps, 5))
+        flops, gemm_bytes, gemv_bytes = 2.0 * M * K * N, w4_bytes(M, K, N), w4_bytes(1, K, N)
+        line.update(metric="w4a16_matmul_m128_k1024_n3072_tflops", value=flops / res["gemm"] / 1e6, unit="TFLOP/s",
+                    ms_per_step=res["gemm"] * 1e-3, gpu_launches=32 * 5,
+                    config={"workload": "config 1: one W4A16 group-64 matmul, M128 K1024 N3072; weights rotate through %d copies (208 MB > L2)" % copies},
+                    e2e={"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                         "h2d_bytes_per_step": int(a.nbytes + slot.nbytes), "d2h_bytes_per_step": int(got.nbytes)},
+                    roofline={"bound": "tensor", "kernel": "w4a16_gemm_sm100_kernel", "achieved": flops / res["gemm"] / 1e6, "peak": peak_tf,
+                              "unit": "TFLOP/s", "frac": flops / res["gemm"] / 1e6 / peak_tf, "traffic": None, "peak_source": peak_src,
+                              "note": "0.8 GFLOP: the ideal math time is 0.5 us, the launch is latency bound; HBM floor %d bytes = %.2f us" % (gemm_bytes, gemm_bytes / peak_hbm / 1e3)},
+                    gemv={"M": 1, "us": res["gemv"], "GBps": gemv_bytes / res["gemv"] / 1e3, "frac_of_measured_hbm": gemv_bytes / res["gemv"] / 1e3 / peak_hbm})
+        if ref is not None:
+            orc = orc_lib()
+            want = np.zeros((M, N), np.float16)
+            t0 = time.time()
+            orc.orc_w4a16_matmul(ptr(a), ptr(slot), ptr(want), M, K, N)
+            t_rest = time.time() - t0
+            b = BlobBuilder()
+            sa, sw = b.add_slot(a), b.add_slot(dequant_f16(nib, sc))
+            b.add_op(OP.MATMUL_F16, [S(sa), S(sw), 1, M, K, N, 0])
+            us, _, reng = _ref_op_us(ref, b.build(), None)
+            err = np.abs(got.astype(np.float64) - want.astype(np.float64)).max()
+            line["checked"] = bool(err <= 1e-2 * np.abs(want.astype(np.float64)).max())
+            line["cpu_baseline"] = {"value": flops / (us.sum() * 1e-6) / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "reference",
+                                    "sample": "the whole matmul once: reference OP_MATMUL_F16 on the dequantised fp16 weights %.2f s; "
+                                              "this repo's C restatement of the group-64 op %.2f s" % (us.sum() * 1e-6, t_rest)}
+    elif c == 2:
+        # ---- RMSNorm [1,1024] + decode attention 16 q / 8 kv heads of 128 over 4096 positions
+        nh, kvh, hd, n_kv, W = 16, 8, 128, 4096, 1024
+        rng = np.random.default_rng(1002)
+        x = rng.standard_normal((1, W), dtype=np.float32).astype(np.float16)
+        gam = rng.normal(1, 0.1, W).astype(np.float16)
+        q = rng.standard_normal((nh, hd), dtype=np.float32).astype(np.float16)
+        ring = rng.standard_normal((n_kv, 2, kvh * hd), dtype=np.float32).astype(np.float16)
+        mask = np.zeros(n_kv, np.float16)
+        scale = float(np.float16(1 / np.sqrt(hd)))
+        copies = 12            # 200 MB of rings in rotation
+        rings = torch.randn(copies, n_kv * 2 * kvh * hd, device="cuda").half()
+        dq, dm = torch.from_numpy(q.view(np.int16)).cuda(), torch.zeros(n_kv, dtype=torch.int16, device="cuda")
+        do = torch.zeros(nh * hd, dtype=torch.int16, device="cuda")
+        dx, dg = torch.from_numpy(x.view(np.int16)).cuda(), torch.from_numpy(gam.view(np.int16)).cuda()
+        dyn = torch.zeros(W, dtype=torch.int16, device="cuda")
+        st = lib.gehtp_cuda_stream()
+        us_attn = _time_graph(lib, torch, lambda i: lib.gehtp_attn_decode_noalloc(dq.data_ptr(), rings[i % copies].data_ptr(), dm.data_ptr(), do.data_ptr(),
+                                                                                   nh, kvh, hd, n_kv, n_kv, scale, st), n=24)
+        us_norm = _time_graph(lib, torch, lambda i: lib.gehtp_dev_rmsnorm(dx.data_ptr(), None, dg.data_ptr(), None, None, dyn.data_ptr(), 1, W), n=24)
+        got = np.zeros((nh, hd), np.float16)
+        yn = np.zeros((1, W), np.float16)
+
+        def e2e_step(i):
+            assert lib.gehtp_rmsnorm(ptr(x), ptr(gam), None, ptr(yn), 1, W) == 0
+            assert lib.gehtp_attn_decode(ptr(q), ptr(ring), ptr(mask), ptr(got), nh, kvh, hd, n_kv, n_kv, scale) == 0
+        e2e_ms = events(e2e_step, max(args.steps, 5))
+        kv_bytes = ring.nbytes
+        line.update(metric="decode_attention_16q8kv_ctx4096_GBps", value=kv_bytes / us_attn / 1e3, unit="GB/s", ms_per_step=(us_attn + us_norm) * 1e-3,
+                    gpu_launches=24 * 5 * 2,
+                    config={"workload": "config 2: RMSNorm [1,1024] + decode GQA attention, 16 q / 8 kv heads of 128, KV context 4096; %d rings in rotation (200 MB > L2)" % copies},
+                    e2e={"value": kv_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                         "h2d_bytes_per_step": int(ring.nbytes + q.nbytes + mask.nbytes + x.nbytes + gam.nbytes), "d2h_bytes_per_step": int(got.nbytes + yn.nbytes)},
+                    roofline={"bound": "hbm", "kernel": "attn_decode (split-KV + merge)", "achieved": kv_bytes / us_attn / 1e3, "peak": peak_hbm, "unit": "GB/s",
+                              "frac": kv_bytes / us_attn / 1e3 / peak_hbm, "traffic": None, "peak_source": peak_src, "bytes_per_launch": kv_bytes, "avg_launch_us": us_attn},
+                    rmsnorm={"rows": 1, "width": W, "us": us_norm, "bytes": 6 * W, "note": "6 KB: latency of one launch, not a bandwidth figure"})
+        if ref is not None:
+            # the reference's op chain on its own KV ring: appends untimed, then gather / scores / scale / mask / softmax / PV timed
+            b = BlobBuilder()
+            b.add_states([kvh * hd * 4 * n_kv])
+            face = b.add_ext_in(2 * kvh * hd * 2)
+            b.add_op(OP.SLICE, [S(face), 1, kvh * hd, 1, 0, 0, 0, kvh * hd, 0, 0, 1, 1, 1, 2 * kvh * hd, 1, 1])
+            b.add_op(OP.SLICE, [S(face), 2, kvh * hd, 1, kvh * hd, 0, 0, 2 * kvh * hd, 0, 0, 1, 1, 1, 2 * kvh * hd, 1, 1])
+            b.add_op(OP.KV_APPEND, [1, 2, ST(0), KV_POS_AUTO])
+            feng = Engine(ref, b.build())
+            for p in range(n_kv):
+                feng.run_io(ring[p].reshape(-1), 0)
+            b = BlobBuilder()
+            b.add_states([kvh * hd * 4 * n_kv])
+            sx, sg, sz, sq = b.add_slot(x), b.add_slot(gam), b.add_slot(np.zeros(W, np.float16)), b.add_slot(q)
+            ssc, smk = b.add_slot(np.array([scale], np.float16)), b.add_slot(mask)
+            b.add_op(OP.RMSNORM2, [S(sx), S(sg), S(sz), 1, W])
+            b.add_op(OP.KV_GATHER, [ST(0), 2, 0, n_kv, nh, kvh, hd])
+            b.add_op(OP.KV_GATHER, [ST(0), 0, 3, n_kv, nh, kvh, hd])
+            b.add_op(OP.MATMUL_F16, [S(sq), 2, 4, 1, hd, n_kv, 4 | nh << 16])
+            b.add_op(OP.BROADCAST, [S(ssc), 5, nh * n_kv, 1, 1, 1, 1, 1, 1, 1, 1, nh * n_kv])
+            b.add_op(OP.BINARY, [4, 5, 6, nh * n_kv, 2])
+            b.add_op(OP.BROADCAST, [S(smk), 7, nh * n_kv, n_kv, 1, 1, 1, n_kv, 1, 1, nh, n_kv])
+            b.add_op(OP.ADD, [6, 7, 8, nh * n_kv])
+            b.add_op(OP.SOFTMAX, [8, 9, nh, n_kv])
+            b.add_op(OP.MATMUL_F16, [9, 3, 10, 1, n_kv, hd, 4 | nh << 16])
+            us, _, reng = _ref_op_us(ref, b.build(), None, reps=3)
+            want = reng.temp(10).astype(np.float64).reshape(nh, hd)
+            err = np.abs(got.astype(np.float64) - want).max()
+            line["checked"] = bool(err <= 1e-2 * np.abs(want).max())
+            line["cpu_baseline"] = {"value": kv_bytes / (us[1:].sum() * 1e-6) / 1e9, "unit": "GB/s", "cores": 1, "kind": "reference",
+                                    "sample": "the whole op chain (KV_GATHER x2, scores, scale, mask, SOFTMAX, PV) %.1f ms and RMSNORM2 %.1f us, "
+                                              "third of 3 runs; the 4096 appends are set-up" % (us[1:].sum() * 1e-3, us[0])}
+    elif c == 3:
+        # ---- Qwen3-0.6B-shaped prefill, 512 tokens, 28 layers + lm_head
+        cfg, seq = QWEN3_0P6B, 512
+        buf, man = build_prefill_runlist(cfg, seq, seed=1003, quant="w4")
+        eng = Engine(lib, buf)
+        ids = np.random.default_rng(1003).integers(0, cfg.vocab, seq).astype(np.int32)
+        out_h = np.zeros(seq * cfg.hidden, np.float16)
+        for _ in range(max(args.warmup, 3)):
+            eng.run_io(ids, man["hidden_temp"], out_h)
+        dids = torch.from_numpy(ids).cuda()
+        dout = torch.zeros(seq * cfg.hidden, dtype=torch.int16, device="cuda")
+        err = ctypes.create_string_buffer(256)
+        l0 = lib.gehtp_cuda_launch_count()
+        e2e_ms = events(lambda i: eng.run_io(ids, man["hidden_temp"], out_h), max(args.steps, 5))
+
+        def dev_step(i):
+            assert lib.gehtp_cuda_run_dev(ctypes.byref(eng.blob), dids.data_ptr(), dout.data_ptr(), man["hidden_temp"], err, 256) == 0, err.value
+        for i in range(3):
+            dev_step(i)
+        l0 = lib.gehtp_cuda_launch_count()
+        ms = events(dev_step, max(args.steps, 5))
+        launches = int(lib.gehtp_cuda_launch_count() - l0)
+        H, F, L, V = cfg.hidden, cfg.ffn, cfg.layers, cfg.vocab
+        nh, kvh, hd = cfg.n_heads, cfg.kv_heads, cfg.head_dim
+        lin = 2.0 * seq * (H * (nh + 2 * kvh) * hd + nh * hd * H + 3 * H * F) * L + 2.0 * seq * H * V
+        att = 4.0 * nh * seq * seq * hd / 2 * L
+        tf = (lin + att) / ms / 1e9
+        line.update(metric="qwen3_0p6b_shape_prefill_512_tokens_per_s", value=seq / ms * 1e3, unit="tok/s", ms_per_step=ms, gpu_launches=launches,
+                    config={"workload": "config 3: Qwen3-0.6B-shaped prefill, 512 tokens, batch 1, 28 layers + lm_head 151936, W4A16 group-64; 298 MB of weights per pass (> L2)"},
+                    e2e={"value": seq / e2e_ms * 1e3, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": int(out_h.nbytes)},
+                    roofline={"bound": "tensor", "kernel": "whole pass (w4a16_gemm_sm100_kernel dominates)", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s",
+                              "frac": tf / peak_tf, "traffic": None, "peak_source": peak_src, "flops_per_step": lin + att})
+        eng.shutdown()
+        if ref is not None:
+            # one layer over the 128-token causal prefix + a 2048-column cut of lm_head on the reference; every op scaled by its own work ratio
+            cut, vs = 128, 2048
+            work = {}
+            for s_ in (cut, seq):
+                bb, mm = build_prefill_runlist(cfg, s_, seed=1003, quant="f16", n_layers=1, vocab=vs)
+                if s_ == cut:
+                    us, ops, reng = _ref_op_us(ref, bb, ids[:cut])
+                work[s_] = [_op_work(o, a_) for o, a_ in (ops if s_ == cut else [(int(x_[0]), x_[1]) for x_ in _blob_ops(lib, bb)])]
+            head_i = [i for i, (o, a_) in enumerate(ops) if o == OP.MATMUL_F16 and a_[5] == vs]
+            tot = 0.0
+            for i in range(len(ops)):
+                ratio = work[seq][i] / work[cut][i] if work[seq][i] and work[cut][i] else seq / cut
+                t = us[i] * ratio
+                tot += t * (V / vs if i in head_i else L) if (i in head_i or i > 2) else t
+            line["cpu_baseline"] = {"value": seq / (tot * 1e-6), "unit": "tok/s", "cores": 1, "kind": "reference",
+                                    "sample": "one of 28 layers over the first 128 of 512 tokens plus a 2048-column cut of lm_head, fp16 weights (%.1f s); "
+                                              "each op scaled by its work ratio to 512 tokens, x28 layers, x74 for the vocabulary: extrapolated" % (us.sum() * 1e-6)}
+    elif c == 5:
+        # ---- gated delta-rule layer: in-projection, conv1d 4096 channels, 32 chunks of 64 tokens x 16 heads, out-projection
+        buf, man = build_gdn_runlist()
+        eng = Engine(lib, buf)
+        h = np.random.default_rng(1005).standard_normal((man["seq"], man["hidden"]), dtype=np.float32).astype(np.float16)
+        last = man["chunk_out"][-1]
+        out_h = np.zeros(man["chunk"] * man["hidden"], np.float16)
+        for _ in range(max(args.warmup, 3)):
+            lib.wt_exec_state_reset()
+            eng.run_io(h, last, out_h)
+        l0 = lib.gehtp_cuda_launch_count()
+        reps = max(args.steps, 5)
+        e2e_ms = events(lambda i: eng.run_io(h, last, out_h), reps)
+        launches = int(lib.gehtp_cuda_launch_count() - l0) // reps
+        dh = torch.from_numpy(h.view(np.int16)).cuda()
+        dout = torch.zeros(out_h.size, dtype=torch.int16, device="cuda")
+        err = ctypes.create_string_buffer(256)
+
+        def dev_step(i):
+            assert lib.gehtp_cuda_run_dev(ctypes.byref(eng.blob), dh.data_ptr(), dout.data_ptr(), last, err, 256) == 0, err.value
+        for i in range(3):
+            dev_step(i)
+        ms = events(dev_step, reps)
+        op_ms = (ctypes.c_float * eng.blob.n_ops)()
+        assert lib.gehtp_cuda_run_profiled(ctypes.byref(eng.blob), h.ctypes.data, last, op_ms, eng.blob.n_ops, err, 256) == 0, err.value
+        by = {}
+        for i in range(eng.blob.n_ops):
+            by[eng.blob.ops[i].opcode] = by.get(eng.blob.ops[i].opcode, 0.0) + op_ms[i]
+        H, D, seq, C = man["H"], man["D"], man["seq"], man["C"]
+        conv_bytes, qkvy_bytes = 2.0 * seq * C * 2, 4.0 * H * seq * D * 2
+        conv_ms, delta_ms = by.get(OP.CONV1D_SSM, 0.0), by.get(OP.DELTA_CHUNK, 0.0)
+        line.update(metric="gated_delta_layer_seq2048_tokens_per_s", value=seq / ms * 1e3, unit="tok/s", ms_per_step=ms, gpu_launches=launches,
+                    config={"workload": "config 5: gated delta-rule layer, 2048 tokens, conv1d k=4 over 4096 channels, 16 heads of 128, 32 chunks of 64, W4A16 in/out projections from hidden 1024"},
+                    e2e={"value": seq / e2e_ms * 1e3, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h.nbytes), "d2h_bytes_per_step": int(out_h.nbytes)},
+                    roofline={"bound": "hbm", "kernel": "delta_chunk_kernel (32 sequential launches)", "achieved": qkvy_bytes / max(delta_ms, 1e-9) / 1e6, "peak": peak_hbm,
+                              "unit": "GB/s", "frac": qkvy_bytes / max(delta_ms, 1e-9) / 1e6 / peak_hbm, "traffic": None, "peak_source": peak_src,
+                              "note": "q/k/v/y traffic of the 32 chunks against HBM; the chunks are sequential per head and on-chip bound"},
+                    kernels={"conv1d_ssm": {"ms": conv_ms, "GBps": conv_bytes / max(conv_ms, 1e-9) / 1e6, "frac_of_measured_hbm": conv_bytes / max(conv_ms, 1e-9) / 1e6 / peak_hbm},
+                             "delta_chunk_x32": {"ms": delta_ms}, "w4a16_projections": {"ms": by.get(OP.MATMUL_W4A16, 0.0)}})
+        eng.shutdown()
+        if ref is not None:
+            # the reference's conv op over the whole sequence and its delta-chunk op over all 32 chunks (no projections)
+            rng = np.random.default_rng(1005)
+            b = BlobBuilder()
+            b.add_states([H * D * D * 4])
+            sx = b.add_slot(rng.standard_normal((seq, C), dtype=np.float32).astype(np.float16))
+            sw = b.add_slot(rng.normal(0, 0.5, (4, C)).astype(np.float16))
+            b.add_op(OP.CONV1D_SSM, [S(sx), sw, 1, seq, C, 4])
+            ck = man["chunk"]
+            kk = rng.standard_normal((H, ck, D), dtype=np.float32)
+            kk = (kk / np.linalg.norm(kk, axis=-1, keepdims=True)).astype(np.float16)
+            sl = [b.add_slot(kk), b.add_slot(rng.standard_normal((H, ck, D), dtype=np.float32).astype(np.float16)),
+                  b.add_slot(rng.standard_normal((H, ck, D), dtype=np.float32).astype(np.float16)),
+                  b.add_slot((1 / (1 + np.exp(-rng.standard_normal((H, ck))))).astype(np.float16)),
+                  b.add_slot(np.log(1 / (1 + np.exp(-rng.standard_normal((H, ck))))).astype(np.float16))]
+            for ci in range(seq // ck):
+                b.add_op(OP.DELTA_CHUNK, [S(s_) for s_ in sl] + [2, ST(0), ck, ck, H, D, 0])
+            us, _, reng = _ref_op_us(ref, b.build(), None)
+            line["cpu_baseline"] = {"value": seq / (us.sum() * 1e-6), "unit": "tok/s", "cores": 1, "kind": "reference",
+                                    "sample": "OP_CONV1D_SSM over 2048 x 4096 (%.2f s) and OP_DELTA_CHUNK over 32 chunks of 64 tokens x 16 heads (%.2f s); "
+                                              "the two W4A16 projections are not in the reference figure" % (us[0] * 1e-6, us[1:].sum() * 1e-6)}
+    line["clocks"] = sampler.stop()
+    line.setdefault("checked", False)
+    return line
+
+
+def _op_work(opcode, a):
+    """Scalar operations of one op record, for scaling a reference timing to another sequence length."""
+    from gehtp_b200.wtop import OP
+    if opcode in (OP.MATMUL_F16, OP.MATMUL_W4A16):
+        bn = (a[6] >> 16) if (opcode == OP.MATMUL_F16 and a[6] & 4) else 1
+        return a[3] * a[4] * a[5] * max(bn, 1)
+    n = {OP.ADD: 3, OP.UNARY: 2, OP.BINARY: 3, OP.BROADCAST: 2, OP.RMSNORM2: 4, OP.GATHER: 3, OP.SLICE: 2, OP.CONCAT: 11}.get(opcode, None)
+    if opcode == OP.SOFTMAX:
+        return a[2] * a[3]
+    if opcode == OP.TRANSPOSE_GEN:
+        return a[3] * a[4] * a[5] * max(a[6], 1)
+    return max(a[n], 1) if n is not None else None    # None: unknown, the caller scales linearly
+
+
+def _blob_ops(lib, buf):
+    from gehtp_b200.wtop import parse_blob
+    rc, blob = parse_blob(lib, np.ascontiguousarray(buf, dtype=np.uint8))
+    assert rc == 0
+    return [(int(blob.ops[i].opcode), list(blob.ops[i].args)) for i in range(blob.n_ops)]
+
+
+def reference_sample(args, reps, check=None):
     """Times the reference's own executor (compiled for the host, scalar code,
     one thread as the reference runs it) on a bounded sample of the workload:
     one decoder layer at the full batch and KV context plus a 2048-column slice
     of lm_head, weights dequantised to fp16 because the reference has no
     group-64 W4A16 op. The step time of the whole model is extrapolated linearly
-    (layers x layer time + vocab/2048 x head-slice time)."""
+    (layers x layer time + vocab/2048 x head-slice time).
+
+    With `check` (the KV ring of layer 0, the input face and the position of the GPU run's first step),
+    the ring is filled with those rows and the first repetition runs that very step, so that its layer
+    output can be compared with the GPU's: the one-layer model carries the weights of the whole model's
+    first layer, and token ids are taken modulo 1024, the period of the synthetic embedding table."""
     from gehtp_b200.runlists import QWEN3_4B, build_decode_runlist, decode_face
     from gehtp_b200.wtop import KV_POS_AUTO, OP, S, ST, BlobBuilder, Engine
     from oracle.refexec import ref_lib
@@ -512,12 +857,22 @@ def reference_sample(args, reps):
     fill = BlobBuilder()
     fill.add_states([kv_elems * 4 * ctx])
     rng = np.random.default_rng(1)
-    kslot = fill.add_slot(rng.standard_normal(kv_elems).astype(np.float16))
-    n_fill = ctx - 1 - reps
-    for _ in range(n_fill):
-        fill.add_op(OP.KV_APPEND, [S(kslot), S(kslot), ST(0), KV_POS_AUTO])
-    feng = Engine(lib, fill.build())
-    feng.run()
+    if check is None:
+        kslot = fill.add_slot(rng.standard_normal(kv_elems).astype(np.float16))
+        n_fill = ctx - 1 - reps
+        for _ in range(n_fill):
+            fill.add_op(OP.KV_APPEND, [S(kslot), S(kslot), ST(0), KV_POS_AUTO])
+        feng = Engine(lib, fill.build())
+        feng.run()
+    else:
+        n_fill = check["p0"]
+        fface = fill.add_ext_in(2 * kv_elems * 2)
+        fill.add_op(OP.SLICE, [S(fface), 1, kv_elems, 1, 0, 0, 0, kv_elems, 0, 0, 1, 1, 1, 2 * kv_elems, 1, 1])
+        fill.add_op(OP.SLICE, [S(fface), 2, kv_elems, 1, kv_elems, 0, 0, 2 * kv_elems, 0, 0, 1, 1, 1, 2 * kv_elems, 1, 1])
+        fill.add_op(OP.KV_APPEND, [1, 2, ST(0), KV_POS_AUTO])
+        feng = Engine(lib, fill.build())
+        for p in range(n_fill):
+            feng.run_io(check["ring"][p], 0)
     eng = Engine(lib, buf)
     n_ops = eng.blob.n_ops
     op_us = (ctypes.c_int64 * n_ops)()
@@ -525,8 +880,13 @@ def reference_sample(args, reps):
     from gehtp_b200.wtop import OP as _OP
     head_ops = [i for i in range(n_ops) if eng.blob.ops[i].opcode == _OP.MATMUL_F16 and eng.blob.ops[i].args[5] == vs]
     times = []
+    layer_out = None
     for r in range(reps):
         face = decode_face(man, rng.integers(0, vs, B), n_fill + r, cfg.head_dim, cfg.rope_theta)
+        if check is not None and r == 0:
+            face = check["face"].copy()
+            ids = face[:2 * B].view(np.int32) % 1024
+            face[:2 * B] = ids.astype(np.int32).view(np.uint16)
         t0 = time.time()
         rc = lib.wt_exec_run_io(ctypes.byref(eng.blob), face.ctypes.data, None, man["token_temp"], None, op_us, err, 256)
         wall = time.time() - t0
@@ -536,10 +896,12 @@ def reference_sample(args, reps):
         layer = us.sum() - head
         full_s = (layer * args.layers + head * (cfg.vocab / vs)) * 1e-6
         times.append((wall, full_s))
+        if check is not None and r == 0:
+            layer_out = eng.temp(man["layer_out"][0]).copy()
     eng.shutdown()
     wall = float(np.mean([t[0] for t in times]))
     full = float(np.mean([t[1] for t in times]))
-    return dict(tok_s=B / full, step_s_extrapolated=full, sample_wall_s=wall, reps=reps,
+    return dict(tok_s=B / full, step_s_extrapolated=full, sample_wall_s=wall, reps=reps, layer_out=layer_out,
                 sample="1 of %d layers at batch %d, KV ctx %d, plus a %d-column slice of lm_head; fp16 weights; "
                        "step time extrapolated linearly; %d repetition(s) of %.1f s" % (args.layers, B, ctx, vs, reps, wall))
 
@@ -614,6 +976,10 @@ def run_main(args):
             for row in run_micro(args.micro):
                 out.append(json.dumps(row))
         return out
+    if args.config:
+        if rank == 0:
+            out.append(json.dumps(run_config(args)))
+        return out
 
     if args.impl == "reference":
         if rank != 0:
@@ -622,10 +988,12 @@ def run_main(args):
         if probe is None:
             out.append(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libgehtp_ref.so was not built"}))
             return out
+        # the probe is the warm-up; the timed repetitions are bounded by a 150 s budget
         reps = int(max(1, min(args.steps, 150.0 // max(probe["sample_wall_s"], 1e-3)))) - 1
         res = reference_sample(args, reps) if reps >= 1 else probe
         line = {"impl": "reference", "metric": METRIC, "value": res["tok_s"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["step_s_extrapolated"] * 1e3,
+                "steps": res["reps"], "steps_requested": args.steps, "warmup": 1, "warmup_requested": args.warmup,
+                "ms_per_step": res["step_s_extrapolated"] * 1e3,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": config, "gpu_launches": 0,
                 "cpu_baseline": {"value": res["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": res["sample"]},
@@ -654,6 +1022,7 @@ def run_main(args):
         # timed by its own event pair inside the same profiled steps
         dom_kernel, dom_us = "attn_decode_tma_kernel", r["attn_kernel_us"]
         achieved = (dbytes / dn) / (dom_us * 1e-6) / 1e9
+    traffic, traffic_src = profile_traffic((dom, B, args.ctx, world))
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
             "ms_per_step": r["dev_ms"] / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic", "config": config, "clocks": r["clocks"],
@@ -661,8 +1030,8 @@ def run_main(args):
                     "d2h_bytes_per_step": r["out_bytes"]},
             "gpu_launches": r["launches"],
             "roofline": {"bound": "hbm", "kernel": dom_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC.get((dom, B, args.ctx, world)), "peak_source": peak_src,
-                         "bytes_per_launch": dbytes / dn, "avg_launch_us": dom_us, "launch_unit_us": dms * 1e3 / dn},
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                         "bytes_per_launch": dbytes / dn, "avg_launch_us": dom_us, "launch_unit_us": dms * 1e3 / dn, **traffic_src},
             "kernels": kernels, "fused_ops": r["fused_ops"], "setup_s": r["setup_s"]}
     if world == 1 and args.shard_of <= 1:
         # the kernel halves of the headline metric: streaming GEMV (vocabulary projection, M = 1) and prefill GEMM
@@ -673,10 +1042,22 @@ def run_main(args):
                                   "frac_of_measured_bf16_peak": hm["frac_of_measured_bf16_peak"]}
         except Exception as ex:      # never lose the bench line over the extra figures
             line["w4a16_kernels_error"] = str(ex)[:200]
+    line["checked"] = False
     if world == 1 and not args.no_cpu_baseline:
-        cb = reference_sample(args, 1)
+        cb = reference_sample(args, 1, check=r.get("check"))
         if cb:
             line["cpu_baseline"] = {"value": cb["tok_s"], "unit": UNIT, "cores": 1, "kind": "reference", "sample": cb["sample"]}
+            if cb.get("layer_out") is not None and r.get("check") and r["check"].get("layer_out") is not None:
+                # output of decoder layer 0 in the GPU run's first step against the reference executor on the same
+                # ring, face and weights: the project's fp16 gate (max |err| <= 1e-2 max|ref|, cosine >= 0.9999)
+                got = r["check"]["layer_out"].astype(np.float64)
+                want = cb["layer_out"].astype(np.float64)
+                err_max, ref_max = float(np.abs(got - want).max()), float(np.abs(want).max())
+                cs = float(got @ want / max(np.sqrt((got @ got) * (want @ want)), 1e-300))
+                line["checked"] = bool(np.isfinite(got).all() and err_max <= 1e-2 * ref_max and cs >= 0.9999)
+                line["check"] = {"what": "layer 0 output of step 0 vs the reference executor (same KV ring, face, weights)",
+                                 "max_err": err_max, "ref_max": ref_max, "cosine": cs}
+                assert line["checked"], "self-check failed: %r" % (line["check"],)
     out.append(json.dumps(line))
     return out
 
