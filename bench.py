@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--config", type=int, default=None, choices=[1, 2, 3, 5],
                     help="one line for another baseline configuration (1: single W4A16 matmul, 2: RMSNorm + decode attention, "
                          "3: 0.6B-shape prefill, 5: gated delta-rule layer) with its roofline and the reference's CPU time")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "gemm512", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "gemm1", "gemm512", "f16gemm", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -408,6 +408,24 @@ def run_micro(which):
             us, _, flops = w4(M, K, N, 2, n=8)
             out.append({"kernel": "w4a16_gemm_tcgen05", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
                         "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
+    if which in ("f16gemm", "all"):   # OP_MATMUL_F16 with weights stored [N, K]: tcgen05 GEMM (M >= 128) and streaming GEMV (M < 32)
+        for (M, K, N) in ((1, 1024, 151936), (8, 2560, 9728), (128, 1024, 3072), (512, 1024, 4096), (2048, 2560, 9728), (8192, 2560, 9728)):
+            copies = min(max(2, int(300e6 // (2 * K * N)) + 1), 16)
+            w = (torch.randn(copies, N, K, device="cuda") * 0.05).half()
+            a = torch.randn(M, K, device="cuda").half()
+            y = torch.zeros(M, N, dtype=torch.half, device="cuda")
+
+            def f(i):
+                assert lib.gehtp_dev_matmul_f16_nk(a.data_ptr(), w[i % copies].data_ptr(), y.data_ptr(), M, K, N) == 0, lib.gehtp_cuda_last_error()
+            us = timeit(f, n=8)
+            flops, nbytes = 2.0 * M * K * N, 2.0 * (K * N + M * K + M * N)
+            row = {"kernel": "f16_gemm_sm100" if M >= 128 else "f16_gemv_nk", "M": M, "K": K, "N": N, "us": us}
+            if M >= 128:
+                row.update(TFLOPs=flops / us / 1e6, frac_of_measured_bf16_peak=flops / us / 1e6 / peak_tf)
+            else:
+                row.update(GBps=nbytes / us / 1e3, frac_of_measured_hbm=nbytes / us / 1e3 / peak_hbm)
+            out.append(row)
+            del w
     if which in ("attn", "attn8", "all"):
         # attn8: the batch-8 shape of the decode bench alone, a small case for profiler captures
         for (nh, kvh, n_kv) in (((256, 64, 8192),) if which == "attn8" else ((256, 64, 8192), (32, 8, 8192), (16, 8, 4096))):

@@ -30,6 +30,7 @@ UNITS = {
     "ops_matmul.cu": [],
     "ops_w4a16.cu": [],
     "w4a16_gemm_sm100.cu": [],
+    "f16_gemm_sm100.cu": [],
     "tp.cu": [],
     "tp_p2p.cu": [],
 }

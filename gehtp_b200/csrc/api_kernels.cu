@@ -134,6 +134,13 @@ int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, co
     return 0;
 }
 
+// y[M, N] = a[M, K] . w^T with w stored [N, K] (fp16): tcgen05 GEMM for M >= 128, streaming GEMV for M < 32
+int gehtp_dev_matmul_f16_nk(const uint16_t* a_dev, const uint16_t* w_dev, uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N) {
+    if (!ensure_device(nullptr, 0)) return -1;
+    if (!k_matmul_f16_nk(g.stream, a_dev, w_dev, y_dev, M, K, N, N, g.d_status)) return fail("matmul_f16 [N,K]: shape not taken by the tensor-core forms");
+    return 0;
+}
+
 int gehtp_dev_w4a16_swiglu(const uint16_t* a_dev, const uint32_t* pg, const uint16_t* sg, const uint32_t* pu,
                            const uint16_t* su, uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N) {
     if (!ensure_device(nullptr, 0)) return -1;

@@ -119,6 +119,7 @@ struct Engine {
 
     // options
     int opt_fuse = 1, opt_graph = 1, trace_on = 0;
+    bool exact_ops = false;       // a dump hook is active: matmuls keep the reference's summation order
     bool skip_dead = false;       // set for the duration of a whole fused run
     bool force_unfused = false;   // a run needed an op that the fused plan gave no memory
     const char* hook_spec = nullptr;

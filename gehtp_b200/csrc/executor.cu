@@ -198,6 +198,7 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
     const bool hooks = hooks_active();
     std::vector<PlanOp*> pending;
     if (hooks) fuse = false;   // dumps need every intermediate temp
+    g.exact_ops = hooks;
     for (uint32_t ii = 0; ii < count;) {
         const uint32_t i = first + ii;
         PlanOp& p = g.plan[i];

@@ -66,6 +66,11 @@ void k_matmul_f16(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_
                   uint32_t K, uint32_t N, uint32_t n0, uint32_t N_full, int t0, int t1,
                   uint32_t Bn);
 
+// W stored [N, K] on the tensor cores (M >= 128: TMA-fed tcgen05 GEMM) or as a streaming GEMV (M < 32),
+// f16_gemm_sm100.cu; y rows are ldy elements apart. false: shape not taken, nothing launched.
+bool k_matmul_f16_nk(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, uint32_t M,
+                     uint32_t K, uint32_t N, uint32_t ldy, unsigned int* status);
+
 // ---- gated delta net (ops_gdn.cu) ----
 void k_conv1d_ssm(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_t* y, uint32_t seq,
                   uint32_t C, uint32_t k);

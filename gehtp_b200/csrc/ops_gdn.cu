@@ -30,10 +30,77 @@ __global__ void conv1d_ssm_kernel(const uint16_t* __restrict__ x, const uint16_t
     }
 }
 
+// The same for C % 8 == 0 and k = 2..4 with 16-byte accesses: a thread owns 8 neighbouring channels and TT
+// consecutive tokens; the k - 1 rows before them slide through registers, so every input row is loaded
+// once per TT outputs (HBM traffic ~ (1 + (k-1)/TT) reads + 1 write per element). Sums run over j
+// ascending and skip rows outside [0, seq-k+1), exactly as above.
+constexpr int CONV_TT = 8;
+template <int K>
+__global__ void __launch_bounds__(256)
+conv1d_ssm_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, uint4* __restrict__ y, uint32_t seq,
+                      uint32_t C8) {
+    const int32_t in_rows = (seq >= (uint32_t)K) ? (int32_t)(seq - K + 1) : 0;
+    const uint32_t c8 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c8 >= C8) return;
+    const uint32_t t0 = blockIdx.y * CONV_TT;
+    float wf[K][8];            // [tap][channel]
+#pragma unroll
+    for (int j = 0; j < K; j++) {
+        const uint4 q = __ldg(w + (size_t)j * C8 + c8);
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { wf[j][2 * i] = h2f((uint16_t)(ww[i] & 0xffffu)); wf[j][2 * i + 1] = h2f((uint16_t)(ww[i] >> 16)); }
+    }
+    // rows t0-(K-1) .. t0+TT-1 of this channel group
+    constexpr int R = CONV_TT + K - 1;
+    float xf[R][8];
+    bool ok[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int32_t src = (int32_t)t0 - (K - 1) + r;
+        ok[r] = src >= 0 && src < in_rows;
+        uint4 q = make_uint4(0, 0, 0, 0);
+        if (ok[r]) q = __ldcs(x + (size_t)src * C8 + c8);
+        const uint32_t xx[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { xf[r][2 * i] = h2f((uint16_t)(xx[i] & 0xffffu)); xf[r][2 * i + 1] = h2f((uint16_t)(xx[i] >> 16)); }
+    }
+#pragma unroll
+    for (int tt = 0; tt < CONV_TT; tt++) {
+        const uint32_t t = t0 + tt;
+        if (t < seq) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < K; j++) {
+                if (ok[tt + j]) {                       // input row t - (K-1) + j
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) acc[ch] += xf[tt + j][ch] * wf[j][ch];
+                }
+            }
+            uint4 o;
+            o.x = (uint32_t)f2h(acc[0]) | ((uint32_t)f2h(acc[1]) << 16);
+            o.y = (uint32_t)f2h(acc[2]) | ((uint32_t)f2h(acc[3]) << 16);
+            o.z = (uint32_t)f2h(acc[4]) | ((uint32_t)f2h(acc[5]) << 16);
+            o.w = (uint32_t)f2h(acc[6]) | ((uint32_t)f2h(acc[7]) << 16);
+            y[(size_t)t * C8 + c8] = o;
+        }
+    }
+}
+
 void k_conv1d_ssm(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_t* y, uint32_t seq,
                   uint32_t C, uint32_t k) {
     size_t total = (size_t)seq * C;
     if (!total) return;
+    if (C % 8 == 0 && k >= 2 && k <= 4 && !((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)y)) & 15)) {
+        const uint32_t C8 = C / 8;
+        const uint32_t bx = C8 >= 128 ? 128 : 64;
+        const dim3 grid((C8 + bx - 1) / bx, (seq + CONV_TT - 1) / CONV_TT);
+        if (k == 4) conv1d_ssm_vec_kernel<4><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        else if (k == 3) conv1d_ssm_vec_kernel<3><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        else conv1d_ssm_vec_kernel<2><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        g_launches++;
+        return;
+    }
     size_t g = (total + 255) / 256;
     if (g > 148 * 16) g = 148 * 16;
     conv1d_ssm_kernel<<<(unsigned)g, 256, 0, st>>>(x, w, y, seq, C, k);

@@ -553,7 +553,15 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
         uint16_t* y = (uint16_t*)P.temp_get(a[2], (uint64_t)M * N_full * Balloc * 2u, p);
         if (!x || !w || !y) FAIL("matmul_f16 ref fail");
         p.engine = WT_ENG_HVX;
-        if (P.build) p.launch = [=](cudaStream_t st) { k_matmul_f16(st, x, w, y, M, K, N, n0, N_full, t0, t1, Bn); };
+        // Weights stored [N, K], one matrix: tensor cores (M >= 128) or the streaming GEMV (M < 32), unless
+        // the one-kernel-per-op plan or a dump hook asks for the reference's summation order bit for bit.
+        const bool nk = t1 && !t0 && !(flags & 4u);
+        if (nk) p.engine = M >= 128 ? WT_ENG_HMX : WT_ENG_HVX;
+        if (P.build) p.launch = [=](cudaStream_t st) {
+            if (nk && g.opt_fuse && !g.exact_ops &&
+                k_matmul_f16_nk(st, x, w + (size_t)n0 * K, y + n0, M, K, N, N_full, g.d_status)) return;
+            k_matmul_f16(st, x, w, y, M, K, N, n0, N_full, t0, t1, Bn);
+        };
         return;
     }
     case OP_RMSNORM2_F16: {  // exec_rmsnorm2, :1817-1872

@@ -100,8 +100,10 @@ class Emitter:
             w = self.b.add_slot(np.concatenate([nib.reshape(-1), scales.view(np.uint8).reshape(-1)]), count=K * N)
             i = self.b.add_op(OP.MATMUL_W4A16, [a_ref, S(w), y, M, K, N])
         else:
-            w = self.b.add_slot(dequant_f16(nib, scales))
-            i = self.b.add_op(OP.MATMUL_F16, [a_ref, S(w), y, M, K, N, 0])
+            # FullyConnected weights are stored [N, K] with the transposed-weight bit, as the reference's
+            # emitter stores them (compiler/tools/wtop_ops/op_matmul.cpp:50)
+            w = self.b.add_slot(np.ascontiguousarray(dequant_f16(nib, scales).T))
+            i = self.b.add_op(OP.MATMUL_F16, [a_ref, S(w), y, M, K, N, 2])
         if row_parallel:
             self.row_parallel_ops.append(i)
         return y
@@ -481,7 +483,7 @@ def build_gdn_runlist(seq=2048, hidden=1024, C=4096, k_conv=4, H=16, D=128, chun
     if quant == "w4":
         w_out = S(e.b.add_slot(np.concatenate([nib_o.reshape(-1), sc_o.view(np.uint8).reshape(-1)]), count=H * D * hidden))
     else:
-        w_out = S(e.b.add_slot(dequant_f16(nib_o, sc_o)))
+        w_out = S(e.b.add_slot(np.ascontiguousarray(dequant_f16(nib_o, sc_o).T)))     # [N, K], as the emitter stores weights
     outs = []
     for ci in range(seq // chunk):
         t0, t1 = ci * chunk, (ci + 1) * chunk
@@ -501,7 +503,7 @@ def build_gdn_runlist(seq=2048, hidden=1024, C=4096, k_conv=4, H=16, D=128, chun
         if quant == "w4":
             e.b.add_op(OP.MATMUL_W4A16, [yt, w_out, yo, chunk, H * D, hidden])
         else:
-            e.b.add_op(OP.MATMUL_F16, [yt, w_out, yo, chunk, H * D, hidden, 0])
+            e.b.add_op(OP.MATMUL_F16, [yt, w_out, yo, chunk, H * D, hidden, 2])
         outs.append(yo)
     man = dict(seq=seq, hidden=hidden, C=C, H=H, D=D, chunk=chunk, conv_temp=conv, chunk_out=outs,
                input_slot=face, quant=quant, n_ops=len(e.b.ops))

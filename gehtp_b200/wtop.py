@@ -234,6 +234,7 @@ def bind(lib):
         vp, u32 = c.c_void_p, c.c_uint32
         lib.gehtp_dev_w4_repack.argtypes = [vp, vp, u32, u32]
         lib.gehtp_dev_w4a16_matmul.argtypes = [vp, vp, vp, vp, u32, u32, u32, c.c_int]
+        lib.gehtp_dev_matmul_f16_nk.argtypes = [vp, vp, vp, u32, u32, u32]
         lib.gehtp_dev_w4a16_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32]
         lib.gehtp_dev_rmsnorm.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32]
         lib.gehtp_cuda_capture_end_replay.argtypes = [c.c_int, P(c.c_float)]

@@ -273,6 +273,7 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
 int gehtp_dev_w4_repack(const uint8_t* slot_dev, uint32_t* packed_dev, uint32_t K, uint32_t N);
 int gehtp_dev_w4a16_matmul(const uint16_t* a_dev, const uint32_t* packed_dev, const uint16_t* scales_dev,
                            uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N, int path);
+int gehtp_dev_matmul_f16_nk(const uint16_t* a_dev, const uint16_t* w_dev, uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N);
 int gehtp_dev_w4a16_swiglu(const uint16_t* a_dev, const uint32_t* pg, const uint16_t* sg,
                            const uint32_t* pu, const uint16_t* su, uint16_t* y_dev,
                            uint32_t M, uint32_t K, uint32_t N);

@@ -122,8 +122,55 @@ def test_matmul_f16_bit_exact(cuda, ref, M, K, N, t0, t1, Bn):
     b = BlobBuilder()
     sa, sw = b.add_slot(a), b.add_slot(w)
     b.add_op(OP.MATMUL_F16, [S(sa), S(sw), 1, M, K, N, flags])
-    (g,), (r,) = run_both(cuda, ref, b, [1])
+    cuda.gehtp_cuda_set_fusion(0)          # the one-kernel-per-op plan keeps the reference's ascending-k sums
+    try:
+        (g,), (r,) = run_both(cuda, ref, b, [1])
+    finally:
+        cuda.gehtp_cuda_set_fusion(1)
     assert np.array_equal(g, r)
+
+
+NK_CASES = [  # M, K, N: weights stored [N, K]; M < 32 -> streaming GEMV, M >= 128 -> tcgen05 GEMM, between -> exact kernel
+    (1, 128, 200), (3, 1024, 520), (8, 2560, 512), (20, 64, 136), (31, 256, 96), (64, 128, 128),
+    (128, 64, 128), (130, 128, 256), (256, 512, 384), (300, 1024, 1280),
+]
+
+
+@pytest.mark.parametrize("M,K,N", NK_CASES)
+def test_matmul_f16_nk_tensor_paths(cuda, ref, M, K, N):
+    """FullyConnected weights as the emitter stores them ([N, K], flags bit 1) under the default plan:
+    the fp16 gate against the reference, and bit-equality on small integers, where every summation
+    order gives the same fp32 sums (the trick of kernels/host/test_gemv_f16.c)."""
+    rng = np.random.default_rng(M + 3 * K + 7 * N)
+    for ints in (False, True):
+        if ints:
+            a = rng.integers(-4, 5, (M, K)).astype(np.float16)
+            w = rng.integers(-3, 4, (N, K)).astype(np.float16)
+        else:
+            a, w = rnd16(rng, (M, K)), rnd16(rng, (N, K), 0.1)
+        b = BlobBuilder()
+        sa, sw = b.add_slot(a), b.add_slot(w)
+        b.add_op(OP.MATMUL_F16, [S(sa), S(sw), 1, M, K, N, 2])
+        (g,), (r,) = run_both(cuda, ref, b, [1])
+        if ints:
+            assert np.array_equal(g, r)
+        else:
+            assert_fp16_close(g.view(np.float16), r.view(np.float16), "matmul_f16 [N,K] %dx%dx%d" % (M, K, N))
+
+
+def test_matmul_f16_nk_split_chunks(cuda, ref):
+    """MATMUL_F16_SPLIT over a tensor-core shape: chunks of 128 columns written into rows of N_full."""
+    rng = np.random.default_rng(45)
+    M, K, N = 256, 256, 384
+    a, w = rnd16(rng, (M, K)), rnd16(rng, (N, K), 0.2)
+    b = BlobBuilder()
+    sa, sw = b.add_slot(a), b.add_slot(w)
+    b.add_op(OP.MATMUL_F16, [S(sa), S(sw), 1, M, K, N, 2])
+    for n0 in range(0, N, 128):
+        b.add_op(OP.MATMUL_F16_SPLIT, [S(sa), S(sw), 2, M, K, N, n0, 128, 2])
+    (g1, g2), (r1, r2) = run_both(cuda, ref, b, [1, 2])
+    assert np.array_equal(g1, g2), "chunked and whole tensor-core runs differ"
+    assert_fp16_close(g1.view(np.float16), r1.view(np.float16), "split matmul")
 
 
 def test_matmul_split_equals_whole(cuda, ref):
