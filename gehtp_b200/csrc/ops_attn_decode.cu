@@ -98,6 +98,14 @@ attn_decode_split_kernel(AttnDecodeArgs A, uint32_t kv_heads_total) {
     const uint32_t n_chunks = (n_kv + CHUNK_POS - 1) / CHUNK_POS;   // <= A.nsplit by construction
     const uint32_t n_items = kv_heads_total * n_chunks;
     const uint32_t kv_elems = A.kv_heads * HD;
+    // slices past the last one that holds positions: marked empty (max = -inf, sum = 0) for the merge kernel,
+    // which reads all nsplit slices of a head
+    for (uint32_t e = blockIdx.x * blockDim.x + tid; e < kv_heads_total * (A.nsplit - n_chunks) * rep; e += gridDim.x * blockDim.x) {
+        const uint32_t r = e % rep, sl = n_chunks + (e / rep) % (A.nsplit - n_chunks), kh = e / (rep * (A.nsplit - n_chunks));
+        float* pml = A.part_ml + (((size_t)kh * A.nsplit + sl) * rep + r) * 2;
+        pml[0] = -INFINITY;
+        pml[1] = 0.0f;
+    }
     float* sm_o = (float*)(smem + STAGES * STAGE_B);     // [NWARP][rep][HD]
     float* sm_ml = sm_o + NWARP * rep * HD;               // [NWARP][rep][2]
 
@@ -687,17 +695,18 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, AttnDecodeArgs 
 }
 
 // out[h][d] = sum_s O_s[d] e^{m_s - m} / sum_s l_s e^{m_s - m}.
-// One CTA of 4 warps per query head: warp w takes chunks w, w+4, ... (all its
-// loads are independent, so they overlap), lanes split head_dim; the four warp
-// sums are added in warp order.
-__global__ void __launch_bounds__(128)
-attn_decode_merge_kernel(const float* part_o, const float* part_ml,
-                         uint16_t* out, uint32_t rep, uint32_t hd, uint32_t nsplit,
-                         const uint32_t* counter, uint32_t n_kv_add, uint32_t n_kv_const,
-                         uint32_t* bump_counter, uint32_t round_to) {
-    __shared__ float s_acc[4][256];
-    __shared__ float s_l[4];
-    __shared__ float s_m[4];
+// One CTA of 16 warps per query head. Warp w folds the slices w, w+16, ... (eight at a time, all their loads in
+// flight together) into a running (max, sum, vector) of its own; the 16 warp results are then combined in warp
+// order. Every slice of the scratch buffers is written by the split-KV kernel (an empty one as max = -inf,
+// sum = 0), so nothing here depends on the position counter and the first loads leave right after the wait.
+constexpr int MERGE_WARPS = 16;
+
+__global__ void __launch_bounds__(MERGE_WARPS * 32)
+attn_decode_merge_kernel(const float* part_o, const float* part_ml, uint16_t* out, uint32_t rep, uint32_t hd,
+                         uint32_t nsplit, uint32_t* bump_counter) {
+    __shared__ float s_acc[MERGE_WARPS][128];
+    __shared__ float s_l[MERGE_WARPS];
+    __shared__ float s_m[MERGE_WARPS];
     const uint32_t h = blockIdx.x;           // query head, = kvh * rep + r
     const uint32_t kvh = h / rep, r = h % rep;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -709,28 +718,16 @@ attn_decode_merge_kernel(const float* part_o, const float* part_ml,
     // placed here, 24 of 24 repeated steps were bit-identical.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const uint32_t n_kv = counter ? __ldcg(counter) + n_kv_add : n_kv_const;
-    uint32_t per = (n_kv + nsplit - 1) / nsplit;
-    per = (per + round_to - 1) / round_to * round_to;
-    const uint32_t n_chunks = (n_kv + per - 1) / per;          // slices that hold positions
-    const size_t row0 = ((size_t)kvh * nsplit) * rep + r;     // chunk s is at row0 + s*rep
-    // global maximum over the chunks
-    float mt = -INFINITY;
-    for (uint32_t s = threadIdx.x; s < n_chunks; s += 128) mt = fmaxf(mt, __ldcg(part_ml + (row0 + (size_t)s * rep) * 2));
-    mt = warp_max(mt);
-    if (lane == 0) s_m[warp] = mt;
-    __syncthreads();
-    mt = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    const size_t row0 = ((size_t)kvh * nsplit) * rep + r;     // slice s is at row0 + s*rep
     const uint32_t per_lane = hd / 32;       // 4 for head_dim 128, 2 for 64
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float lt = 0.0f;
-    // batches of 8 slices: all loads of a batch are issued before any is used
-    for (uint32_t s0 = warp; s0 < n_chunks; s0 += 32) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float m_run = -INFINITY, l_run = 0.0f;
+    for (uint32_t s0 = warp; s0 < nsplit; s0 += MERGE_WARPS * 8) {
         float ms[8], ls[8], ov[8][4];
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const uint32_t s = s0 + 4 * u;
-            const bool ok = s < n_chunks;
+            const uint32_t s = s0 + MERGE_WARPS * u;
+            const bool ok = s < nsplit;
             const size_t base = row0 + (size_t)(ok ? s : s0) * rep;
             ms[u] = ok ? __ldcg(part_ml + base * 2) : -INFINITY;
             ls[u] = ok ? __ldcg(part_ml + base * 2 + 1) : 0.0f;
@@ -743,21 +740,40 @@ attn_decode_merge_kernel(const float* part_o, const float* part_ml,
                 ov[u][0] = v.x; ov[u][1] = v.y; ov[u][2] = 0.0f; ov[u][3] = 0.0f;
             }
         }
+        float m_new = m_run;
+#pragma unroll
+        for (int u = 0; u < 8; u++) m_new = fmaxf(m_new, ms[u]);
+        if (m_new == -INFINITY) continue;                      // nothing but empty slices so far
+        const float keep = (m_run == -INFINITY) ? 0.0f : __expf(m_run - m_new);
+        l_run *= keep;
+#pragma unroll
+        for (int k = 0; k < 4; k++) acc[k] *= keep;
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const float w = (ms[u] == -INFINITY) ? 0.0f : __expf(ms[u] - mt);
-            lt += ls[u] * w;
+            if (ms[u] == -INFINITY) continue;                   // empty slice: its vector may be stale memory
+            const float w = __expf(ms[u] - m_new);
+            l_run += ls[u] * w;
 #pragma unroll
             for (int k = 0; k < 4; k++) acc[k] += ov[u][k] * w;
         }
+        m_run = m_new;
     }
     for (uint32_t k = 0; k < per_lane; k++) s_acc[warp][lane * per_lane + k] = acc[k];
-    if (lane == 0) s_l[warp] = lt;
+    if (lane == 0) { s_l[warp] = l_run; s_m[warp] = m_run; }
     __syncthreads();
-    const float ltot = s_l[0] + s_l[1] + s_l[2] + s_l[3];
-    for (uint32_t d = threadIdx.x; d < hd; d += 128) {
-        float a = s_acc[0][d] + s_acc[1][d] + s_acc[2][d] + s_acc[3][d];
-        out[(size_t)h * hd + d] = f2h(ltot > 0.0f ? a / ltot : 0.0f);
+    if (threadIdx.x < hd) {
+        const uint32_t d = threadIdx.x;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < MERGE_WARPS; w++) mt = fmaxf(mt, s_m[w]);
+        float num = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < MERGE_WARPS; w++) {
+            const float f = (s_m[w] == -INFINITY) ? 0.0f : __expf(s_m[w] - mt);
+            num += s_acc[w][d] * f;
+            den += s_l[w] * f;
+        }
+        out[(size_t)h * hd + d] = f2h(den > 0.0f ? num / den : 0.0f);
     }
     // all readers of the counter in this launch must be done before it moves: the
     // last block to finish advances it
@@ -869,7 +885,6 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
     // the opt-in to large dynamic shared memory is per device: one record per device ordinal
     static int have_tma[64] = {}, have_group[64] = {}, have_s128[64] = {}, have_s64[64] = {};
     bool ok = true;
-    const uint32_t merge_tile = (hd == 128 && kv_heads_total % 4 == 0) ? 16u : (uint32_t)TILE;
     if (hd == 128 && kv_heads_total % 4 == 0) {
         const CUtensorMap* tm = ring_tensor_map(a.ring, a.nslots, a.kv_heads * hd, a.no_cache != 0);
         const size_t tsmem = 1024 + (size_t)TMA_STAGES * TMA_STAGE_B + 2 * TMA_STAGES * sizeof(uint64_t);
@@ -896,8 +911,8 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
         }
     }
     if (!ok) { cudaGetLastError(); return false; }
-    ok = launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(128), 0, st,
-                    (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.counter, a.n_kv_add, a.n_kv, a.bump_counter, merge_tile) == cudaSuccess;
+    ok = launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(MERGE_WARPS * 32), 0, st,
+                    (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.bump_counter) == cudaSuccess;
     if (!ok) { cudaGetLastError(); return false; }
     g_launches += 2;
     return true;
