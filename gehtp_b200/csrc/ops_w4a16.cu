@@ -102,15 +102,23 @@ void k_w4_unpack_i8(cudaStream_t st, const uint32_t* packed, int8_t* out, uint32
 //   WALK_ANY  : ragged tail; per-group bounds tests.
 enum { WALK_ANY = 0, WALK_FULL = 1, WALK_ONE = 2 };
 
-template <int MT, int UNROLL, bool DUAL, int WALK, bool ROPE = false>
+template <int MT, int UNROLL, bool DUAL, int WALK, bool ROPE = false, bool STAGE = false>
 __global__ void __launch_bounds__(MT >= 4 ? 512 : 640)
 w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp,
                     const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2,
                     const uint16_t* __restrict__ sc2, uint16_t* __restrict__ y, uint32_t M,
                     uint32_t K, uint32_t N, uint32_t kgw, W4Epilogue ep) {
-    extern __shared__ float red[];  // [nwarps][NACC][32]
+    extern __shared__ float red[];  // [nwarps][NACC][32], then (MT == 1) the activation stage [nwarps][UNROLL][rows][144 B]
     constexpr int NACC = MT * 4 * (DUAL ? 2 : 1);
     constexpr bool FULL = WALK != WALK_ANY, ONE = WALK == WALK_ONE;
+    // STAGE (one or two rows of activations): a warp's activations for a batch of UNROLL k groups are copied into
+    // shared memory in one go right after the dependency wait (cp.async, all requests in flight together) and the
+    // fragments are read from there. Fetched group by group from global memory, every group of a warp costs one L2
+    // round trip: the activations have just been written by the kernel before, they are in L2 and nowhere nearer.
+    // With more rows the CTAs of an SM share the activations through L1 and the stage only costs occupancy
+    // (measured on B200: batch 1 decode step -8 %, batch 8 unchanged, vocabulary projection at 8 rows +35 %).
+    static_assert(!STAGE || MT == 1, "the activation stage holds one row tile");
+    constexpr uint32_t AROW = 144;        // bytes of a staged row of 64 fp16 (+16: the 8 rows of a group fall on different banks)
     // Programmatic dependent launch: let the next kernel start early, and order
     // this one after its predecessor only once the first batch of weight loads
     // (constants, independent of the predecessor) is in flight.
@@ -177,9 +185,36 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
         }
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // activations of group `rel`, fetched one group ahead of their use
+    const uint32_t last = kg1 - kg0 - 1;
+    const uint32_t rows = min(M - m0, 8u);                      // STAGE: rows staged per group
+    unsigned char* stage = (unsigned char*)(red + nwarps * NACC * 32) + (size_t)warp * UNROLL * rows * AROW;
+    // STAGE: groups relb .. relb+UNROLL-1 of this warp into its stage; returns when they have landed
+    auto stage_batch = [&](uint32_t relb) {
+        __syncwarp();                                           // the batch before has been read
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            if (!FULL && relb + u > last) break;
+            for (uint32_t c = lane; c < rows * 8; c += 32) {
+                const uint32_t r = c >> 3, col = c & 7;
+                const uint16_t* src = a + (size_t)(m0 + r) * K + (size_t)(kg0 + relb + u) * 64 + col * 8;
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + ((size_t)u * rows + r) * AROW + col * 16);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+    };
+    // activations of group `rel`: STAGE reads slot rel % UNROLL of the stage (rows past M read row M-1), the other
+    // forms fetch from global memory one group ahead of their use
     uint4 bc[MT][2];
     auto load_act = [&](uint4 (&b)[MT][2], uint32_t rel) {
+        if (STAGE) {
+            const unsigned char* sp = stage + ((size_t)(rel % UNROLL) * rows + min((uint32_t)g, rows - 1)) * AROW + t * 32;
+            b[0][0] = *(const uint4*)sp;
+            b[0][1] = *(const uint4*)(sp + 16);
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < MT; i++) {
             const uint4* ap = (const uint4*)(arow[i] + rel * 128u);   // 64 fp16 per group
@@ -187,12 +222,12 @@ w4a16_skinny_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ wp
             b[i][1] = ld_ordered(ap + 1);
         }
     };
-    // MT <= 2: the next group's activations are requested one group ahead; wider
+    // MT <= 2 without a stage: the next group's activations are requested one group ahead; wider
     // row tiles (MT = 4) have no registers for that and load them at their use.
-    constexpr bool PRE = MT <= 2;
+    constexpr bool PRE = MT <= 2 && !STAGE;
     if (PRE) load_act(bc, 0);
-    const uint32_t last = kg1 - kg0 - 1;
     auto batch = [&](uint32_t relb, bool more) {   // groups relb .. relb+UNROLL-1
+        if (STAGE) stage_batch(relb);
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             if (!FULL && relb + u > last) break;
@@ -325,6 +360,22 @@ static uint32_t skinny_kgw(uint32_t KG, uint32_t strips) {
     return fallback ? fallback : 8;
 }
 
+// Launch of a one-row-tile form: dynamic shared memory = the reduction buffer + the activation stage
+// (M <= 2: nwarps x UNROLL groups x M rows x 144 bytes), opted in per device when it passes 48 KB.
+template <int UNROLL, bool DUAL, int WALK, bool ROPE, typename... Args>
+static void launch_skinny1(dim3 grid, dim3 block, uint32_t M, cudaStream_t st, Args... args) {
+    static int have[64];
+    const uint32_t nwarps = block.x / 32;
+    const size_t red = (size_t)nwarps * (DUAL ? 8 : 4) * 32 * sizeof(float);
+    if (M > 2) {
+        launch_pdl(w4a16_skinny_kernel<1, UNROLL, DUAL, WALK, ROPE, false>, grid, block, red, st, args...);
+        return;
+    }
+    const size_t smem = red + (size_t)nwarps * UNROLL * M * 144;
+    if (smem > 48 * 1024 && !ensure_dyn_smem(w4a16_skinny_kernel<1, UNROLL, DUAL, WALK, ROPE, true>, 200 * 1024, have)) return;
+    launch_pdl(w4a16_skinny_kernel<1, UNROLL, DUAL, WALK, ROPE, true>, grid, block, smem, st, args...);
+}
+
 #define SKINNY_ARGS(P1, S1, P2, S2) a, (const uint4*)(P1), S1, (const uint4*)(P2), (const uint16_t*)(S2), y, M, K, N, kgw, ep
 
 void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
@@ -335,13 +386,12 @@ void k_w4a16_skinny(cudaStream_t st, const uint16_t* a, const uint32_t* packed, 
     const dim3 block(nwarps * 32);
     if (M <= 8) {
         const dim3 grid(N / 16, 1);
-        const size_t smem = (size_t)nwarps * 4 * 32 * sizeof(float);
         if (kgw == 8 && KG % 8 == 0)
-            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ONE>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+            launch_skinny1<8, false, WALK_ONE, false>(grid, block, M, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
         else if (kgw % 8 == 0 && KG % 8 == 0)
-            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_FULL>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+            launch_skinny1<8, false, WALK_FULL, false>(grid, block, M, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
         else
-            launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ANY>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+            launch_skinny1<8, false, WALK_ANY, false>(grid, block, M, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     } else if (M <= 16 || nwarps > 16) {
         const dim3 grid(N / 16, (M + 15) / 16);
         const size_t smem = (size_t)nwarps * 8 * 32 * sizeof(float);
@@ -362,8 +412,7 @@ bool k_w4a16_skinny_qkv_rope(cudaStream_t st, const uint16_t* a, const uint32_t*
     const uint32_t kgw = 8, nwk = KG / 8;
     uint16_t* y = nullptr;
     const dim3 grid(N / 32, 1), block(2 * nwk * 32);
-    const size_t smem = (size_t)2 * nwk * 4 * 32 * sizeof(float);
-    launch_pdl(w4a16_skinny_kernel<1, 8, false, WALK_ONE, true>, grid, block, smem, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
+    launch_skinny1<8, false, WALK_ONE, true>(grid, block, M, st, SKINNY_ARGS(packed, sc, nullptr, nullptr));
     g_launches++;
     return true;
 }
@@ -381,9 +430,9 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
         if (KG % 4 == 0 && KG / 4 <= 20) {   // whole 4-group warps: the branch-free variant
             kgw = 4;
             nwarps = KG / 4;
-            launch_pdl(w4a16_skinny_kernel<1, 4, true, WALK_ONE>, grid, dim3(nwarps * 32), (size_t)nwarps * 8 * 32 * sizeof(float), st, SKINNY_ARGS(pg, sg, pu, su));
+            launch_skinny1<4, true, WALK_ONE, false>(grid, dim3(nwarps * 32), M, st, SKINNY_ARGS(pg, sg, pu, su));
         } else {
-            launch_pdl(w4a16_skinny_kernel<1, 4, true, WALK_ANY>, grid, dim3(nwarps * 32), (size_t)nwarps * 8 * 32 * sizeof(float), st, SKINNY_ARGS(pg, sg, pu, su));
+            launch_skinny1<4, true, WALK_ANY, false>(grid, dim3(nwarps * 32), M, st, SKINNY_ARGS(pg, sg, pu, su));
         }
     } else {
         const dim3 grid(N / 16, (M + 15) / 16);
