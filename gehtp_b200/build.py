@@ -23,6 +23,7 @@ UNITS = {
     "api_kernels.cu": [],
     "ops_elem.cu": ["--fmad=false"],
     "ops_gdn.cu": ["--fmad=false"],
+    "gdn_delta_mma.cu": [],
     "ops_attn.cu": [],
     "ops_attn_decode.cu": [],
     "ops_attn_prefill.cu": [],

@@ -76,6 +76,9 @@ void k_conv1d_ssm(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_
                   uint32_t C, uint32_t k);
 void k_conv1d_step(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_t* y, float* win,
                    uint32_t C, uint32_t dc);
+// Tensor-core form of the chunked delta rule (gdn_delta_mma.cu): head dim 64 or 128. false: shape not taken.
+bool k_delta_chunk_mma(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_t* q, const uint16_t* beta,
+                       const uint16_t* g, uint16_t* y, float* S, uint32_t c, uint32_t ntok, uint32_t H, uint32_t D, uint32_t q_raw);
 void k_delta_chunk(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_t* q,
                    const uint16_t* beta, const uint16_t* g, uint16_t* y, float* S, uint32_t c,
                    uint32_t ntok, uint32_t H, uint32_t D, uint32_t q_raw);

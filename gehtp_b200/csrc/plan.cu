@@ -671,7 +671,11 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
         if ((uint64_t)4 * c * (D + 1) * 4 + 17408 > 227u * 1024u) FAIL("delta chunk c=%u D=%u exceeds shared memory", c, D);
         float* S = (float*)g.st_buf[si];
         p.engine = WT_ENG_HVX;
-        if (P.build) p.launch = [=](cudaStream_t st) { k_delta_chunk(st, k, v, q, be, gg, y, S, c, ntok, H, D, q_raw); };
+        if (P.build) p.launch = [=](cudaStream_t st) {
+            // fused plans take the tensor-core form; the one-kernel-per-op plan keeps the scalar loops in the reference's order
+            if (g.opt_fuse && !g.exact_ops && k_delta_chunk_mma(st, k, v, q, be, gg, y, S, c, ntok, H, D, q_raw)) return;
+            k_delta_chunk(st, k, v, q, be, gg, y, S, c, ntok, H, D, q_raw);
+        };
         return;
     }
     default:

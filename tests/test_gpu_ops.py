@@ -327,6 +327,49 @@ def test_conv1d_and_delta(cuda, ref):
     ref.wt_exec_state_reset()
 
 
+@pytest.mark.parametrize("H,D,c,nchunks", [(4, 128, 64, 6), (2, 64, 64, 4), (3, 128, 40, 3)])
+def test_delta_chunk_tensor_core_form(cuda, ref, H, D, c, nchunks):
+    """The mma form of the chunked delta rule (fused plans) against the scalar form (one kernel per op) and the
+    reference, over several chunks that carry the fp32 state: y of every chunk within the fp16 gate of the reference,
+    within one fp16 step of the largest output of the scalar form (hi + lo operands keep the products fp32-class; what
+    differs is the order of the fp32 sums), and the final state equal to the scalar form's to 1e-5 of its largest entry."""
+    rng = np.random.default_rng(500 + D + c)
+    ntok = c
+    b = BlobBuilder()
+    b.add_states([H * D * D * 4])
+    outs = []
+    for ch in range(nchunks):
+        kk = rnd16(rng, (H, ntok, D))
+        kk = (kk / np.linalg.norm(kk.astype(np.float32), axis=-1, keepdims=True)).astype(np.float16)
+        vv, qq = rnd16(rng, (H, ntok, D)), rnd16(rng, (H, ntok, D))
+        beta = (1 / (1 + np.exp(-rng.standard_normal((H, ntok))))).astype(np.float16)
+        gg = np.log(1 / (1 + np.exp(-rng.standard_normal((H, ntok))))).astype(np.float16) * np.float16(0.25)
+        sl = [b.add_slot(a) for a in (kk, vv, qq, beta, gg)]
+        b.add_op(OP.DELTA_CHUNK, [S(sl[0]), S(sl[1]), S(sl[2]), S(sl[3]), S(sl[4]), 1 + ch, ST(0), c, ntok, H, D, ch & 1])
+        outs.append(1 + ch)
+    buf = b.build()
+    res, states = {}, {}
+    for name, lib, fusion in (("mma", cuda, 1), ("scalar", cuda, 0), ("ref", ref, None)):
+        if fusion is not None:
+            cuda.gehtp_cuda_set_fusion(fusion)
+        lib.wt_exec_state_reset()
+        eng = Engine(lib, buf)
+        eng.run_io(None, outs[0], None)
+        res[name] = [eng.temp(t).view(np.float16).reshape(H, ntok, D).copy() for t in outs]
+        if lib is cuda:
+            st = np.zeros(H * D * D, np.float32)
+            assert cuda.gehtp_cuda_state_read(0, st.ctypes.data, st.nbytes) == 0
+            states[name] = st
+        eng.shutdown()
+        lib.wt_exec_state_reset()
+    cuda.gehtp_cuda_set_fusion(1)
+    for ch in range(nchunks):
+        assert_fp16_close(res["mma"][ch], res["ref"][ch], "delta chunk %d vs reference" % ch)
+        a, sc = res["mma"][ch].astype(np.float64), res["scalar"][ch].astype(np.float64)
+        assert np.abs(a - sc).max() <= 2.0 ** -10 * np.abs(sc).max(), ch
+    assert np.abs(states["mma"] - states["scalar"]).max() <= 1e-5 * np.abs(states["scalar"]).max()
+
+
 def test_error_strings_match_reference(cuda, ref):
     """Bad operands are refused before any launch, with the reference's message and op index."""
     cases = []
