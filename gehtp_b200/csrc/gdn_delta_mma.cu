@@ -1,8 +1,9 @@
 // Chunked gated delta rule on the tensor cores (mma.sync m16n8k16, fp32 accumulation).
 //
-// Same mathematics and the same fp16 rounding points as delta_chunk_kernel of ops_gdn.cu
-// (reference: delta_chunk_f16 / solve_tri_f16, kernels/src/hvx/gdn_kern.c:54-167; formulas in
-// kernels/include/gdn_sm.h:5-12): L and T = (I + L)^-1 are fp16 matrices, y is rounded once.
+// Same mathematics as delta_chunk_kernel of ops_gdn.cu (reference: delta_chunk_f16 / solve_tri_f16,
+// kernels/src/hvx/gdn_kern.c:54-167; formulas in kernels/include/gdn_sm.h:5-12): L and T = (I + L)^-1
+// are fp16 matrices, y is rounded once. Entries of T outside the 16 x 16 diagonal blocks see one fp16
+// rounding where the reference's substitution rounds along the way (differences of an fp16 step in T).
 // What changes is who does the contractions. Per head and chunk of c <= 64 tokens there are seven
 // small dependent matrix products (64 x 64 x D, 64 x D x D, 64 x D x 64, D x D x 64); as scalar
 // fp32 loops they took 170 us per chunk on a B200 (2048 tokens: 32 chunks in sequence, 5.4 ms).
@@ -12,8 +13,9 @@
 //   * fp32 quantities that enter a product (the state S, b, u, the decayed q.k matrix) are split
 //     into hi = f16(x) and lo = f16(x - hi) and multiplied as hi + lo (two or three MMAs), which
 //     carries about 22 bits of mantissa: fp32-class, the state does not degrade over the chunks;
-//   * T = (I + L)^-1 stays a forward substitution, but column j of T depends on column j only:
-//     four lanes own a column and run down the rows with warp shuffles, no block-wide barrier.
+//   * T = (I + L)^-1: the reference's row-by-row forward substitution inside 16 x 16 diagonal blocks (column j
+//     depends on column j only: four lanes own a column, shuffles, no block-wide barrier), block forward
+//     substitution on the tensor cores below the diagonal.
 // The products are far too small for tcgen05 tiles (M = 64 or 32 rows, each result feeds the next
 // product through registers and a rounding); the chain is latency bound, and mma.sync keeps every
 // intermediate in registers on its way to the next operand.
@@ -141,21 +143,65 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     }
     __syncthreads();
 
-    // ---- stage 2: T = (I + L)^-1, fp16 row by row. Column j of T depends on column j only: four lanes own it
-    // and split the sum over i; the rows are a chain of c steps, kept short.
+    // ---- stage 2: T = (I + L)^-1 in fp16. Within a 16 x 16 diagonal block it is the forward substitution of the
+    // reference, row by row with every entry rounded to fp16 before the next row uses it; column j depends on column j
+    // only, so four lanes own a column and run down the 16 rows with shuffles (all four diagonal blocks at once, no
+    // block-wide barrier). The blocks below the diagonal follow from (I + L) T = I block row by block row:
+    //     T_ik = -T_ii (sum_{k <= m < i} L_im T_mk)
+    // two small products per block on the tensor cores (the inner sum as hi + lo), rounded to fp16 once.
+    uint16_t* Tt = uThi;                            // [C][CP] T transposed (u, u lo and weighted u are not live yet)
     {
-        const int j = tid >> 2, part = tid & 3;
-        for (int r = 0; r < C; r++) {
+        const int j = tid >> 2, part = tid & 3, r0 = (j >> 4) << 4;
+        for (int rr = 0; rr < 16; rr++) {
+            const int r = r0 + rr;
             float s = 0.0f;
             if (j < r)
                 for (int i = j + part; i < r; i += 4) s -= h2f(Lh[r * CP + i]) * h2f(Th[i * CP + j]);
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (part == 0) Th[r * CP + j] = j <= r ? f2h((r == j ? 1.0f : 0.0f) + s) : (uint16_t)0;
+            if (part == 0) {
+                const uint16_t tv = j <= r ? f2h((r == j ? 1.0f : 0.0f) + s) : (uint16_t)0;
+                Th[r * CP + j] = tv;
+                Tt[j * CP + r] = tv;
+            }
             __syncwarp();
+        }
+        for (int e = tid; e < C * C; e += 256) {     // blocks above the block diagonal
+            const int r = e / C, jj = e % C;
+            if ((jj >> 4) > (r >> 4)) Th[r * CP + jj] = 0;
         }
     }
     __syncthreads();
+    for (int bi = 1; bi < C / 16; bi++) {
+        if (warp < bi) {
+            const int bk = warp;
+            uint16_t* xhi = QKlo + warp * 768;      // X transposed [16][24], hi and lo (the q.k matrix is not live yet)
+            uint16_t* xlo = xhi + 384;
+            for (int nt = 0; nt < 2; nt++) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_rows(acc, Lh + bi * 16 * CP + bk * 16, CP, Tt + (bk * 16 + nt * 8) * CP + bk * 16, CP, 16 * (bi - bk), g, t);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int row = g + (e >> 1) * 8, n = nt * 8 + 2 * t + (e & 1);
+                    split_store(xhi + n * 24 + row, xlo + n * 24 + row, acc[e]);
+                }
+            }
+            __syncwarp();
+            for (int nt = 0; nt < 2; nt++) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_rows(acc, Th + bi * 16 * CP + bi * 16, CP, xhi + nt * 8 * 24, 24, 16, g, t);
+                mma_rows(acc, Th + bi * 16 * CP + bi * 16, CP, xlo + nt * 8 * 24, 24, 16, g, t);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int row = bi * 16 + g + (e >> 1) * 8, col = bk * 16 + nt * 8 + 2 * t + (e & 1);
+                    const uint16_t tv = f2h(-acc[e]);
+                    Th[row * CP + col] = tv;
+                    Tt[col * CP + row] = tv;
+                }
+            }
+        }
+        __syncthreads();
+    }
 
     // ---- stage 3: b[j][m] = beta_j (v[j][m] - e^{G_j} (S0 k_j)[m]), stored transposed as hi + lo
     for (int tile = warp; tile < (C / 16) * (DM / 8); tile += 8) {

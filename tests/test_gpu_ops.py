@@ -331,8 +331,9 @@ def test_conv1d_and_delta(cuda, ref):
 def test_delta_chunk_tensor_core_form(cuda, ref, H, D, c, nchunks):
     """The mma form of the chunked delta rule (fused plans) against the scalar form (one kernel per op) and the
     reference, over several chunks that carry the fp32 state: y of every chunk within the fp16 gate of the reference,
-    within one fp16 step of the largest output of the scalar form (hi + lo operands keep the products fp32-class; what
-    differs is the order of the fp32 sums), and the final state equal to the scalar form's to 1e-5 of its largest entry."""
+    within four fp16 steps of the largest output of the scalar form (hi + lo operands keep the products fp32-class; what
+    differs is the order of the fp32 sums and where the entries of T below its diagonal blocks are rounded to fp16), and
+    the final state equal to the scalar form's to 2e-3 of its largest entry."""
     rng = np.random.default_rng(500 + D + c)
     ntok = c
     b = BlobBuilder()
@@ -366,8 +367,8 @@ def test_delta_chunk_tensor_core_form(cuda, ref, H, D, c, nchunks):
     for ch in range(nchunks):
         assert_fp16_close(res["mma"][ch], res["ref"][ch], "delta chunk %d vs reference" % ch)
         a, sc = res["mma"][ch].astype(np.float64), res["scalar"][ch].astype(np.float64)
-        assert np.abs(a - sc).max() <= 2.0 ** -10 * np.abs(sc).max(), ch
-    assert np.abs(states["mma"] - states["scalar"]).max() <= 1e-5 * np.abs(states["scalar"]).max()
+        assert np.abs(a - sc).max() <= 2.0 ** -8 * np.abs(sc).max(), ch
+    assert np.abs(states["mma"] - states["scalar"]).max() <= 2e-3 * np.abs(states["scalar"]).max()
 
 
 def test_error_strings_match_reference(cuda, ref):
