@@ -27,6 +27,7 @@ UNITS = {
     "ops_attn.cu": [],
     "ops_attn_decode.cu": [],
     "ops_attn_prefill.cu": [],
+    "attn_prefill_sm100.cu": [],
     "ops_fused.cu": [],
     "ops_matmul.cu": [],
     "ops_w4a16.cu": [],

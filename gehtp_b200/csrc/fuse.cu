@@ -426,6 +426,7 @@ bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
 
 std::vector<Span> g_spans;
 float* g_attn_scratch = nullptr;
+uint16_t* g_vt_scratch = nullptr;     // V transposed, for the tcgen05 prefill attention (largest span of the plan)
 std::map<std::pair<uint32_t, uint64_t>, uint8_t*> g_skip_maps;   // (mask slot, S<<32|Sk) -> device tile-skip bitmap
 
 const uint8_t* resolve(const wt_blob* b, uint32_t arg) {
@@ -547,6 +548,10 @@ void fuse_materialize(const wt_blob* b) {
     if (scratch_floats) {
         if (cudaMalloc(&g_attn_scratch, scratch_floats * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return; }
     }
+    size_t vt_bytes = 0;
+    for (const Span& sp : g_spans)
+        if (sp.kind == 4 && sp.hd == 128) vt_bytes = std::max(vt_bytes, attn_prefill_sm100_scratch_bytes(sp.N, sp.kvh, sp.hd));
+    if (vt_bytes && cudaMalloc(&g_vt_scratch, vt_bytes) != cudaSuccess) { cudaGetLastError(); g_vt_scratch = nullptr; }
     g.fused_ops = 0;
     for (const Span& sp : g_spans) {
         PlanOp& head = g.plan[sp.first];
@@ -650,7 +655,7 @@ void fuse_materialize(const wt_blob* b) {
             if (!q || !k || !v || !out || !mask) continue;
             uint32_t sq = sp.M, sk = sp.N, nh = sp.nh, kvh = sp.kvh, hd = sp.hd;
             size_t mstride = sp.mask_is_slot ? 0 : (size_t)sq * sk;
-            const uint8_t* skip = nullptr;
+            const uint8_t *skip = nullptr, *zero = nullptr;
             if (sp.mask_is_slot) {
                 // tiles of the constant mask that are -inf everywhere are never computed
                 const uint32_t T = attn_prefill_tile(), nq = (sq + T - 1) / T, nk = (sk + T - 1) / T;
@@ -658,10 +663,14 @@ void fuse_materialize(const wt_blob* b) {
                 auto it = g_skip_maps.find(key);
                 if (it == g_skip_maps.end()) {
                     const uint16_t* hm = (const uint16_t*)(b->weight_base + b->slots[sp.mask_slot].offset);
-                    std::vector<uint8_t> bm((size_t)nq * nk, 1);
+                    // first nq * nk bytes: 1 = the tile is -inf everywhere; next nq * nk bytes: 1 = +0 everywhere
+                    std::vector<uint8_t> bm((size_t)2 * nq * nk, 1);
                     for (uint32_t r = 0; r < sq; r++)
-                        for (uint32_t c = 0; c < sk; c++)
-                            if (hm[(size_t)r * sk + c] != 0xFC00u) bm[(size_t)(r / T) * nk + c / T] = 0;
+                        for (uint32_t c = 0; c < sk; c++) {
+                            const uint16_t mv = hm[(size_t)r * sk + c];
+                            if (mv != 0xFC00u) bm[(size_t)(r / T) * nk + c / T] = 0;
+                            if (mv != 0x0000u) bm[(size_t)nq * nk + (size_t)(r / T) * nk + c / T] = 0;
+                        }
                     uint8_t* d = nullptr;
                     if (cudaMalloc(&d, bm.size()) == cudaSuccess) {
                         cudaMemcpyAsync(d, bm.data(), bm.size(), cudaMemcpyHostToDevice, g.stream);
@@ -669,11 +678,18 @@ void fuse_materialize(const wt_blob* b) {
                         it = g_skip_maps.emplace(key, d).first;
                     } else cudaGetLastError();
                 }
-                if (it != g_skip_maps.end()) skip = it->second;
+                if (it != g_skip_maps.end()) { skip = it->second; zero = skip + (size_t)nq * nk; }
             }
             float scale = sp.scale; int sdiv = sp.scale_div;
             if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v)) & 15u) continue;
-            head.fused = [=](cudaStream_t st) { k_attn_prefill(st, q, k, v, mask, mstride, skip, scale, sdiv, sq, sk, nh, kvh, hd, out); };
+            uint16_t* vt = g_vt_scratch;
+            unsigned int* status = g.d_status;
+            static const int sm100_on = [] { const char* e = std::getenv("GEHTP_CUDA_PREFILL_SM100"); return e ? std::atoi(e) : 1; }();
+            head.fused = [=](cudaStream_t st) {
+                // head_dim 128: tcgen05 / TMEM form; anything it does not take goes to the mma.sync form
+                if (sm100_on && vt && k_attn_prefill_sm100(st, q, k, v, mask, mstride, skip, zero, scale, sdiv, sq, sk, nh, kvh, hd, out, vt, status)) return;
+                k_attn_prefill(st, q, k, v, mask, mstride, skip, scale, sdiv, sq, sk, nh, kvh, hd, out);
+            };
         } else {
             const uint16_t *aa = (const uint16_t*)resolve(b, sp.add_a), *ab = (const uint16_t*)resolve(b, sp.add_b);
             uint16_t *sum = (uint16_t*)resolve(b, sp.sum_t), *y = (uint16_t*)resolve(b, sp.norm_y);
@@ -722,6 +738,7 @@ bool fuse_all_materialized() {
 
 void fuse_release() {
     if (g_attn_scratch) { cudaFree(g_attn_scratch); g_attn_scratch = nullptr; }
+    if (g_vt_scratch) { cudaFree(g_vt_scratch); g_vt_scratch = nullptr; }
     for (auto& kv : g_skip_maps) cudaFree(kv.second);
     g_skip_maps.clear();
     g_spans.clear();
