@@ -45,6 +45,7 @@ struct __align__(8) ABars {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full;
     uint64_t pair[4];         // the two softmax warps of a row quarter meet here (bounded, unlike bar.sync)
     uint32_t tmem_base, abort_flag;
+    unsigned long long live, zero;   // bit kt: tile (qt, kt) has a live entry / a mask of +0 everywhere (n_kt <= 64)
     float xmax[2][128];       // tile maxima of the two column halves of a row
     float xsum[2][128];
 };
@@ -68,6 +69,31 @@ __device__ __forceinline__ float score_of(float dot, float rscale, float maskv) 
     return round_h(__fadd_rn(s, maskv));
 }
 
+// Two fp32 values -> one half2 word (low half = a) in one instruction, and back. The softmax warps are bound by
+// the ALU pipe: the score roundings run on pairs.
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t h) { return __half22float2(*(const __half2*)&h); }
+// the scores of two neighbouring positions with the roundings of the op chain; mk = their two mask values (half2 word)
+template <bool MASKED>
+__device__ __forceinline__ float2 score2(float d0, float d1, float rscale, uint32_t mk) {
+    float2 f = unpack_h2(pack_h2(d0, d1));
+    f = unpack_h2(pack_h2(__fmul_rn(f.x, rscale), __fmul_rn(f.y, rscale)));
+    if (MASKED) {
+        const float2 m = unpack_h2(mk);
+        f = unpack_h2(pack_h2(__fadd_rn(f.x, m.x), __fadd_rn(f.y, m.y)));
+    }
+    return f;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -78,6 +104,31 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// P of one row for 64 positions: 2^(s log2e + m_off) rounded to fp16, eight 16-byte chunks; adds the unrounded values to l
+template <bool MASKED>
+__device__ __forceinline__ void probs64(uint32_t taddr, const uint4 (&mk)[8], float rscale, float m_off, float& l, uint4 (&pk)[8]) {
+    const float LOG2E = 1.4426950408889634f;
+#pragma unroll
+    for (int c = 0; c < 2; c++) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        const uint32_t* m32 = (const uint32_t*)mk + c * 16;
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int e0 = ch * 8 + 2 * i;
+                const float2 sc = score2<MASKED>(__uint_as_float(v[e0]), __uint_as_float(v[e0 + 1]), rscale, MASKED ? m32[e0 >> 1] : 0u);
+                const float p0 = ex2(fmaf(sc.x, LOG2E, m_off)), p1 = ex2(fmaf(sc.y, LOG2E, m_off));
+                l += p0 + p1;
+                w[i] = pack_h2(p0, p1);
+            }
+            pk[c * 4 + ch] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
 }
 
 // true: the 128 x 128 tile (qt, kt) has no live entry
@@ -137,11 +188,22 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp == 3) {
+        // which key tiles this CTA works on, read once (the tables are constants: no need to wait for the predecessor)
+        unsigned long long lv = 0, zr = 0;
+        for (uint32_t kt = lane; kt < n_kt; kt += 32) {
+            if (!tile_dead(A.skip, qt, kt, nq64, nk64)) lv |= 1ull << kt;
+            if (tile_zero(A.zero, qt, kt, nq64, nk64)) zr |= 1ull << kt;
+        }
+        for (int o = 16; o; o >>= 1) { lv |= __shfl_xor_sync(0xffffffffu, lv, o); zr |= __shfl_xor_sync(0xffffffffu, zr, o); }
+        if (lane == 0) { bars->live = lv; bars->zero = zr; }
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = bars->tmem_base;
     const uint32_t tm_o = tmem + 256;
+    const unsigned long long live = bars->live, zero_tiles = bars->zero;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -153,7 +215,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             uint32_t ik = 0, iv = 0;
             for (int pass = 0; pass < 2 && !*abort_flag; pass++)
                 for (uint32_t kt = 0; kt < n_kt && !*abort_flag; kt++) {
-                    if (tile_dead(A.skip, qt, kt, nq64, nk64)) continue;
+                    if (!((live >> kt) & 1ull)) continue;
                     {
                         const uint32_t s = ik & 1, ph = (ik >> 1) & 1;
                         if (!mbar_wait(&bars->k_empty[s], ph ^ 1)) { *abort_flag = 1; break; }
@@ -202,15 +264,14 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
             };
             // pass 1
             for (uint32_t kt = 0; ok && kt < n_kt && !*abort_flag; kt++) {
-                if (tile_dead(A.skip, qt, kt, nq64, nk64)) continue;
+                if (!((live >> kt) & 1ull)) continue;
                 ok = issue_s();
             }
             // pass 2: S of the next live tile is issued before P V of the current one
-            uint32_t live = 0;
-            for (uint32_t kt = 0; kt < n_kt; kt++) live += tile_dead(A.skip, qt, kt, nq64, nk64) ? 0 : 1;
-            if (ok && live && !*abort_flag) ok = issue_s();
-            for (uint32_t j = 0; ok && j < live && !*abort_flag; j++) {
-                if (j + 1 < live) ok = issue_s();
+            const uint32_t n_live = (uint32_t)__popcll(live);
+            if (ok && n_live && !*abort_flag) ok = issue_s();
+            for (uint32_t j = 0; ok && j < n_live && !*abort_flag; j++) {
+                if (j + 1 < n_live) ok = issue_s();
                 if (!ok) break;
                 const uint32_t s = j & 1;
                 if (!mbar_wait(&bars->v_full[s], (j >> 1) & 1) || !mbar_wait(&bars->p_full, j & 1)) { ok = false; break; }
@@ -263,9 +324,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         for (int pass = 0; pass < 2 && ok; pass++) {
             uint32_t jp = 0;
             for (uint32_t kt = 0; kt < n_kt && ok; kt++) {
-                if (tile_dead(A.skip, qt, kt, nq64, nk64)) continue;
+                if (!((live >> kt) & 1ull)) continue;
                 // a tile whose mask is +0 everywhere and that lies inside the sequence needs no mask values
-                const bool plain = (!mrow || tile_zero(A.zero, qt, kt, nq64, nk64)) && (kt + 1) * BKV <= A.seq_k;
+                const bool plain = (!mrow || ((zero_tiles >> kt) & 1ull)) && (kt + 1) * BKV <= A.seq_k;
                 uint4 mk[8];
                 if (!plain) mask64(kt, half * 64, mk);
                 const uint32_t buf = is & 1;
@@ -285,9 +346,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
                             for (int i = 0; i < 32; i++) mt = fmaxf(mt, __uint_as_float(v[i]));
                         } else {
-                            const uint16_t* m16 = (const uint16_t*)mk + c * 32;
+                            const uint32_t* m32 = (const uint32_t*)mk + c * 16;
 #pragma unroll
-                            for (int i = 0; i < 32; i++) mt = fmaxf(mt, score_of(__uint_as_float(v[i]), rscale, h2f(m16[i])));
+                            for (int i = 0; i < 16; i++) {
+                                const float2 sc = score2<true>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), rscale, m32[i]);
+                                mt = fmaxf(mt, fmaxf(sc.x, sc.y));
+                            }
                         }
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -302,35 +366,23 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
                         if (!pair_sync()) { ok = false; break; }
                         m_run = fmaxf(bars->xmax[0][row], bars->xmax[1][row]);
                     }
-                    // P of this warp's 64 columns: 8 chunks of 8 positions, 16 bytes each, swizzled by row
+                    // P of this warp's 64 columns: 8 chunks of 8 positions, 16 bytes each, swizzled by row. The values are
+                    // formed first; the buffer (still read by P V of the tile before) is waited for only then.
+                    uint4 pk[8];
+                    // exp(s - m) as 2^(s log2e - m log2e); a row with no live position (m = -inf) gives zeros through m_off = 0
+                    const float m_off = m_run == -INFINITY ? 0.0f : -m_run * 1.4426950408889634f;
+                    if (plain) probs64<false>(tmem + lane_addr + buf * 128 + half * 64, mk, rscale, m_off, l_run, pk);
+                    else probs64<true>(tmem + lane_addr + buf * 128 + half * 64, mk, rscale, m_off, l_run, pk);
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->s_empty[buf]);
                     if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_empty, (jp & 1) ^ 1))) { ok = false; break; }
                     unsigned char* prow = sP + half * TILE_BYTES + row * 128;
 #pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem + lane_addr + buf * 128 + half * 64 + c * 32, v);
-                        const uint16_t* m16 = (const uint16_t*)mk + c * 32;
-#pragma unroll
-                        for (int ch = 0; ch < 4; ch++) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const int e0 = ch * 8 + 2 * i;
-                                const float s0 = score_of(__uint_as_float(v[e0]), rscale, plain ? 0.0f : h2f(m16[e0]));
-                                const float s1 = score_of(__uint_as_float(v[e0 + 1]), rscale, plain ? 0.0f : h2f(m16[e0 + 1]));
-                                const float p0 = m_run == -INFINITY ? 0.0f : __expf(s0 - m_run);
-                                const float p1 = m_run == -INFINITY ? 0.0f : __expf(s1 - m_run);
-                                l_run += p0 + p1;
-                                w[i] = (uint32_t)f2h(p0) | ((uint32_t)f2h(p1) << 16);
-                            }
-                            const uint32_t chunk = (uint32_t)(c * 4 + ch);
-                            *(uint4*)(prow + ((chunk ^ (row & 7u)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
+                    for (uint32_t chunk = 0; chunk < 8; chunk++) *(uint4*)(prow + ((chunk ^ (row & 7u)) << 4)) = pk[chunk];
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) { mbar_arrive(&bars->s_empty[buf]); mbar_arrive(&bars->p_full); }
+                    if (lane == 0) mbar_arrive(&bars->p_full);
                     jp++;
                 }
                 is++;
@@ -416,7 +468,7 @@ bool k_attn_prefill_sm100(cudaStream_t st, const uint16_t* q, const uint16_t* k,
                           size_t mask_head_stride, const uint8_t* skip, const uint8_t* zero, float scale, int scale_div, uint32_t seq_q,
                           uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out, uint16_t* vt_scratch,
                           unsigned int* status) {
-    if (hd != 128 || !seq_q || !seq_k || !kvh || nh % kvh || !vt_scratch) return false;
+    if (hd != 128 || !seq_q || !seq_k || seq_k > 64 * BKV || !kvh || nh % kvh || !vt_scratch) return false;
     if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out) | ((uintptr_t)vt_scratch)) & 15u) return false;
     const uint32_t ld = (seq_k + 7) / 8 * 8;
     CUtensorMap tq, tk, tv;
