@@ -794,9 +794,10 @@ def run_config(args):
         line.update(metric="gated_delta_layer_seq2048_tokens_per_s", value=seq / ms * 1e3, unit="tok/s", ms_per_step=ms, gpu_launches=launches,
                     config={"workload": "config 5: gated delta-rule layer, 2048 tokens, conv1d k=4 over 4096 channels, 16 heads of 128, 32 chunks of 64, W4A16 in/out projections from hidden 1024"},
                     e2e={"value": seq / e2e_ms * 1e3, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h.nbytes), "d2h_bytes_per_step": int(out_h.nbytes)},
-                    roofline={"bound": "hbm", "kernel": "delta_chunk_kernel (32 sequential launches)", "achieved": qkvy_bytes / max(delta_ms, 1e-9) / 1e6, "peak": peak_hbm,
+                    roofline={"bound": "hbm", "kernel": "delta_chunk_mma_kernel (32 sequential launches)", "achieved": qkvy_bytes / max(delta_ms, 1e-9) / 1e6, "peak": peak_hbm,
                               "unit": "GB/s", "frac": qkvy_bytes / max(delta_ms, 1e-9) / 1e6 / peak_hbm, "traffic": None, "peak_source": peak_src,
-                              "note": "q/k/v/y traffic of the 32 chunks against HBM; the chunks are sequential per head and on-chip bound"},
+                              "note": "q/k/v/y traffic of the 32 chunks against HBM; the chunks are sequential per head (the state carries) and latency bound: "
+                                      "seven dependent small products per chunk, 10.5 MFLOP per head and chunk on mma.sync"},
                     kernels={"conv1d_ssm": {"ms": conv_ms, "GBps": conv_bytes / max(conv_ms, 1e-9) / 1e6, "frac_of_measured_hbm": conv_bytes / max(conv_ms, 1e-9) / 1e6 / peak_hbm},
                              "delta_chunk_x32": {"ms": delta_ms}, "w4a16_projections": {"ms": by.get(OP.MATMUL_W4A16, 0.0)}})
         eng.shutdown()
