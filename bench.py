@@ -942,21 +942,16 @@ def init_tp(lib, rank, world):
     if os.environ.get("GEHTP_TP_P2P", "1") != "0":
         # mailboxes for the one-kernel all-reduce over peer memory: gather the IPC handles in rank order
         hb = (ctypes.c_uint8 * 64)()
-        ok = lib.gehtp_cuda_tp_p2p_export(hb, 64) == 0
+        lib.gehtp_cuda_tp_p2p_export(hb, 64)
         mine = torch.tensor(list(hb), dtype=torch.uint8, device="cuda")
         allh = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allh, mine)
         raw = b"".join(bytes(h.cpu().tolist()) for h in allh)
         hbuf = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(raw)
-        ok = ok and lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) == 0
-        # every rank uses the peer-memory kernels or none does
-        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            if not ok:
-                print("[tp] rank %d: peer-memory mailboxes unavailable (%s); all ranks use NCCL all-reduces"
-                      % (rank, lib.gehtp_cuda_last_error().decode(errors="replace")), file=sys.stderr)
-            lib.gehtp_cuda_tp_p2p_disable()
+        # every rank calls import; it ends with the ranks' agreement: all use the peer-memory kernels or none does
+        if lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) != 0:
+            print("[tp] rank %d: peer-memory mailboxes unavailable (%s); all ranks use NCCL all-reduces"
+                  % (rank, lib.gehtp_cuda_last_error().decode(errors="replace")), file=sys.stderr)
         dist.barrier()
 
 

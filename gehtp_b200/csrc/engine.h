@@ -144,6 +144,7 @@ void drop_plan(bool keep_states);
 // tp.cu
 extern std::vector<uint8_t> g_allreduce_after;   // per op: 1 = all-reduce its first output over the ranks
 int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
+int tp_all_agree(int mine);
 // tp_p2p.cu
 bool tp_p2p_ready();
 bool tp_p2p_allreduce_f16(cudaStream_t st, void* buf, size_t elems);

@@ -806,8 +806,10 @@ int gehtp_cuda_state_save_hds1(const struct wt_blob* b, const char* path, char* 
     return 0;
 }
 
-// 0 = loaded, 1 = no such file (states untouched), -1 = bad file or a state table of another shape
-// (states untouched), as host_decode_state_load reports them.
+// 0 = loaded, 1 = no such file (states untouched), -1 = bad file or a state table of another shape, as
+// host_decode_state_load reports them. The file is read and checked as a whole before the first state is
+// written, so a bad file leaves the states untouched; a device copy that fails midway (reported through err)
+// leaves the states before it loaded.
 int gehtp_cuda_state_load_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn) {
     if (!path) { set_err(err, errn, "null argument"); return -1; }
     if (!ensure_device(err, errn)) return -1;

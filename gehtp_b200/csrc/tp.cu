@@ -66,4 +66,19 @@ int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems) {
     ncclResult_t r = ncclAllReduce(buf, buf, elems, ncclHalf, ncclSum, (ncclComm_t)g.nccl_comm, st);
     return r == ncclSuccess ? 0 : -1;
 }
+
+// Minimum of a flag over the ranks (NCCL, blocking): 1 only if every rank passed 1. -1: no communicator.
+int tp_all_agree(int mine) {
+    if (g.tp_world <= 1) return mine ? 1 : 0;
+    if (!g.nccl_comm) return -1;
+    int* d = nullptr;
+    if (cudaMalloc(&d, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    int v = mine ? 1 : 0;
+    cudaMemcpyAsync(d, &v, sizeof v, cudaMemcpyHostToDevice, g.stream);
+    const ncclResult_t r = ncclAllReduce(d, d, 1, ncclInt32, ncclMin, (ncclComm_t)g.nccl_comm, g.stream);
+    cudaMemcpyAsync(&v, d, sizeof v, cudaMemcpyDeviceToHost, g.stream);
+    const cudaError_t e = cudaStreamSynchronize(g.stream);
+    cudaFree(d);
+    return (r == ncclSuccess && e == cudaSuccess) ? v : -1;
+}
 }  // namespace gehtp

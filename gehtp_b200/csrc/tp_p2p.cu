@@ -305,13 +305,15 @@ int gehtp_cuda_tp_p2p_export(void* handle_out, size_t handle_bytes) {
 }
 
 int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int world) {
-    if (!handles || handle_stride < sizeof(cudaIpcMemHandle_t) || world != g.tp_world || world > kMaxWorld || !p2p.my_box) {
-        g.last_error = "tp p2p: bad import arguments (export first, world must match tp_init)";
+    if (!handles || handle_stride < sizeof(cudaIpcMemHandle_t) || world != g.tp_world || world > kMaxWorld) {
+        g.last_error = "tp p2p: bad import arguments (world must match tp_init)";
         return -1;
     }
     P2PCtx c{};
     c.rank = g.tp_rank; c.world = world; c.epoch = p2p.epoch; c.status = g.d_status; c.spin_limit = p2p.spin_limit;
-    for (int r = 0; r < world; r++) {
+    bool mine = p2p.my_box != nullptr;      // a rank whose export failed still takes part in the agreement below
+    if (!mine) g.last_error = "tp p2p: this rank has no mailbox (its export failed)";
+    for (int r = 0; r < world && mine; r++) {
         if (r == g.tp_rank) { c.box[r] = p2p.my_box; continue; }
         cudaIpcMemHandle_t h;
         std::memcpy(&h, (const unsigned char*)handles + (size_t)r * handle_stride, sizeof h);
@@ -319,10 +321,25 @@ int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int worl
         if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
             g.last_error = "tp p2p: cudaIpcOpenMemHandle failed (no peer access between the ranks' GPUs?)";
             cudaGetLastError();
-            return -1;
+            mine = false;
+            break;
         }
         p2p.peer_base[r] = p;
         c.box[r] = (unsigned char*)p;
+    }
+    // Every rank takes the peer-memory path or none does: a rank that fell back to NCCL while its peers post into
+    // mailboxes would leave them polling. The ranks agree here (minimum of the flags over the communicator of
+    // tp_init), so the caller needs no agreement of its own; which launches are eligible afterwards depends on row
+    // count and width only, which are the same on every rank.
+    const int all = tp_all_agree(mine ? 1 : 0);
+    if (all != 1) {
+        for (int r = 0; r < kMaxWorld; r++)
+            if (p2p.peer_base[r]) { cudaIpcCloseMemHandle(p2p.peer_base[r]); p2p.peer_base[r] = nullptr; }
+        p2p.ready = false;
+        if (mine) g.last_error = all < 0 ? "tp p2p: the ranks could not agree (no communicator: call gehtp_cuda_tp_init first)"
+                                         : "tp p2p: another rank could not map the mailboxes; all ranks use NCCL";
+        if (g.planned) drop_plan(true);
+        return -1;
     }
     p2p.ctx = c;
     p2p.ready = true;

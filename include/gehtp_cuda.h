@@ -135,12 +135,14 @@ int gehtp_cuda_tp_allreduce_after(const uint32_t* op_idx, uint32_t n);
  * and adds the slots in rank order). After gehtp_cuda_tp_init, every rank
  * calls _export (64-byte CUDA IPC handle of its mailbox), the caller gathers
  * the handles of all ranks in rank order (`handle_stride` bytes apart) and
- * every rank calls _import. Vectors above 1 MiB keep using NCCL. A peer that
- * never arrives makes the run return an error instead of hanging. */
+ * every rank calls _import — every rank, also one whose _export failed: _import ends with an
+ * agreement over the communicator of tp_init (minimum of the ranks' success flags), so that either
+ * all ranks use the mailboxes (0) or none does (-1 on every rank; all-reduces then go through NCCL).
+ * Vectors above 1 MiB keep using NCCL. A peer that never arrives makes the run return an error
+ * instead of hanging. */
 int gehtp_cuda_tp_p2p_export(void* handle_out, size_t handle_bytes);
 int gehtp_cuda_tp_p2p_import(const void* handles, size_t handle_stride, int world);
-/* Back to NCCL for every all-reduce (all ranks must agree: call it on every rank when the
- * export or import failed on any of them). */
+/* Back to NCCL for every all-reduce (call it on every rank or on none). */
 void gehtp_cuda_tp_p2p_disable(void);
 /* Number of polls a device-side wait of the peer-memory exchange makes before it gives up,
  * leaves a code in the engine's status word and lets the run return "all-reduce timed out"
@@ -213,7 +215,7 @@ int gehtp_cuda_state_read(uint32_t idx, void* dst, size_t bytes);
  * 42-state decode table: KV rings 0..5 with 512 values per face, conv windows 6..23, delta
  * states 24..41 (decode_state_gid, compiler/tools/wtop_ops/wtop_ops.hpp:478-492). KV faces
  * are fp16 on the device and fp32 in the file; positions 0..count-1 are exchanged.
- * save: 0 or -1. load: 0 loaded, 1 no such file, -1 bad file or table (states untouched),
+ * save: 0 or -1. load: 0 loaded, 1 no such file, -1 bad file or table (checked before anything is written),
  * the return values of host_decode_state_load. */
 int gehtp_cuda_state_save_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn);
 int gehtp_cuda_state_load_hds1(const struct wt_blob* b, const char* path, char* err, size_t errn);

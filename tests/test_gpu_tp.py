@@ -70,7 +70,16 @@ def _worker(rank, world, port, p2p, ret):
         allh = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allh, mine)
         hbuf = (ctypes.c_uint8 * (64 * world)).from_buffer_copy(b"".join(bytes(h.cpu().tolist()) for h in allh))
-        assert lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) == 0, lib.gehtp_cuda_last_error()
+        if p2p == 3:
+            # rank 1 is handed a handle that maps nothing: its import fails on the host (an error code of
+            # cudaIpcOpenMemHandle, no GPU involved), and the agreement inside import makes rank 0 give up as well:
+            # -1 on both ranks, and the run goes through NCCL
+            if rank == 1:
+                hbuf = (ctypes.c_uint8 * (64 * world))(*([0xA5] * (64 * world)))
+            assert lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) == -1
+            assert b"NCCL" in lib.gehtp_cuda_last_error() or b"cudaIpcOpenMemHandle" in lib.gehtp_cuda_last_error()
+        else:
+            assert lib.gehtp_cuda_tp_p2p_import(hbuf, 64, world) == 0, lib.gehtp_cuda_last_error()
         if p2p == 2:    # mailboxes mapped, then given up on every rank: the run must go through NCCL again
             lib.gehtp_cuda_tp_p2p_disable()
     cfg = _cfg()
@@ -98,7 +107,7 @@ def _worker(rank, world, port, p2p, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("p2p", [0, 1, 2])
+@pytest.mark.parametrize("p2p", [0, 1, 2, 3])
 def test_tp2_decode_matches_single_gpu(p2p):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
