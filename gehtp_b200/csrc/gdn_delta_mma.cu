@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(256)
 delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, const uint16_t* __restrict__ q,
                        const uint16_t* __restrict__ beta, const uint16_t* __restrict__ gl, uint16_t* __restrict__ y,
                        float* __restrict__ Sg, int c, int ntok, int q_raw) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr int DM = D / 4, DP = D + 8;
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t* Kh = (uint16_t*)smem;                 // [C][DP]   k
@@ -286,7 +288,7 @@ bool launch(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_
     constexpr int DM = D / 4, DP = D + 8;
     const size_t smem = (size_t)(2 * C * DP + D * CP + 2 * DM * DP + 6 * DM * CP + 3 * C * CP) * 2 + 4 * C * sizeof(float);
     if (!ensure_dyn_smem(delta_chunk_mma_kernel<D>, smem, have)) return false;
-    delta_chunk_mma_kernel<D><<<dim3(H, 4), 256, smem, st>>>(k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)q_raw);
+    launch_pdl(delta_chunk_mma_kernel<D>, dim3(dim3(H, 4)), dim3(256), smem, st, k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)q_raw);
     g_launches++;
     return true;
 }

@@ -42,13 +42,15 @@ __device__ __forceinline__ float unary_apply(float v, uint32_t subtype) {
 
 __global__ void unary_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, uint32_t n,
                              uint32_t subtype) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         y[i] = f2h(unary_apply(h2f(x[i]), subtype));
 }
 
 void k_unary(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t n, uint32_t subtype) {
     if (!n) return;
-    unary_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, y, n, subtype);
+    launch_pdl(unary_kernel, dim3(grid_for(n, 256)), dim3(256), 0, st, x, y, n, subtype);
     g_launches++;
 }
 
@@ -58,6 +60,8 @@ void k_unary(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t n, uint32
 __global__ void binary_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
                               uint16_t* __restrict__ y, uint32_t n, uint32_t subtype,
                               int guard_div) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         float x0 = h2f(a[i]), x1 = h2f(b[i]), r = x0;
         switch (subtype) {
@@ -76,7 +80,7 @@ __global__ void binary_kernel(const uint16_t* __restrict__ a, const uint16_t* __
 void k_binary(cudaStream_t st, const uint16_t* a, const uint16_t* b, uint16_t* y, uint32_t n,
               uint32_t subtype, bool guard_div) {
     if (!n) return;
-    binary_kernel<<<grid_for(n, 256), 256, 0, st>>>(a, b, y, n, subtype, guard_div ? 1 : 0);
+    launch_pdl(binary_kernel, dim3(grid_for(n, 256)), dim3(256), 0, st, a, b, y, n, subtype, guard_div ? 1 : 0);
     g_launches++;
 }
 
@@ -102,6 +106,8 @@ void k_select(cudaStream_t st, const uint16_t* c, uint32_t cn, const uint16_t* t
 
 // ---------------------------------------------------------------- byte moves
 __global__ void copy16_kernel(const uint4* __restrict__ s, uint4* __restrict__ d, size_t n16) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
          i += (size_t)gridDim.x * blockDim.x)
         d[i] = s[i];
@@ -115,7 +121,7 @@ __global__ void copy1_kernel(const uint8_t* __restrict__ s, uint8_t* __restrict_
 void k_copy_bytes(cudaStream_t st, const void* src, void* dst, size_t bytes) {
     if (!bytes || src == dst) return;
     if ((((uintptr_t)src | (uintptr_t)dst | bytes) & 15u) == 0)
-        copy16_kernel<<<grid_for(bytes / 16, 256), 256, 0, st>>>((const uint4*)src, (uint4*)dst,
+        launch_pdl(copy16_kernel, dim3(grid_for(bytes / 16, 256)), dim3(256), 0, st, (const uint4*)src, (uint4*)dst,
                                                                 bytes / 16);
     else
         copy1_kernel<<<grid_for(bytes, 256), 256, 0, st>>>((const uint8_t*)src, (uint8_t*)dst,
@@ -139,6 +145,8 @@ void k_fill16(cudaStream_t st, uint16_t* dst, size_t n, uint16_t v) {
 __global__ void rows_move_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                                  uint32_t outer, uint32_t seg, uint32_t xs, uint32_t xo,
                                  uint32_t ys, uint32_t yo) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     size_t total = (size_t)outer * seg;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -149,7 +157,7 @@ __global__ void rows_move_kernel(const uint16_t* __restrict__ x, uint16_t* __res
 void k_concat_seg(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t outer, uint32_t seg,
                   uint32_t total_axis, uint32_t start) {
     if (!outer || !seg) return;
-    rows_move_kernel<<<grid_for((size_t)outer * seg, 256), 256, 0, st>>>(x, y, outer, seg, seg, 0,
+    launch_pdl(rows_move_kernel, dim3(grid_for((size_t)outer * seg, 256)), dim3(256), 0, st, x, y, outer, seg, seg, 0,
                                                                        total_axis, start);
     g_launches++;
 }
@@ -157,7 +165,7 @@ void k_concat_seg(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t oute
 void k_split_seg(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t outer, uint32_t seg,
                  uint32_t total_axis, uint32_t off) {
     if (!outer || !seg) return;
-    rows_move_kernel<<<grid_for((size_t)outer * seg, 256), 256, 0, st>>>(x, y, outer, seg,
+    launch_pdl(rows_move_kernel, dim3(grid_for((size_t)outer * seg, 256)), dim3(256), 0, st, x, y, outer, seg,
                                                                        total_axis, off, seg, 0);
     g_launches++;
 }
@@ -168,6 +176,8 @@ struct U5 { uint32_t v[5]; };
 // Strided slice, rank <= 3 (oplist_exec.c:1950-1988).
 __global__ void slice_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                              uint32_t n_out, uint32_t rk, U4 b, U4 s, U4 istr, U4 ostr) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_out;
          i += gridDim.x * blockDim.x) {
         uint32_t rem = i, in_lin = 0;
@@ -184,13 +194,15 @@ void k_slice(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t n_out, ui
     if (!n_out) return;
     U4 b{}, s{}, is{}, os{};
     for (uint32_t i = 0; i < 3; i++) { b.v[i] = b3[i]; s.v[i] = s3[i]; is.v[i] = istr3[i]; os.v[i] = ostr3[i]; }
-    slice_kernel<<<grid_for(n_out, 256), 256, 0, st>>>(x, y, n_out, rk, b, s, is, os);
+    launch_pdl(slice_kernel, dim3(grid_for(n_out, 256)), dim3(256), 0, st, x, y, n_out, rk, b, s, is, os);
     g_launches++;
 }
 
 // numpy-style broadcast, right aligned (oplist_exec.c:1876-1907).
 __global__ void broadcast_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                                  uint32_t n, uint32_t r, uint32_t lead, U4 in_d, U4 istr, U4 ostr) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint32_t rem = i, in_lin = 0;
         for (uint32_t d = 0; d < r; d++) {
@@ -208,13 +220,15 @@ void k_broadcast(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t n, ui
     if (!n) return;
     U4 d{}, is{}, os{};
     for (uint32_t i = 0; i < 4; i++) { d.v[i] = in_d4[i]; is.v[i] = istr4[i]; os.v[i] = ostr4[i]; }
-    broadcast_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, y, n, r, lead, d, is, os);
+    launch_pdl(broadcast_kernel, dim3(grid_for(n, 256)), dim3(256), 0, st, x, y, n, r, lead, d, is, os);
     g_launches++;
 }
 
 // General N-D transpose, rank 2..4 (oplist_exec.c:1910-1948).
 __global__ void transpose_gen_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                                      uint32_t n, uint32_t rk, U4 si, U4 so, U4 p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
         uint32_t rem = t, ic[4] = {0, 0, 0, 0};
         for (uint32_t i = 0; i < rk; i++) { ic[i] = rem / si.v[i]; rem %= si.v[i]; }
@@ -228,7 +242,7 @@ void k_transpose_gen(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t n
     if (!n) return;
     U4 si{}, so{}, p{};
     for (uint32_t i = 0; i < 4; i++) { si.v[i] = si4[i]; so.v[i] = so4[i]; p.v[i] = perm4[i]; }
-    transpose_gen_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, y, n, rk, si, so, p);
+    launch_pdl(transpose_gen_kernel, dim3(grid_for(n, 256)), dim3(256), 0, st, x, y, n, rk, si, so, p);
     g_launches++;
 }
 
@@ -379,6 +393,8 @@ void k_cumsum(cudaStream_t st, const uint16_t* x, uint16_t* y, uint32_t rows, ui
 __global__ void gather_kernel(const uint16_t* __restrict__ tbl, const int32_t* __restrict__ idx,
                               uint16_t* __restrict__ y, uint32_t n, uint32_t axis, uint32_t xrank,
                               uint32_t irank, U5 td, U5 xd, U5 os, U5 ts, U5 xs) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint32_t rem = i, oc[5];
         for (int d = 0; d < 5; d++) { oc[d] = rem / os.v[d]; rem %= os.v[d]; }
@@ -416,7 +432,7 @@ void k_gather(cudaStream_t st, const uint16_t* tbl, const int32_t* idx, uint16_t
         xs.v[d] = xs.v[d + 1] * xd.v[d + 1];
     }
     for (int d = 0; d < 5; d++) { if (!os.v[d]) os.v[d] = 1; if (!xd.v[d]) xd.v[d] = 1; }
-    gather_kernel<<<grid_for(n, 256), 256, 0, st>>>(tbl, idx, y, n, axis, xrank, irank, td, xd, os,
+    launch_pdl(gather_kernel, dim3(grid_for(n, 256)), dim3(256), 0, st, tbl, idx, y, n, axis, xrank, irank, td, xd, os,
                                                    ts, xs);
     g_launches++;
 }

@@ -39,6 +39,8 @@ template <int K>
 __global__ void __launch_bounds__(256)
 conv1d_ssm_vec_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, uint4* __restrict__ y, uint32_t seq,
                       uint32_t C8) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int32_t in_rows = (seq >= (uint32_t)K) ? (int32_t)(seq - K + 1) : 0;
     const uint32_t c8 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c8 >= C8) return;
@@ -95,9 +97,9 @@ void k_conv1d_ssm(cudaStream_t st, const uint16_t* x, const uint16_t* w, uint16_
         const uint32_t C8 = C / 8;
         const uint32_t bx = C8 >= 128 ? 128 : 64;
         const dim3 grid((C8 + bx - 1) / bx, (seq + CONV_TT - 1) / CONV_TT);
-        if (k == 4) conv1d_ssm_vec_kernel<4><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
-        else if (k == 3) conv1d_ssm_vec_kernel<3><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
-        else conv1d_ssm_vec_kernel<2><<<grid, bx, 0, st>>>((const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        if (k == 4) launch_pdl(conv1d_ssm_vec_kernel<4>, dim3(grid), dim3(bx), 0, st, (const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        else if (k == 3) launch_pdl(conv1d_ssm_vec_kernel<3>, dim3(grid), dim3(bx), 0, st, (const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
+        else launch_pdl(conv1d_ssm_vec_kernel<2>, dim3(grid), dim3(bx), 0, st, (const uint4*)x, (const uint4*)w, (uint4*)y, seq, C8);
         g_launches++;
         return;
     }
