@@ -76,14 +76,16 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     uint16_t* uTlo = uThi + DM * CP;
     uint16_t* wuhi = uTlo + DM * CP;                // [DM][CP]  decay-weighted u transposed
     uint16_t* wulo = wuhi + DM * CP;
-    uint16_t* Lh = wulo + DM * CP;                  // [C][CP]   L, later the decayed q.k matrix (hi)
+    uint16_t* Lh = wulo + DM * CP;                  // [C][CP]   L
     uint16_t* Th = Lh + C * CP;                     // [C][CP]   T
     uint16_t* QKlo = Th + C * CP;                   // [C][CP]   the decayed q.k matrix (lo)
-    float* G = (float*)(QKlo + C * CP);             // [C] running sum of the log decays
+    uint16_t* QKhi = QKlo + C * CP;                 // [C][CP]   the decayed q.k matrix (hi)
+    uint16_t* Tt = QKhi + C * CP;                   // [C][CP]   T transposed (operand of the block forward substitution)
+    uint16_t* xs = Tt + C * CP;                     // [3][2][16][24] per-warp scratch of that substitution
+    float* G = (float*)(xs + 3 * 768);              // [C] running sum of the log decays
     float* bj = G + C;                              // [C] beta
     float* eG = bj + C;                             // [C] exp(G)
     float* wd = eG + C;                             // [C] exp(G_last - G_i)
-    uint16_t* QKhi = Lh;
 
     const int h = blockIdx.x, m0 = blockIdx.y * DM, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -132,7 +134,7 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     }
     __syncthreads();
 
-    // ---- stage 1: L[j][i] = f16(exp(G_j - G_i) (k_j . k_i) beta_j) for i < j, else 0
+    // ---- stage 1 (with 3 and 5 below): L[j][i] = f16(exp(G_j - G_i) (k_j . k_i) beta_j) for i < j, else 0
     for (int tile = warp; tile < (C / 16) * (C / 8); tile += 8) {
         const int mi = tile / (C / 8), ni = tile % (C / 8);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -143,6 +145,31 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
             Lh[j * CP + i] = i < j ? f2h(expf(G[j] - G[i]) * acc[e] * bj[j]) : (uint16_t)0;
         }
     }
+    // stages 3 and 5 need the operands only, not L or T: same phase, one barrier for the three
+    // ---- stage 3: b[j][m] = beta_j (v[j][m] - e^{G_j} (S0 k_j)[m]), stored transposed as hi + lo
+    for (int tile = warp; tile < (C / 16) * (DM / 8); tile += 8) {
+        const int mi = tile / (DM / 8), ni = tile % (DM / 8);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_rows(acc, Kh + mi * 16 * DP, DP, Shi + ni * 8 * DP, DP, D, g, t);
+        mma_rows(acc, Kh + mi * 16 * DP, DP, Slo + ni * 8 * DP, DP, D, g, t);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int j = mi * 16 + g + (e >> 1) * 8, m = ni * 8 + 2 * t + (e & 1);
+            const float vv = j < c ? h2f(vh[(size_t)j * D + m0 + m]) : 0.0f;
+            split_store(bThi + m * CP + j, bTlo + m * CP + j, bj[j] * (vv - eG[j] * acc[e]));
+        }
+    }
+    // ---- stage 5: QK[t][i] = exp(G_t - G_i) (q_t . k_i) for i <= t, as hi + lo
+    for (int tile = warp; tile < (C / 16) * (C / 8); tile += 8) {
+        const int mi = tile / (C / 8), ni = tile % (C / 8);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (ni * 8 < mi * 16 + 16) mma_rows(acc, Qh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int tt = mi * 16 + g + (e >> 1) * 8, i = ni * 8 + 2 * t + (e & 1);
+            split_store(QKhi + tt * CP + i, QKlo + tt * CP + i, i <= tt ? acc[e] * scale * expf(G[tt] - G[i]) : 0.0f);
+        }
+    }
     __syncthreads();
 
     // ---- stage 2: T = (I + L)^-1 in fp16. Within a 16 x 16 diagonal block it is the forward substitution of the
@@ -151,7 +178,6 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     // block-wide barrier). The blocks below the diagonal follow from (I + L) T = I block row by block row:
     //     T_ik = -T_ii (sum_{k <= m < i} L_im T_mk)
     // two small products per block on the tensor cores (the inner sum as hi + lo), rounded to fp16 once.
-    uint16_t* Tt = uThi;                            // [C][CP] T transposed (u, u lo and weighted u are not live yet)
     {
         const int j = tid >> 2, part = tid & 3, r0 = (j >> 4) << 4;
         for (int rr = 0; rr < 16; rr++) {
@@ -177,7 +203,7 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     for (int bi = 1; bi < C / 16; bi++) {
         if (warp < bi) {
             const int bk = warp;
-            uint16_t* xhi = QKlo + warp * 768;      // X transposed [16][24], hi and lo (the q.k matrix is not live yet)
+            uint16_t* xhi = xs + warp * 768;        // X transposed [16][24], hi and lo
             uint16_t* xlo = xhi + 384;
             for (int nt = 0; nt < 2; nt++) {
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -205,21 +231,6 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
         __syncthreads();
     }
 
-    // ---- stage 3: b[j][m] = beta_j (v[j][m] - e^{G_j} (S0 k_j)[m]), stored transposed as hi + lo
-    for (int tile = warp; tile < (C / 16) * (DM / 8); tile += 8) {
-        const int mi = tile / (DM / 8), ni = tile % (DM / 8);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_rows(acc, Kh + mi * 16 * DP, DP, Shi + ni * 8 * DP, DP, D, g, t);
-        mma_rows(acc, Kh + mi * 16 * DP, DP, Slo + ni * 8 * DP, DP, D, g, t);
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int j = mi * 16 + g + (e >> 1) * 8, m = ni * 8 + 2 * t + (e & 1);
-            const float vv = j < c ? h2f(vh[(size_t)j * D + m0 + m]) : 0.0f;
-            split_store(bThi + m * CP + j, bTlo + m * CP + j, bj[j] * (vv - eG[j] * acc[e]));
-        }
-    }
-    __syncthreads();
-
     // ---- stage 4: u = T b ; also u_i weighted with the decay to the end of the chunk (for the state update)
     for (int tile = warp; tile < (C / 16) * (DM / 8); tile += 8) {
         const int mi = tile / (DM / 8), ni = tile % (DM / 8);
@@ -231,19 +242,6 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
             const int j = mi * 16 + g + (e >> 1) * 8, m = ni * 8 + 2 * t + (e & 1);
             split_store(uThi + m * CP + j, uTlo + m * CP + j, acc[e]);
             split_store(wuhi + m * CP + j, wulo + m * CP + j, j < c ? wd[j] * acc[e] : 0.0f);
-        }
-    }
-    __syncthreads();
-
-    // ---- stage 5: QK[t][i] = exp(G_t - G_i) (q_t . k_i) for i <= t, as hi + lo
-    for (int tile = warp; tile < (C / 16) * (C / 8); tile += 8) {
-        const int mi = tile / (C / 8), ni = tile % (C / 8);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (ni * 8 < mi * 16 + 16) mma_rows(acc, Qh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int tt = mi * 16 + g + (e >> 1) * 8, i = ni * 8 + 2 * t + (e & 1);
-            split_store(QKhi + tt * CP + i, QKlo + tt * CP + i, i <= tt ? acc[e] * scale * expf(G[tt] - G[i]) : 0.0f);
         }
     }
     __syncthreads();
@@ -286,7 +284,7 @@ bool launch(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_
             uint16_t* y, float* S, uint32_t c, uint32_t ntok, uint32_t H, uint32_t q_raw) {
     static int have[64];
     constexpr int DM = D / 4, DP = D + 8;
-    const size_t smem = (size_t)(2 * C * DP + D * CP + 2 * DM * DP + 6 * DM * CP + 3 * C * CP) * 2 + 4 * C * sizeof(float);
+    const size_t smem = (size_t)(2 * C * DP + D * CP + 2 * DM * DP + 6 * DM * CP + 5 * C * CP + 3 * 768) * 2 + 4 * C * sizeof(float);
     if (!ensure_dyn_smem(delta_chunk_mma_kernel<D>, smem, have)) return false;
     launch_pdl(delta_chunk_mma_kernel<D>, dim3(dim3(H, 4)), dim3(256), smem, st, k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)q_raw);
     g_launches++;
