@@ -143,6 +143,14 @@ int build_plan(const wt_blob* b, char* err, size_t errn);
 void drop_plan(bool keep_states);
 // tp.cu
 extern std::vector<uint8_t> g_allreduce_after;   // per op: 1 = all-reduce its first output over the ranks
+// Fewest rows for which a W4A16 matmul goes to the tcgen05 GEMM (TMA zero-fills the rows a 128-row tile has
+// beyond M; with few tiles K is split over the SMs); below it the streaming kernel runs, which re-reads and
+// re-dequantises the weights once per 16 or 32 rows. Measured at 64 rows, Qwen3-4B shapes: the batch-64 decode step
+// 18.8 -> 18.0 ms with the GEMM. $GEHTP_CUDA_GEMM_MIN_M moves the switch (>= 17).
+inline uint32_t w4_gemm_min_rows() {
+    static const uint32_t v = [] { const char* e = std::getenv("GEHTP_CUDA_GEMM_MIN_M"); int x = e ? std::atoi(e) : 64; return (uint32_t)(x >= 17 ? x : 64); }();
+    return v;
+}
 int tp_allreduce_f16(cudaStream_t st, void* buf, size_t elems);
 int tp_all_agree(int mine);
 // tp_p2p.cu

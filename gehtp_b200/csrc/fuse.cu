@@ -344,7 +344,7 @@ bool match_swiglu(const Graph& G, uint32_t ip, Span& sp) {
     const wt_op &gt = b->ops[gate], &u = b->ops[up];
     if (gt.args[0] != u.args[0] || gt.args[3] != u.args[3] || gt.args[4] != u.args[4] || gt.args[5] != u.args[5]) return false;
     uint32_t M = gt.args[3], n = M * gt.args[5];
-    if (M > 64 || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
+    if (M > 64 || M >= w4_gemm_min_rows() || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
     std::vector<uint32_t> ops = {(uint32_t)gate, (uint32_t)sig, (uint32_t)act, (uint32_t)up, ip};
     uint32_t first;
     if (!contiguous(ops, first) || !closed(G, ops, {ip})) return false;
@@ -401,7 +401,7 @@ bool match_swiglu_tail(const Graph& G, uint32_t ip, Span& sp) {
     if (gt.args[3] != u.args[3] || gt.args[5] != u.args[5]) return false;
     const uint64_t n64 = (uint64_t)gt.args[3] * gt.args[5];
     const uint32_t n = (uint32_t)n64;
-    if (n64 > 0xFFFFFFFFull || gt.args[3] <= 64 || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
+    if (n64 > 0xFFFFFFFFull || (gt.args[3] <= 64 && gt.args[3] < w4_gemm_min_rows()) || pr.args[3] != n || b->ops[act].args[3] != n || b->ops[sig].args[2] != n) return false;
     if (!is_temp_ref(gt.args[2]) || !is_temp_ref(u.args[2]) || !is_temp_ref(pr.args[2])) return false;
     std::vector<uint32_t> ops = {(uint32_t)gate, (uint32_t)sig, (uint32_t)act, (uint32_t)up, ip};
     uint32_t first;

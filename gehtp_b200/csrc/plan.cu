@@ -194,7 +194,7 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
             p.launch = [=](cudaStream_t st) {
                 W4Epilogue ep;
                 ep.status = g.d_status;
-                if (M >= 128 && k_w4a16_gemm_sm100(st, act, pk, sc, y, M, K, N, ep)) return;
+                if (M >= w4_gemm_min_rows() && k_w4a16_gemm_sm100(st, act, pk, sc, y, M, K, N, ep)) return;
                 k_w4a16_skinny(st, act, pk, sc, y, M, K, N, ep);
             };
         }

@@ -20,8 +20,13 @@
 //                the magic-number trick, multiplies by the group scale and stores
 //                16-byte chunks into the stage's B tile in the 128B-swizzled
 //                K-major form tcgen05.mma reads.
+// Few-tile shapes (prefill projections with N = 1024, decode at 64 rows): K is cut into S runs, one work item per
+// (tile, run); a run writes its fp32 partial sums and w4a16_splitk_reduce_kernel adds the runs in order (same bits
+// on every call) and applies the epilogue. 512 x 3072 x 1024: 22.9 -> 12.7 us.
 // All mbarrier waits are bounded; on a timeout the CTA raises a flag, every role
 // stops, in-flight copies are waited for (bounded), and the TMEM is freed.
+#include <cstdlib>
+#include <initializer_list>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -109,7 +114,7 @@ template <int MH, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4* __restrict__ wp,
                         const uint16_t* __restrict__ sc, uint16_t* __restrict__ y, uint32_t M, uint32_t K,
-                        uint32_t N, W4Epilogue ep) {
+                        uint32_t N, W4Epilogue ep, uint32_t S, float* __restrict__ part) {
     using C = Cfg<MH, BN>;
     constexpr int STAGES = C::STAGES, RSTAGES = C::RSTAGES, NBUF = C::NBUF;
     constexpr int A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES, RAW_BYTES = C::RAW_BYTES, RAW_SLOT = C::RAW_SLOT;
@@ -130,6 +135,10 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (M + 128 * MH - 1) / (128 * MH), n_tiles = N / BN;
     const uint32_t tiles = m_tiles * n_tiles;
+    // Split K: S > 1 cuts the k blocks of every tile into S runs, one work item each (item = run * tiles + tile);
+    // a run leaves its fp32 partial sums in `part` ([run][row][N]) and a small kernel behind this one adds the
+    // runs in order and writes y. Few-tile shapes so fill the SMs instead of walking a long K in a few CTAs.
+    const uint32_t items = tiles * S, KGS = KG / S;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -155,9 +164,10 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         if (lane == 0) {
             asm volatile("griddepcontrol.wait;" ::: "memory");   // A is the predecessor's output
             uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const uint32_t tile = item % tiles, kb0 = (item / tiles) * KGS;
                 const uint32_t m0 = (tile % m_tiles) * (128 * MH);
-                for (uint32_t kb = 0; kb < KG; kb++, it++) {
+                for (uint32_t kb = kb0; kb < kb0 + KGS; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->empty[s], ph ^ 1)) { *abort_flag = 1; break; }
                     mbar_expect_tx(&bars->full[s], A_BYTES);
@@ -174,12 +184,12 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
-            for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, t++) {
+            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, t++) {
                 const uint32_t buf = t % NBUF;
                 if (!mbar_wait(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1)) { *abort_flag = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + buf * ACC_COLS;
-                for (uint32_t kb = 0; kb < KG; kb++, it++) {
+                for (uint32_t kb = 0; kb < KGS; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->full[s], ph)) { *abort_flag = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -203,11 +213,12 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         // ---- int4 tiles and scales by bulk copy
         if (lane == 0) {
             uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const uint32_t tile = item % tiles, kb0 = (item / tiles) * KGS;
                 const uint32_t n0 = (tile / m_tiles) * BN;
                 const uint4* wsrc = wp + (size_t)(n0 / 16) * 32;
                 const uint16_t* ssrc = sc + n0;
-                for (uint32_t kb = 0; kb < KG; kb++, it++) {
+                for (uint32_t kb = kb0; kb < kb0 + KGS; kb++, it++) {
                     const uint32_t r = it % RSTAGES, ph = (it / RSTAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->raw_empty[r], ph ^ 1)) { *abort_flag = 1; break; }
                     unsigned char* dst = sRaw + r * RAW_SLOT;
@@ -225,8 +236,32 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         uint32_t t = 0;
         // y (and the residual) may be memory the predecessor still reads or writes
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, t++) {
+        // 32 accumulator values of row m from column n on their way to y
+        auto emit = [&](uint32_t m, uint32_t n, const uint32_t (&v)[32]) {
+            const size_t o = (size_t)m * N + n;       // 64-byte aligned: N and n are multiples of 32
+            uint4* dst = (uint4*)(y + o);
+            if (ep.mode == 1) {
+                const uint4* res = (const uint4*)(ep.res + o);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint4 r = res[q];
+                    dst[q] = make_uint4(pack_out_res(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]), r.x),
+                                        pack_out_res(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]), r.y),
+                                        pack_out_res(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]), r.z),
+                                        pack_out_res(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]), r.w));
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    dst[q] = make_uint4(pack_out(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                                        pack_out(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                                        pack_out(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                                        pack_out(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+            }
+        };
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, t++) {
             const uint32_t buf = t % NBUF;
+            const uint32_t tile = item % tiles, run = item / tiles;
             const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
             bool ok = !__any_sync(0xffffffffu, *abort_flag != 0);
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[buf], (t / NBUF) & 1));
@@ -248,27 +283,13 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                         : "r"(taddr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (m < M) {
-                        const size_t o = (size_t)m * N + n0 + c * 32;       // 64-byte aligned: N and n0 are multiples of 128
-                        uint4* dst = (uint4*)(y + o);
-                        if (ep.mode == 1) {
-                            const uint4* res = (const uint4*)(ep.res + o);
+                    if (S == 1) {
+                        if (m < M) emit(m, n0 + c * 32, v);
+                    } else if (m < M) {
+                        // this run's partial sums: [run][row][N] fp32
+                        uint4* dst = (uint4*)(part + ((size_t)run * M + m) * N + n0 + c * 32);
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                const uint4 r = res[q];
-                                dst[q] = make_uint4(pack_out_res(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]), r.x),
-                                                    pack_out_res(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]), r.y),
-                                                    pack_out_res(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]), r.z),
-                                                    pack_out_res(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]), r.w));
-                            }
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 4; q++)
-                                dst[q] = make_uint4(pack_out(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
-                                                    pack_out(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
-                                                    pack_out(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
-                                                    pack_out(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
-                        }
+                        for (int q = 0; q < 8; q++) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     }
                 }
             }
@@ -284,8 +305,8 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         constexpr int UPW = BN / 64;       // strip units per warp and k block: 2 or 4
         constexpr int GROUPS = C::GROUPS;
         const uint32_t dw = warp - 8, q = dw >> 2, j = dw & 3, g = lane >> 2, t = lane & 3;
-        const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const uint32_t total = my_tiles * KG;
+        const uint32_t my_items = blockIdx.x < items ? (items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = my_items * KGS;
         const uint32_t sB_u32 = smem_u32(sB), sRaw_u32 = smem_u32(sRaw);
         // byte offsets of this lane's four 16-byte chunks inside unit 0 of a B stage; a unit is 16 rows = 2048 bytes:
         // row r, 16-byte chunk c (8 k) lives at r*128 + ((c ^ (r & 7)) << 4), and r & 7 does not depend on the unit
@@ -355,6 +376,48 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     }
 }
 
+// y[m][n] = sum over the runs of part[run][m][n], in run order, with the epilogue of the GEMM
+__global__ void __launch_bounds__(256)
+w4a16_splitk_reduce_kernel(const float* __restrict__ part, uint16_t* __restrict__ y, uint32_t M, uint32_t N, uint32_t S, W4Epilogue ep) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t quads = (size_t)M * N / 4, plane = (size_t)M * N / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < S; r++) {
+            const float4 p = __ldcg((const float4*)part + r * plane + i);
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        uint2 o;
+        if (ep.mode == 1) {
+            const uint2 res = *((const uint2*)ep.res + i);
+            o = make_uint2(pack_out_res(acc.x, acc.y, res.x), pack_out_res(acc.z, acc.w, res.y));
+        } else {
+            o = make_uint2(pack_out(acc.x, acc.y), pack_out(acc.z, acc.w));
+        }
+        *((uint2*)y + i) = o;
+    }
+}
+
+// Scratch of the split-K form (fp32 partial sums), per device, made on first use and grown when needed.
+struct SplitScratch { float* part = nullptr; size_t bytes = 0; };
+
+SplitScratch* split_scratch(cudaStream_t st, size_t need) {
+    static SplitScratch per_dev[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SplitScratch& sc = per_dev[dev];
+    if (sc.bytes >= need) return &sc;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }   // no allocation inside a capture
+    cudaDeviceSynchronize();          // a launch in flight may still use the old buffer
+    if (sc.part) cudaFree(sc.part);
+    sc.part = nullptr; sc.bytes = 0;
+    if (cudaMalloc(&sc.part, need) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    sc.bytes = need;
+    return &sc;
+}
+
 template <int MH, int BN>
 bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, const uint16_t* sc, uint16_t* y,
             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms) {
@@ -362,13 +425,43 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + (size_t)C::RSTAGES * C::RAW_SLOT + sizeof(Barriers) + 16;
     static int have[64] = {};
     if (!ensure_dyn_smem(w4a16_gemm_sm100_kernel<MH, BN>, smem, have)) return false;
-    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN);
-    const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc, y, M, K, N, ep) != cudaSuccess) {
+    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN), KG = K / BK;
+    // Split K when the tiles alone leave SMs idle. A CTA walks a k block in about 0.42 us whatever the shape, so
+    // the launch lasts (items per CTA) x (k blocks per item + set-up); S is the divisor of K/64 that makes that
+    // smallest, a run keeping at least one trip round the operand ring, the partial sums at most 64 MB.
+    static const int split_on = [] { const char* e = std::getenv("GEHTP_CUDA_SPLITK"); return e ? std::atoi(e) : 1; }();
+    uint32_t S = 1;
+    if (split_on && tiles < (uint32_t)sms) {
+        float best = (float)(KG + 4);
+        for (uint32_t c = 2; c <= 32 && c <= KG; c++) {
+            if (KG % c || KG / c < (uint32_t)C::STAGES || (size_t)c * M * N * sizeof(float) > ((size_t)64 << 20)) continue;
+            const uint32_t rounds = (tiles * c + sms - 1) / sms;
+            const float cost = (float)rounds * (float)(KG / c + 4) + 0.75f * (float)c + 6.0f;   // + the reduction: one launch, c reads
+            if (cost < best) { best = cost; S = c; }
+        }
+    }
+    float* part = nullptr;
+    if (S > 1) {
+        SplitScratch* ss = split_scratch(st, (size_t)S * M * N * sizeof(float));
+        if (ss) part = ss->part; else S = 1;
+    }
+    const uint32_t items = tiles * S;
+    const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
+    if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc, y, M, K, N, ep, S, part) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
     g_launches++;
+    if (S > 1) {
+        const size_t quads = (size_t)M * N / 4;
+        uint32_t rg = (uint32_t)((quads + 255) / 256);
+        if (rg > (uint32_t)sms * 8) rg = (uint32_t)sms * 8;
+        if (launch_pdl(w4a16_splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float*)part, y, M, N, S, ep) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        g_launches++;
+    }
     return true;
 }
 
