@@ -288,6 +288,38 @@ def test_prefill_runlist_matches_reference(cuda, ref, seq):
     assert_fp16_close(outs[0], unfused, "fused vs op-by-op prefill")
 
 
+def test_kernel_family_switches_agree(cuda, tmp_path):
+    """The environment switches that put an older kernel form back in (read once per process, hence child processes):
+    prefill attention on mma.sync instead of tcgen05 ($GEHTP_CUDA_PREFILL_SM100=0) and the W4A16 GEMM without split K
+    ($GEHTP_CUDA_SPLITK=0). Each gives the logits of the default build within the fp16 gate, and not the same bits
+    (so the switch did change the kernel)."""
+    import os
+    import subprocess
+    import sys
+    script = (
+        "import sys, numpy as np\n"
+        "sys.path.insert(0, %r)\n"
+        "import gehtp_b200\n"
+        "from gehtp_b200.runlists import DecoderConfig, build_prefill_runlist\n"
+        "from gehtp_b200.wtop import Engine\n"
+        "cfg = DecoderConfig(1024, 1, 8, 4, 128, 2048, 512, 1e6, 'switch')   # K = 2048 of the down projection: 32 k blocks on 16 tiles, split\n"
+        "buf, man = build_prefill_runlist(cfg, 200, seed=21, quant='w4')\n"
+        "ids = (np.arange(200, dtype=np.int32) * 37 + 11) %% cfg.vocab\n"
+        "eng = Engine(gehtp_b200.lib(), buf)\n"
+        "eng.run_io(ids, man['logits_temp'], None)\n"
+        "np.save(sys.argv[1], eng.temp(man['logits_temp']).copy())\n"
+        "eng.shutdown()\n") % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = {}
+    for name, env in (("default", {}), ("mma_attention", {"GEHTP_CUDA_PREFILL_SM100": "0"}), ("no_split_k", {"GEHTP_CUDA_SPLITK": "0"})):
+        out = tmp_path / (name + ".npy")
+        r = subprocess.run([sys.executable, "-c", script, str(out)], env=dict(os.environ, **env), capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs[name] = np.load(out)
+    for name in ("mma_attention", "no_split_k"):
+        assert_fp16_close(outs[name], outs["default"], name)
+        assert not np.array_equal(outs[name].view(np.uint16), outs["default"].view(np.uint16)), name + ": the switch changed nothing"
+
+
 @pytest.mark.parametrize("tokens", [70, 133])
 def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens):
     """The head of a prefill block (3 SPLITs + 2 rotary chains, 17 ops, one kernel) and a SwiGLU over
