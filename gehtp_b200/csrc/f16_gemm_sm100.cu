@@ -55,7 +55,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) { return (uint32_t)f
 template <int MH, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                      uint16_t* __restrict__ y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy, unsigned int* status) {
+                      uint16_t* __restrict__ y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy, unsigned int* status,
+                      uint32_t S, float* __restrict__ part) {
     using C = FCfg<MH, BN>;
     constexpr int STAGES = C::STAGES, NBUF = C::NBUF, A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES;
     constexpr uint32_t ACC_COLS = C::ACC_COLS, TMEM_COLS = C::TMEM_COLS;
@@ -69,6 +70,9 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t KG = K / BK;
     const uint32_t m_tiles = (M + 128 * MH - 1) / (128 * MH), tiles = m_tiles * (N / BN);
+    // Split K (S > 1): a work item is (tile, run of K/64/S k blocks), item = run * tiles + tile; a run leaves its fp32
+    // partial sums in part[run][row][N] and f16_splitk_reduce_kernel adds the runs in order.
+    const uint32_t items = tiles * S, KGS = KG / S;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -89,9 +93,10 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (lane == 0) {
             asm volatile("griddepcontrol.wait;" ::: "memory");   // A (and a weight that is a temp) come from the predecessor
             uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const uint32_t tile = item % tiles, kb0 = (item / tiles) * KGS;
                 const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
-                for (uint32_t kb = 0; kb < KG; kb++, it++) {
+                for (uint32_t kb = kb0; kb < kb0 + KGS; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->empty[s], ph ^ 1)) { *abort_flag = 1; break; }
                     mbar_expect_tx(&bars->full[s], A_BYTES + B_BYTES);
@@ -108,12 +113,12 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (lane == 0) {
             uint32_t it = 0, t = 0;
             const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
-            for (uint32_t tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, t++) {
+            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, t++) {
                 const uint32_t buf = t % NBUF;
                 if (!mbar_wait(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1)) { *abort_flag = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + buf * ACC_COLS;
-                for (uint32_t kb = 0; kb < KG; kb++, it++) {
+                for (uint32_t kb = 0; kb < KGS; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->full[s], ph)) { *abort_flag = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -136,8 +141,9 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const uint32_t lane_base = (warp & 3) * 32;
         uint32_t t = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");   // y may be memory the predecessor still reads
-        for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, t++) {
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, t++) {
             const uint32_t buf = t % NBUF;
+            const uint32_t tile = item % tiles, run = item / tiles;
             const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
             bool ok = !__any_sync(0xffffffffu, *abort_flag != 0);
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[buf], (t / NBUF) & 1));
@@ -159,7 +165,11 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                         : "r"(taddr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (m < M) {
+                    if (m < M && S > 1) {
+                        uint4* dst = (uint4*)(part + ((size_t)run * M + m) * N + n0 + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 8; q++) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else if (m < M) {
                         uint4* dst = (uint4*)(y + (size_t)m * ldy + n0 + c * 32);     // 16-byte aligned: y is, ldy is a multiple of 8
 #pragma unroll
                         for (int q = 0; q < 4; q++)
@@ -194,6 +204,43 @@ bool make_map(CUtensorMap* tm, const uint16_t* base, uint32_t rows, uint32_t K, 
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// y[m][n] (rows ldy apart) = sum over the runs of part[run][m][n], in run order
+__global__ void __launch_bounds__(256)
+f16_splitk_reduce_kernel(const float* __restrict__ part, uint16_t* __restrict__ y, uint32_t M, uint32_t N, uint32_t ldy, uint32_t S) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t quads = (size_t)M * N / 4, plane = quads;
+    const uint32_t nq = N / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < S; r++) {
+            const float4 p = __ldcg((const float4*)part + r * plane + i);
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        const size_t m = i / nq, n = (i % nq) * 4;
+        *(uint2*)(y + m * ldy + n) = make_uint2(pack2(acc.x, acc.y), pack2(acc.z, acc.w));
+    }
+}
+
+struct SplitScratch { float* part = nullptr; size_t bytes = 0; };
+
+// fp32 partial sums of the split-K form, per device, made on first use and grown when needed (never inside a capture)
+SplitScratch* split_scratch(cudaStream_t st, size_t need) {
+    static SplitScratch per_dev[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SplitScratch& sc = per_dev[dev];
+    if (sc.bytes >= need) return &sc;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }
+    cudaDeviceSynchronize();          // a launch in flight may still use the old buffer
+    if (sc.part) cudaFree(sc.part);
+    sc.part = nullptr; sc.bytes = 0;
+    if (cudaMalloc(&sc.part, need) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    sc.bytes = need;
+    return &sc;
+}
+
 template <int MH, int BN>
 bool launch(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy,
             unsigned int* status, int sms) {
@@ -203,13 +250,41 @@ bool launch(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, 
     const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + sizeof(FBarriers) + 16;
     static int have[64] = {};
     if (!ensure_dyn_smem(f16_gemm_sm100_kernel<MH, BN>, smem, have)) return false;
-    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN);
-    const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    if (launch_pdl(f16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, ta, tw, y, M, K, N, ldy, status) != cudaSuccess) {
+    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN), KG = K / BK;
+    // Split K while the tiles alone leave SMs idle (same rule as the W4A16 GEMM): the divisor of K/64 that makes
+    // (items per CTA) x (k blocks per item + set-up) smallest, a run at least one trip round the ring, partial sums <= 64 MB.
+    uint32_t S = 1;
+    if (tiles < (uint32_t)sms) {
+        float best = (float)(KG + 4);
+        for (uint32_t c = 2; c <= 32 && c <= KG; c++) {
+            if (KG % c || KG / c < (uint32_t)C::STAGES || (size_t)c * M * N * sizeof(float) > ((size_t)64 << 20)) continue;
+            const uint32_t rounds = (tiles * c + sms - 1) / sms;
+            const float cost = (float)rounds * (float)(KG / c + 4) + 0.75f * (float)c + 6.0f;
+            if (cost < best) { best = cost; S = c; }
+        }
+    }
+    float* part = nullptr;
+    if (S > 1) {
+        SplitScratch* ss = split_scratch(st, (size_t)S * M * N * sizeof(float));
+        if (ss) part = ss->part; else S = 1;
+    }
+    const uint32_t items = tiles * S;
+    const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
+    if (launch_pdl(f16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, ta, tw, y, M, K, N, ldy, status, S, part) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
     g_launches++;
+    if (S > 1) {
+        const size_t quads = (size_t)M * N / 4;
+        uint32_t rg = (uint32_t)((quads + 255) / 256);
+        if (rg > (uint32_t)sms * 8) rg = (uint32_t)sms * 8;
+        if (launch_pdl(f16_splitk_reduce_kernel, dim3(rg), dim3(256), 0, st, (const float*)part, y, M, N, ldy, S) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        g_launches++;
+    }
     return true;
 }
 

@@ -133,6 +133,7 @@ def test_matmul_f16_bit_exact(cuda, ref, M, K, N, t0, t1, Bn):
 NK_CASES = [  # M, K, N: weights stored [N, K]; M < 32 -> streaming GEMV, M >= 128 -> tcgen05 GEMM, between -> exact kernel
     (1, 128, 200), (3, 1024, 520), (8, 2560, 512), (20, 64, 136), (31, 256, 96), (64, 128, 128),
     (128, 64, 128), (130, 128, 256), (256, 512, 384), (300, 1024, 1280),
+    (256, 3072, 512),     # 8 tiles, 48 k blocks: K is split into runs
 ]
 
 
