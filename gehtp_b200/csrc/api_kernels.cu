@@ -144,7 +144,12 @@ int gehtp_dev_matmul_f16_nk(const uint16_t* a_dev, const uint16_t* w_dev, uint16
 int gehtp_dev_w4a16_swiglu(const uint16_t* a_dev, const uint32_t* pg, const uint16_t* sg, const uint32_t* pu,
                            const uint16_t* su, uint16_t* y_dev, uint32_t M, uint32_t K, uint32_t N) {
     if (!ensure_device(nullptr, 0)) return -1;
-    if (!M || M > 16 || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
+    if (!M || !K || !N || K % 64 || N % 16) return fail("w4a16 shape");
+    if (M >= w4_gemm_min_rows()) {       // the engine's rule: the tcgen05 gate | up GEMM from this many rows
+        if (k_w4a16_gemm_sm100_swiglu(g.stream, a_dev, pg, sg, pu, su, y_dev, M, K, N, g.d_status)) return 0;
+        return fail("w4a16 swiglu: shape not taken by the tcgen05 form");
+    }
+    if (M > 16) return fail("w4a16 swiglu: more than 16 rows below the GEMM's row count");
     k_w4a16_skinny_swiglu(g.stream, a_dev, pg, sg, pu, su, y_dev, M, K, N);
     return 0;
 }

@@ -409,6 +409,9 @@ bool match_swiglu_tail(const Graph& G, uint32_t ip, Span& sp) {
     sp.kind = 6; sp.first = first; sp.count = 5; sp.ops = ops; sp.keep = {(uint32_t)gate, (uint32_t)up};
     sp.gate_op = (uint32_t)gate; sp.up_op = (uint32_t)up; sp.gate_t = gt.args[2]; sp.up_t = u.args[2];
     sp.a_ref = gt.args[0]; sp.y = pr.args[2]; sp.n = n;
+    // one input and one K: the pair can also run as the gate | up GEMM
+    sp.M = gt.args[3]; sp.N = gt.args[5]; sp.K = (gt.args[0] == u.args[0] && gt.args[4] == u.args[4]) ? gt.args[4] : 0;
+    sp.wg = gt.args[1]; sp.wu = u.args[1];
     return true;
 }
 
@@ -646,7 +649,26 @@ void fuse_materialize(const wt_blob* b) {
             if ((((uintptr_t)gt) | ((uintptr_t)up) | ((uintptr_t)y)) & 15u) continue;
             auto lg = pg.launch, lu = pu.launch;
             size_t n = sp.n;
-            head.fused = [=](cudaStream_t st) { lg(st); lu(st); k_swiglu_tail(st, gt, up, y, n); };
+            // both projections and the elementwise tail on one tcgen05 kernel when they share input and shape
+            const uint16_t* act = sp.K ? (const uint16_t*)resolve(b, sp.a_ref) : nullptr;
+            auto find = [&](uint32_t wref) -> const W4Packed* {
+                uint64_t key = (uint64_t)(wref & 0x7FFFu) | ((uint64_t)sp.K << 16) | ((uint64_t)sp.N << 40);
+                auto it = g.w4.find(key);
+                return it == g.w4.end() ? nullptr : &it->second;
+            };
+            const W4Packed *wg = act ? find(sp.wg) : nullptr, *wu = act ? find(sp.wu) : nullptr;
+            if (wg && wu && !g.exact_ops && w4a16_gemm_sm100_swiglu_takes(sp.M, sp.K, sp.N) && !(((uintptr_t)act) & 15u)) {
+                const uint32_t *qg = wg->packed, *qu = wu->packed;
+                const uint16_t *sg = wg->scales, *su = wu->scales;
+                const uint32_t M = sp.M, K = sp.K, N = sp.N;
+                unsigned int* status = g.d_status;
+                head.fused = [=](cudaStream_t st) {
+                    if (k_w4a16_gemm_sm100_swiglu(st, act, qg, sg, qu, su, y, M, K, N, status)) return;
+                    lg(st); lu(st); k_swiglu_tail(st, gt, up, y, n);
+                };
+            } else {
+                head.fused = [=](cudaStream_t st) { lg(st); lu(st); k_swiglu_tail(st, gt, up, y, n); };
+            }
         } else if (sp.kind == 4) {
             const uint16_t *q = (const uint16_t*)resolve(b, sp.pq), *k = (const uint16_t*)resolve(b, sp.pk),
                            *v = (const uint16_t*)resolve(b, sp.pv);

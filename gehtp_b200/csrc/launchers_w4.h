@@ -63,5 +63,12 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,
                         const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
                         const W4Epilogue& ep, int tile = 0);
+// Gate and up projections of a gated FFN plus its three elementwise ops on the same kernel: y[M, N] =
+// fp16(fp16(g * fp16(sigmoid(g))) * u), g = a . Wg, u = a . Wu (both [K, N]), neither g nor u written to memory.
+// `takes`: the shape test alone (N a multiple of 128, K of 64); the launcher also wants
+// 16-byte aligned operands. false: nothing launched.
+bool w4a16_gemm_sm100_swiglu_takes(uint32_t M, uint32_t K, uint32_t N);
+bool k_w4a16_gemm_sm100_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* pg, const uint16_t* sg, const uint32_t* pu,
+                               const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, unsigned int* status);
 
 }  // namespace gehtp

@@ -140,11 +140,65 @@ __global__ void qkv_split_rope_kernel(const uint16_t* qkv, const uint16_t* __res
     }
 }
 
+// The same with 16-byte accesses: 8 consecutive values of a row per thread and step (head_dim a multiple of 16, so
+// that a group of 8 lies in one half of a head; all operands 16-byte aligned). Same products and roundings.
+__global__ void qkv_split_rope_vec8_kernel(const uint16_t* qkv, const uint16_t* __restrict__ cos_q,
+                                           const uint16_t* __restrict__ sin_q, const uint16_t* __restrict__ cos_k,
+                                           const uint16_t* __restrict__ sin_k, uint16_t* __restrict__ q_out,
+                                           uint16_t* __restrict__ k_out, uint16_t* __restrict__ v_out, uint32_t tokens,
+                                           uint32_t nh, uint32_t kvh, uint32_t hd) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t h = hd / 2, wq = nh * hd, wk = kvh * hd, W = wq + 2 * wk, W8 = W / 8;
+    const uint32_t n8 = tokens * W8;          // < 2^32: the caller checks
+    for (uint32_t e8 = blockIdx.x * blockDim.x + threadIdx.x; e8 < n8; e8 += gridDim.x * blockDim.x) {
+        const uint32_t t = e8 / W8, c = (e8 % W8) * 8;
+        const size_t e = (size_t)t * W + c;
+        const uint4 xv = *(const uint4*)(qkv + e);
+        if (c >= wq + wk) {
+            *(uint4*)(v_out + (size_t)t * wk + (c - wq - wk)) = xv;
+            continue;
+        }
+        const bool is_q = c < wq;
+        const uint32_t cc = is_q ? c : c - wq, d = cc % hd;
+        const size_t o = (size_t)t * (is_q ? wq : wk) + cc;
+        const uint4 pv = *(const uint4*)(qkv + (d < h ? e + h : e - h));
+        const uint4 cv = *(const uint4*)((is_q ? cos_q : cos_k) + o), sv = *(const uint4*)((is_q ? sin_q : sin_k) + o);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, pw[4] = {pv.x, pv.y, pv.z, pv.w};
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            uint16_t rr[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const float xf = h2f((uint16_t)(xw[w] >> (16 * k))), pf = h2f((uint16_t)(pw[w] >> (16 * k)));
+                const float rot = d < h ? -pf : pf;
+                const float xc = h2f(f2h(__fmul_rn(xf, h2f((uint16_t)(cw[w] >> (16 * k))))));
+                const float xs = h2f(f2h(__fmul_rn(rot, h2f((uint16_t)(sw[w] >> (16 * k))))));
+                rr[k] = f2h(__fadd_rn(xc, xs));
+            }
+            r[w] = (uint32_t)rr[0] | ((uint32_t)rr[1] << 16);
+        }
+        *(uint4*)((is_q ? q_out : k_out) + o) = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+}
+
 void k_qkv_split_rope(cudaStream_t st, const uint16_t* qkv, const uint16_t* cos_q, const uint16_t* sin_q,
                       const uint16_t* cos_k, const uint16_t* sin_k, uint16_t* q_out, uint16_t* k_out, uint16_t* v_out,
                       uint32_t tokens, uint32_t nh, uint32_t kvh, uint32_t hd) {
     const size_t n = (size_t)tokens * (nh + 2 * kvh) * hd;
     if (!n) return;
+    const uintptr_t all = (uintptr_t)qkv | (uintptr_t)cos_q | (uintptr_t)sin_q | (uintptr_t)cos_k | (uintptr_t)sin_k | (uintptr_t)q_out |
+                          (uintptr_t)k_out | (uintptr_t)v_out;
+    if (hd % 16 == 0 && !(all & 15u) && n / 8 < 0xFFFFFFFFull) {
+        size_t grid = (n / 8 + 255) / 256;
+        if (grid > 148 * 8) grid = 148 * 8;
+        launch_pdl(qkv_split_rope_vec8_kernel, dim3((unsigned)grid), dim3(256), 0, st, qkv, cos_q, sin_q, cos_k, sin_k, q_out, k_out, v_out,
+                   tokens, nh, kvh, hd);
+        g_launches++;
+        return;
+    }
     size_t grid = (n / 2 + 255) / 256;
     if (grid > 148 * 16) grid = 148 * 16;
     launch_pdl(qkv_split_rope_kernel, dim3((unsigned)grid), dim3(256), 0, st, qkv, cos_q, sin_q, cos_k, sin_k, q_out, k_out, v_out,

@@ -16,7 +16,7 @@
 //   warp 3     : owns the TMEM allocation.
 //   warps 4-7  : epilogue (tcgen05.ld -> fp16 -> 64-byte row segments).
 //   warps 8-23 : dequant, one group of four warps per operand stage (the 3-stage
-//                configuration leaves four warps idle). A warp turns its strip units into fp16 with
+//                configurations have no stage for warps 20-23: idle, or epilogue helpers in the gate | up form). A warp turns its strip units into fp16 with
 //                the magic-number trick, multiplies by the group scale and stores
 //                16-byte chunks into the stage's B tile in the 128B-swizzled
 //                K-major form tcgen05.mma reads.
@@ -33,6 +33,7 @@
 #include "common.cuh"
 #include "launchers_w4.h"
 #include "sm100_umma.cuh"
+#include "w4_stream.cuh"
 
 namespace gehtp {
 
@@ -53,9 +54,14 @@ constexpr int DQ_PER_STAGE = 4, EPI_WARPS = 4;   // 16 dequant warps, 4 of them 
 //   <2,256>: 256x256, 3 stages, one accumulator buffer (all 512 TMEM columns): per FLOP it reads
 //            45 % fewer operand bytes from L2 and a third fewer from shared memory than 256x128;
 //            the epilogue is not overlapped (a few % of a K >= 2048 main loop).
+//   <1,256>: 128x256, 3 stages, two accumulator buffers: the gate | up form (DUAL) at few rows.
+// DUAL (BN = 256 only): the B tile of a k block holds 128 columns of a first weight matrix (gate) and the same 128
+// columns of a second one (up); one N = 256 instruction feeds both accumulators and the epilogue writes
+// fp16(fp16(gate * fp16(sigmoid(gate))) * up), 128 output columns per tile: the two projections of a gated FFN and
+// the three elementwise ops behind them in one launch, neither projection's output going through memory.
 template <int MH, int BN>
 struct Cfg {
-    static constexpr int STAGES = (MH == 2 && BN == 256) ? 3 : 4;
+    static constexpr int STAGES = BN == 256 ? 3 : 4;
     static constexpr int NBUF = (MH * BN == 512) ? 1 : 2;
     // One dequant group (4 warps) per operand stage, and one int4/scale slot per group: group q only
     // ever waits on stage q and slot q, so it sees every phase of those barriers in turn. (A parity
@@ -69,12 +75,6 @@ struct Cfg {
     // instruction descriptor, kind::f16: A,B fp16 K-major, D fp32, M128 x N = BN
     static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 };
-
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 
 // 8 nibbles of one packed word -> 4 fp16 pairs (q-8)*scale: lo pairs belong to column g, hi pairs to g+8
 __device__ __forceinline__ void dequant_word(uint32_t w, __half2 slo, __half2 shi, uint32_t (&o)[4]) {
@@ -110,12 +110,24 @@ __device__ __forceinline__ uint32_t pack_out_res(float a, float b, uint32_t res)
     return (uint32_t)f2h(__fadd_rn(h2f(f2h(a)), ra)) | ((uint32_t)f2h(__fadd_rn(h2f(f2h(b)), rb)) << 16);
 }
 
-template <int MH, int BN>
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+template <int MH, int BN, bool DUAL = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4* __restrict__ wp,
-                        const uint16_t* __restrict__ sc, uint16_t* __restrict__ y, uint32_t M, uint32_t K,
+                        const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2, const uint16_t* __restrict__ sc2,
+                        uint16_t* __restrict__ y, uint32_t M, uint32_t K,
                         uint32_t N, W4Epilogue ep, uint32_t S, float* __restrict__ part) {
     using C = Cfg<MH, BN>;
+    static_assert(!DUAL || BN == 256, "the gate | up form pairs two 128-column halves");
+    static_assert(!DUAL || C::GROUPS == 3, "warps 20-23 help the epilogue of the gate | up form: they must own no operand stage");
+    constexpr uint32_t BN_OUT = DUAL ? BN / 2 : BN;      // output (and weight) columns of one tile
     constexpr int STAGES = C::STAGES, RSTAGES = C::RSTAGES, NBUF = C::NBUF;
     constexpr int A_BYTES = C::A_BYTES, B_BYTES = C::B_BYTES, RAW_BYTES = C::RAW_BYTES, RAW_SLOT = C::RAW_SLOT;
     constexpr uint32_t ACC_COLS = C::ACC_COLS, TMEM_COLS = C::TMEM_COLS;
@@ -133,7 +145,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     // drains; only the A loads and the epilogue's global accesses order themselves after it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m_tiles = (M + 128 * MH - 1) / (128 * MH), n_tiles = N / BN;
+    const uint32_t m_tiles = (M + 128 * MH - 1) / (128 * MH), n_tiles = N / BN_OUT;
     const uint32_t tiles = m_tiles * n_tiles;
     // Split K: S > 1 cuts the k blocks of every tile into S runs, one work item each (item = run * tiles + tile);
     // a run leaves its fp32 partial sums in `part` ([run][row][N]) and a small kernel behind this one adds the
@@ -146,7 +158,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             mbar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < RSTAGES; s++) { mbar_init(&bars->raw_full[s], 1); mbar_init(&bars->raw_empty[s], DQ_PER_STAGE); }
-        for (int s = 0; s < NBUF; s++) { mbar_init(&bars->tmem_full[s], 1); mbar_init(&bars->tmem_empty[s], EPI_WARPS); }
+        for (int s = 0; s < NBUF; s++) { mbar_init(&bars->tmem_full[s], 1); mbar_init(&bars->tmem_empty[s], DUAL ? 2 * EPI_WARPS : EPI_WARPS); }
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -215,24 +227,35 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
             uint32_t it = 0;
             for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
                 const uint32_t tile = item % tiles, kb0 = (item / tiles) * KGS;
-                const uint32_t n0 = (tile / m_tiles) * BN;
+                const uint32_t n0 = (tile / m_tiles) * BN_OUT;
                 const uint4* wsrc = wp + (size_t)(n0 / 16) * 32;
                 const uint16_t* ssrc = sc + n0;
+                const uint4* wsrc2 = DUAL ? wp2 + (size_t)(n0 / 16) * 32 : nullptr;
+                const uint16_t* ssrc2 = DUAL ? sc2 + n0 : nullptr;
                 for (uint32_t kb = kb0; kb < kb0 + KGS; kb++, it++) {
                     const uint32_t r = it % RSTAGES, ph = (it / RSTAGES) & 1;
                     if (*abort_flag || !mbar_wait(&bars->raw_empty[r], ph ^ 1)) { *abort_flag = 1; break; }
                     unsigned char* dst = sRaw + r * RAW_SLOT;
                     mbar_expect_tx(&bars->raw_full[r], RAW_SLOT);
-                    bulk_load(dst, wsrc + (size_t)kb * NB * 32, RAW_BYTES, &bars->raw_full[r]);
-                    bulk_load(dst + RAW_BYTES, ssrc + (size_t)kb * N, BN * 2, &bars->raw_full[r]);
+                    if (DUAL) {      // strip units 0-7 and scales 0-127 from the first matrix, the rest from the second
+                        bulk_load(dst, wsrc + (size_t)kb * NB * 32, RAW_BYTES / 2, &bars->raw_full[r]);
+                        bulk_load(dst + RAW_BYTES / 2, wsrc2 + (size_t)kb * NB * 32, RAW_BYTES / 2, &bars->raw_full[r]);
+                        bulk_load(dst + RAW_BYTES, ssrc + (size_t)kb * N, BN_OUT * 2, &bars->raw_full[r]);
+                        bulk_load(dst + RAW_BYTES + BN_OUT * 2, ssrc2 + (size_t)kb * N, BN_OUT * 2, &bars->raw_full[r]);
+                    } else {
+                        bulk_load(dst, wsrc + (size_t)kb * NB * 32, RAW_BYTES, &bars->raw_full[r]);
+                        bulk_load(dst + RAW_BYTES, ssrc + (size_t)kb * N, BN * 2, &bars->raw_full[r]);
+                    }
                 }
             }
             if (*abort_flag)
                 for (uint32_t j = it > (uint32_t)RSTAGES ? it - RSTAGES : 0; j < it; j++) mbar_wait(&bars->raw_full[j % RSTAGES], (j / RSTAGES) & 1);
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ---- epilogue: TMEM lane = output row; a warp may touch lanes (warp % 4) * 32 .. +31
+    } else if ((warp >= 4 && warp < 8) || (DUAL && warp >= 20)) {
+        // ---- epilogue: TMEM lane = output row; a warp may touch lanes (warp % 4) * 32 .. +31. The gate | up form
+        // (three operand stages: dequant warps 20-23 have no stage) gives those four warps every second column chunk.
         const uint32_t lane_base = (warp & 3) * 32;
+        const uint32_t chunk0 = (DUAL && warp >= 20) ? 1 : 0;
         uint32_t t = 0;
         // y (and the residual) may be memory the predecessor still reads or writes
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -262,7 +285,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, t++) {
             const uint32_t buf = t % NBUF;
             const uint32_t tile = item % tiles, run = item / tiles;
-            const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN;
+            const uint32_t m0 = (tile % m_tiles) * (128 * MH), n0 = (tile / m_tiles) * BN_OUT;
             bool ok = !__any_sync(0xffffffffu, *abort_flag != 0);
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[buf], (t / NBUF) & 1));
             if (!ok) { *abort_flag = 1; break; }
@@ -270,6 +293,28 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
 #pragma unroll 1
             for (int h = 0; h < MH; h++) {
                 const uint32_t m = m0 + h * 128 + lane_base + lane;
+                if (DUAL) {
+                    // gate in accumulator columns 0-127, up in 128-255: 16 columns of each at a time
+#pragma unroll 1
+                    for (uint32_t c = chunk0; c < BN_OUT / 16; c += 2) {
+                        uint32_t vg[16], vu[16];
+                        const uint32_t taddr = tmem + (lane_base << 16) + buf * ACC_COLS + h * BN + c * 16;
+                        tmem_ld16(taddr, vg);
+                        tmem_ld16(taddr + BN_OUT, vu);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (m < M) {
+                            uint32_t o[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                o[q] = swiglu_chain2(__uint_as_float(vg[2 * q]), __uint_as_float(vg[2 * q + 1]), __uint_as_float(vu[2 * q]),
+                                                     __uint_as_float(vu[2 * q + 1]));
+                            uint4* dst = (uint4*)(y + (size_t)m * N + n0 + c * 16);     // 32-byte aligned: N and n0 are multiples of 128
+                            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
+                    }
+                    continue;
+                }
 #pragma unroll 1
                 for (uint32_t c = 0; c < BN / 32; c++) {
                     uint32_t v[32];
@@ -418,20 +463,21 @@ SplitScratch* split_scratch(cudaStream_t st, size_t need) {
     return &sc;
 }
 
-template <int MH, int BN>
+template <int MH, int BN, bool DUAL = false>
 bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, const uint16_t* sc, uint16_t* y,
-            uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms) {
+            uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms, const uint32_t* packed2 = nullptr,
+            const uint16_t* sc2 = nullptr) {
     using C = Cfg<MH, BN>;
     const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + (size_t)C::RSTAGES * C::RAW_SLOT + sizeof(Barriers) + 16;
     static int have[64] = {};
-    if (!ensure_dyn_smem(w4a16_gemm_sm100_kernel<MH, BN>, smem, have)) return false;
-    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / BN), KG = K / BK;
+    if (!ensure_dyn_smem(w4a16_gemm_sm100_kernel<MH, BN, DUAL>, smem, have)) return false;
+    const uint32_t tiles = ((M + 128 * MH - 1) / (128 * MH)) * (N / (DUAL ? BN / 2 : BN)), KG = K / BK;
     // Split K when the tiles alone leave SMs idle. A CTA walks a k block in about 0.42 us whatever the shape, so
     // the launch lasts (items per CTA) x (k blocks per item + set-up); S is the divisor of K/64 that makes that
     // smallest, a run keeping at least one trip round the operand ring, the partial sums at most 64 MB.
     static const int split_on = [] { const char* e = std::getenv("GEHTP_CUDA_SPLITK"); return e ? std::atoi(e) : 1; }();
     uint32_t S = 1;
-    if (split_on && tiles < (uint32_t)sms) {
+    if (split_on && !DUAL && tiles < (uint32_t)sms) {      // the gate | up form keeps its product in the epilogue: no runs
         float best = (float)(KG + 4);
         for (uint32_t c = 2; c <= 32 && c <= KG; c++) {
             if (KG % c || KG / c < (uint32_t)C::STAGES || (size_t)c * M * N * sizeof(float) > ((size_t)64 << 20)) continue;
@@ -447,7 +493,8 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     }
     const uint32_t items = tiles * S;
     const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
-    if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc, y, M, K, N, ep, S, part) != cudaSuccess) {
+    if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN, DUAL>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc,
+                   (const uint4*)packed2, sc2, y, M, K, N, ep, S, part) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
@@ -465,15 +512,18 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     return true;
 }
 
-}  // namespace
-
-bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
-                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile) {
-    if (!M || K % BK || N % 128) return false;
-    if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)sc & 15) || ((uintptr_t)y & 15)) return false;
-    if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
+bool make_a_map(CUtensorMap* tmap, const uint16_t* a, uint32_t M, uint32_t K) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
+    cuuint64_t dims[2] = {K, M};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {BK, 128};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
     static int sms_of[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -482,14 +532,19 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
+    return sms;
+}
+
+}  // namespace
+
+bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
+                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile) {
+    if (!M || K % BK || N % 128) return false;
+    if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)sc & 15) || ((uintptr_t)y & 15)) return false;
+    if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
+    const int sms = sm_count();
     CUtensorMap tmap;
-    cuuint64_t dims[2] = {K, M};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {BK, 128};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
+    if (!make_a_map(&tmap, a, M, K)) return false;
     // Largest tile that still gives every SM a tile.
     const uint32_t t256 = ((M + 255) / 256) * (N / 256);
     const uint32_t t128 = ((M + 255) / 256) * (N / 128);
@@ -498,6 +553,25 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
         return launch<2, 256>(st, tmap, packed, sc, y, M, K, N, ep, sms);
     if (force == 2 || (force == 0 && M > 128 && t128 >= (uint32_t)sms)) return launch<2, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
     return launch<1, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
+}
+
+bool w4a16_gemm_sm100_swiglu_takes(uint32_t M, uint32_t K, uint32_t N) {
+    static const int on = [] { const char* e = std::getenv("GEHTP_CUDA_GEMM_SWIGLU"); return e ? std::atoi(e) : 1; }();
+    return on && M && K && K % BK == 0 && N && N % 128 == 0;
+}
+
+bool k_w4a16_gemm_sm100_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* pg, const uint16_t* sg, const uint32_t* pu,
+                               const uint16_t* su, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, unsigned int* status) {
+    if (!w4a16_gemm_sm100_swiglu_takes(M, K, N)) return false;
+    if (((uintptr_t)a | (uintptr_t)pg | (uintptr_t)sg | (uintptr_t)pu | (uintptr_t)su | (uintptr_t)y) & 15) return false;
+    const int sms = sm_count();
+    CUtensorMap tmap;
+    if (!make_a_map(&tmap, a, M, K)) return false;
+    W4Epilogue ep;
+    ep.status = status;
+    // 256 rows per tile once that still gives every SM a tile
+    if (M > 128 && ((M + 255) / 256) * (N / 128) >= (uint32_t)sms) return launch<2, 256, true>(st, tmap, pg, sg, y, M, K, N, ep, sms, pu, su);
+    return launch<1, 256, true>(st, tmap, pg, sg, y, M, K, N, ep, sms, pu, su);
 }
 
 }  // namespace gehtp

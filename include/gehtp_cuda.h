@@ -269,7 +269,9 @@ int gehtp_attn_decode(const uint16_t* q, const uint16_t* kv_ring, const uint16_t
  * waited for. `packed_dev` is the strip-major layout made by gehtp_dev_w4_repack
  * from the nibble part of a weight slot (K*N/2 bytes in, K*N/2 bytes out);
  * `scales_dev` is the fp16 [K/64][N] part of the slot. gehtp_dev_w4a16_swiglu
- * computes silu-gated gate/up projections in one pass (M <= 16);
+ * computes silu-gated gate/up projections in one pass (M <= 16: the streaming
+ * kernel; M >= 64 with N a multiple of 128: the tcgen05 GEMM with both
+ * accumulators in TMEM; -1 for shapes neither form takes);
  * gehtp_dev_rmsnorm normalises f16(x + res) when res_dev is given (and stores
  * that sum to sum_dev when not NULL). */
 int gehtp_dev_w4_repack(const uint8_t* slot_dev, uint32_t* packed_dev, uint32_t K, uint32_t N);

@@ -320,14 +320,17 @@ def test_kernel_family_switches_agree(cuda, tmp_path):
         assert not np.array_equal(outs[name].view(np.uint16), outs["default"].view(np.uint16)), name + ": the switch changed nothing"
 
 
-@pytest.mark.parametrize("tokens", [70, 133])
-def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens):
+@pytest.mark.parametrize("tokens,F,hd", [(70, 512, 128), (133, 512, 128), (300, 9728, 128), (133, 320, 128), (70, 512, 24)])
+def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens, F, hd):
     """The head of a prefill block (3 SPLITs + 2 rotary chains, 17 ops, one kernel) and a SwiGLU over
-    more than 64 rows (two GEMMs + one elementwise kernel for the 3 elementwise ops) keep every fp16
-    rounding point of the ops they replace: fused and op-by-op plans agree bit for bit."""
+    64 rows or more keep every fp16 rounding point of the ops they replace: fused and op-by-op plans agree
+    bit for bit. The SwiGLU runs as one tcgen05 launch (gate and up accumulators side by side in TMEM, the
+    three elementwise ops in the epilogue; 128-row tiles, and 256-row tiles at the 9728-wide case) or, where
+    the width is no multiple of 128 (320), as two GEMMs and one elementwise kernel. Head size 24 takes the split +
+    rotary kernel's 4-byte form, the others its 16-byte form."""
     from gehtp_b200.runlists import Emitter, rand_w4, rope_tables
     rng = np.random.default_rng(31)
-    H, nh, kvh, hd, F = 256, 4, 2, 128, 512
+    H, nh, kvh = 256, 4, 2
     e = Emitter("w4")
     face = e.b.add_ext_in(tokens * H * 2)
     cos, sin = rope_tables(hd, np.arange(tokens), 1e6)
