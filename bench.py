@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--config", type=int, default=None, choices=[1, 2, 3, 5],
                     help="one line for another baseline configuration (1: single W4A16 matmul, 2: RMSNorm + decode attention, "
                          "3: 0.6B-shape prefill, 5: gated delta-rule layer) with its roofline and the reference's CPU time")
-    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "swiglu", "gemm1", "gemm512", "f16gemm", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
+    ap.add_argument("--micro", default=None, choices=["gemv", "lmhead", "gemm", "swiglu", "swiglu512", "gemm1", "gemm512", "f16gemm", "headline", "gemmtiles", "attn", "attn8", "norm", "prefill", "gdn", "all"],
                     help="time single kernels (device-resident operands, graph replay) instead of the decode step")
     return ap.parse_args()
 
@@ -414,6 +414,11 @@ def run_micro(which):
             us1, _, _ = w4(M, K, N, 2, n=8)
             out.append({"kernel": "w4a16_gemm_tcgen05_swiglu", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
                         "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf, "one_projection_alone_us": us1})
+    if which == "swiglu512":   # the gate | up launch of the 0.6B-shape prefill alone: a small case for profiler captures
+        M, K, N = 512, 1024, 3072
+        us, _, flops = w4(M, K, N, 0, dual=True, n=4)
+        out.append({"kernel": "w4a16_gemm_tcgen05_swiglu", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
+                    "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
     if which in ("f16gemm", "all"):   # OP_MATMUL_F16 with weights stored [N, K]: tcgen05 GEMM (M >= 128) and streaming GEMV (M < 32)
         for (M, K, N) in ((1, 1024, 151936), (8, 2560, 9728), (128, 1024, 3072), (512, 1024, 4096), (2048, 2560, 9728), (8192, 2560, 9728)):
             copies = min(max(2, int(300e6 // (2 * K * N)) + 1), 16)

@@ -110,19 +110,22 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&bars->full[j % STAGES], (j / STAGES) & 1);
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            uint32_t it = 0, t = 0;
-            const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
-            for (uint32_t item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, t++) {
-                const uint32_t buf = t % NBUF;
-                if (!mbar_wait(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1)) { *abort_flag = 1; break; }
+        // MMA issue. The whole warp walks the loop, so that the loop counters, the descriptors and the barrier
+        // addresses are warp-uniform values; lane 0 alone executes the tcgen05 instructions.
+        uint32_t it = 0, t = 0;
+        const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
+        bool live = true;
+        for (uint32_t item = blockIdx.x; item < items && live; item += gridDim.x, t++) {
+            const uint32_t buf = t % NBUF;
+            if (!__all_sync(0xffffffffu, mbar_wait_or_abort(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1, abort_flag))) { *abort_flag = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + buf * ACC_COLS;
+            for (uint32_t kb = 0; kb < KGS; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait_or_abort(&bars->full[s], ph, abort_flag))) { *abort_flag = 1; live = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t acc = tmem + buf * ACC_COLS;
-                for (uint32_t kb = 0; kb < KGS; kb++, it++) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (*abort_flag || !mbar_wait(&bars->full[s], ph)) { *abort_flag = 1; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da0 = umma_desc(a_base + s * A_BYTES), db0 = umma_desc(b_base + s * B_BYTES);
+                const uint64_t da0 = umma_desc(a_base + s * A_BYTES), db0 = umma_desc(b_base + s * B_BYTES);
+                if (lane == 0) {
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; k4++) {
 #pragma unroll
@@ -132,9 +135,11 @@ f16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     }
                     umma_commit(&bars->empty[s]);
                 }
-                if (*abort_flag) break;
-                umma_commit(&bars->tmem_full[buf]);
+                __syncwarp();
             }
+            if (!live) break;
+            if (lane == 0) umma_commit(&bars->tmem_full[buf]);
+            __syncwarp();
         }
     } else if (warp >= 4) {
         // epilogue: TMEM lane = output row; a warp may touch lanes (warp % 4) * 32 .. +31
