@@ -194,21 +194,20 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
     } else if (warp == 1) {
         // ---- MMA issue. The whole warp walks the loop, so that the loop counters, the descriptors and the barrier
         // addresses are warp-uniform values; lane 0 alone executes the tcgen05 instructions.
-        uint32_t it = 0, t = 0;
-        const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
+        uint32_t t = 0, s = 0, ph = 0;          // operand stage and phase parity of the k block in hand
+        // descriptors of stage 0's first K16 slice; a stage lies A_BYTES / B_BYTES further, a K16 slice 32 bytes
+        // (the start-address field counts 16-byte units), the second row half HALF_A_BYTES
+        const uint64_t da_base = umma_desc(smem_u32(sA)), db_base = umma_desc(smem_u32(sB));
         bool live = true;
         for (uint32_t item = blockIdx.x; item < items && live; item += gridDim.x, t++) {
             const uint32_t buf = t % NBUF;
             if (!__all_sync(0xffffffffu, mbar_wait_or_abort(&bars->tmem_empty[buf], ((t / NBUF) & 1) ^ 1, abort_flag))) { *abort_flag = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + buf * ACC_COLS;
-            for (uint32_t kb = 0; kb < KGS; kb++, it++) {
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            for (uint32_t kb = 0; kb < KGS; kb++) {
                 if (!__all_sync(0xffffffffu, mbar_wait_or_abort(&bars->full[s], ph, abort_flag))) { *abort_flag = 1; live = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // descriptors of the stage's first K16 slice; the next slices start 32 bytes further
-                // (the start-address field counts 16-byte units), the second row half HALF_A_BYTES further
-                const uint64_t da0 = umma_desc(a_base + s * A_BYTES), db0 = umma_desc(b_base + s * B_BYTES);
+                const uint64_t da0 = da_base + (uint64_t)(s * (A_BYTES >> 4)), db0 = db_base + (uint64_t)(s * (B_BYTES >> 4));
                 if (lane == 0) {
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; k4++) {
@@ -220,6 +219,7 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                     umma_commit(&bars->empty[s]);
                 }
                 __syncwarp();
+                if (++s == (uint32_t)STAGES) { s = 0; ph ^= 1u; }
             }
             if (!live) break;
             if (lane == 0) umma_commit(&bars->tmem_full[buf]);
