@@ -21,6 +21,8 @@ struct KvGeom {
     uint32_t* posmap = nullptr;  // device, nslots entries
 };
 
+struct W4Epilogue;
+
 // One runlist op after planning: resolved device pointers baked into `launch`.
 struct PlanOp {
     int rc = 0;                 // non-zero: the op fails when reached, with `err`
@@ -33,6 +35,8 @@ struct PlanOp {
     int kv_append_state = -1;   // AUTO append: host counter check / bump
     int kv_gather_state = -1;   // AUTO gather: host counter check
     uint32_t w4_m = 0;          // M of a W4A16 matmul (reported through engine_m)
+    // a W4A16 matmul at GEMM row counts: the tcgen05 GEMM with an epilogue of the caller's (false: shape not taken)
+    std::function<bool(cudaStream_t, const W4Epilogue&)> launch_w4_gemm;
     // fusion: when `fused` is set on op i, it replaces ops [i, i + span)
     std::function<void(cudaStream_t)> fused;
     uint32_t span = 0;

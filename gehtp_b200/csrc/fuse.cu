@@ -722,6 +722,29 @@ void fuse_materialize(const wt_blob* b) {
             if (!rw || sp.n % rw) continue;
             uint32_t rows = sp.n / rw;
             head.fused = [=](cudaStream_t st) { k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw); };
+            // One GPU: when the addend is the output of the W4A16 GEMM right before the ADD, the three ops run as the
+            // GEMM with the add and the norm in its epilogue (with K split into runs: in the kernel that adds the runs).
+            if (g.tp_world <= 1 && sp.first > 0 && !g.exact_ops && rw > 512) {
+                PlanOp& lin = g.plan[sp.first - 1];
+                const bool b_is_out = is_temp_ref(sp.add_b) && lin.out_id[0] == sp.add_b;
+                const bool a_is_out = is_temp_ref(sp.add_a) && lin.out_id[0] == sp.add_a;
+                if (lin.launch_w4_gemm && lin.launch && !lin.fused && !lin.rc && !lin.uses_internal && (a_is_out != b_is_out) &&
+                    lin.out_bytes[0] == sp.n * 2u && lin.w4_m == rows && sum && gam) {
+                    auto gemm = lin.launch_w4_gemm;
+                    auto plain = lin.launch;
+                    const uint16_t* res = b_is_out ? aa : ab;
+                    unsigned int* status = g.d_status;
+                    lin.fused = [=](cudaStream_t st) {
+                        W4Epilogue ep;
+                        ep.mode = 3; ep.status = status; ep.res = res; ep.gamma = gam; ep.beta = bet; ep.sum_out = sum; ep.norm_out = y;
+                        if (gemm(st, ep)) return;
+                        plain(st);
+                        k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw);
+                    };
+                    lin.span = 3;
+                    g.fused_ops += 1;
+                }
+            }
             // Tensor parallel: when the addend is the partial sum of the row-parallel
             // projection right before the ADD, projection + all-reduce + add + norm run
             // as two launches: the projection, then one kernel that exchanges the rows

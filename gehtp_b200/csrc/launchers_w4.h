@@ -14,9 +14,16 @@ namespace gehtp {
 //           (matmul output -> fp16, x*cos -> fp16, rot(x)*sin -> fp16, sum -> fp16), q goes to
 //           q_out, k and v go straight into the KV ring slot of the position (SPLIT x3 + rotary
 //           chain x2 + KV_APPEND of the runlist). Streaming kernel only, M <= 8.
+//   mode 3: the matmul is followed by a residual ADD and an RMSNORM2 (tcgen05 GEMM only): y = f16(acc) as in
+//           mode 0, sum_out = f16(y + res), norm_out = rmsnorm(sum_out) * gamma + beta with the roundings of the
+//           two ops. With K split into runs the kernel that adds the runs also adds the residual and normalises
+//           (one CTA per row); otherwise the add + norm kernel is launched behind the GEMM.
 struct W4Epilogue {
     int mode = 0;
     const uint16_t* res = nullptr;
+    // mode 3
+    const uint16_t *gamma = nullptr, *beta = nullptr;
+    uint16_t *sum_out = nullptr, *norm_out = nullptr;
     unsigned int* status = nullptr;   // engine status word: the tcgen05 GEMM reports a barrier wait that ran out here
     // mode 2
     const uint16_t *cos_q = nullptr, *sin_q = nullptr, *cos_k = nullptr, *sin_k = nullptr;   // [M*heads][hd]

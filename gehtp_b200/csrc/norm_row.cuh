@@ -17,8 +17,16 @@ namespace gehtp {
 // (a kernel that normalises several rows side by side). The partition of the
 // sums over threads depends on BLOCK only, so both uses give the same bits. `a` and `r` are
 // read with L2-only loads: they may have been written by other CTAs of the same launch.
-template <int BLOCK, class Sync>
-__device__ __forceinline__ void rmsnorm_row_t(const uint32_t tid, Sync sync, const uint16_t* a, const uint16_t* r,
+// `load_a(i)` returns the 8 values a[i .. i+7] of the row: by default a 16-byte L2 load of `a`; a kernel that forms
+// the row itself (the sum of a split-K GEMM's runs) passes its own and a null `a` - only the 16-byte paths
+// use it, so such a caller must meet their conditions (width a multiple of 8, 16-byte aligned operands).
+struct NormLoadGlobal {
+    const uint16_t* a;
+    __device__ __forceinline__ uint4 operator()(uint32_t i) const { return __ldcg((const uint4*)(a + i)); }
+};
+
+template <int BLOCK, class Sync, class LoadA>
+__device__ __forceinline__ void rmsnorm_row_t(const uint32_t tid, Sync sync, LoadA load_a, const uint16_t* a, const uint16_t* r,
                                               const uint16_t* __restrict__ g, const uint16_t* __restrict__ b,
                                               uint16_t* sum_out, uint16_t* y, uint32_t width, float* row, double* part,
                                               float* s_rms) {
@@ -36,7 +44,7 @@ __device__ __forceinline__ void rmsnorm_row_t(const uint32_t tid, Sync sync, con
                 const uint32_t i = tid * 8 + u * BLOCK * 8;
                 qa4[u] = make_uint4(0, 0, 0, 0); qr4[u] = make_uint4(0, 0, 0, 0);
                 if (i < width) {
-                    qa4[u] = __ldcg((const uint4*)(a + i));
+                    qa4[u] = load_a(i);
                     if (r) qr4[u] = __ldcg((const uint4*)(r + i));
                 }
             }
@@ -112,7 +120,7 @@ __device__ __forceinline__ void rmsnorm_row_t(const uint32_t tid, Sync sync, con
                 const uint32_t i = i0 + u * BLOCK * 8;
                 qa4[u] = make_uint4(0, 0, 0, 0); qr4[u] = make_uint4(0, 0, 0, 0);
                 if (i < width) {
-                    qa4[u] = __ldcg((const uint4*)(a + i));
+                    qa4[u] = load_a(i);
                     if (r) qr4[u] = __ldcg((const uint4*)(r + i));
                 }
             }
@@ -193,7 +201,7 @@ template <int BLOCK>
 __device__ __forceinline__ void rmsnorm_row(const uint16_t* a, const uint16_t* r, const uint16_t* __restrict__ g,
                                             const uint16_t* __restrict__ b, uint16_t* sum_out, uint16_t* y,
                                             uint32_t width, float* row, double* part, float* s_rms) {
-    rmsnorm_row_t<BLOCK>(threadIdx.x, [] { __syncthreads(); }, a, r, g, b, sum_out, y, width, row, part, s_rms);
+    rmsnorm_row_t<BLOCK>(threadIdx.x, [] { __syncthreads(); }, NormLoadGlobal{a}, a, r, g, b, sum_out, y, width, row, part, s_rms);
 }
 
 }  // namespace gehtp

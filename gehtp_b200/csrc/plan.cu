@@ -197,6 +197,8 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
                 if (M >= w4_gemm_min_rows() && k_w4a16_gemm_sm100(st, act, pk, sc, y, M, K, N, ep)) return;
                 k_w4a16_skinny(st, act, pk, sc, y, M, K, N, ep);
             };
+            if (M >= w4_gemm_min_rows())
+                p.launch_w4_gemm = [=](cudaStream_t st, const W4Epilogue& ep) { return k_w4a16_gemm_sm100(st, act, pk, sc, y, M, K, N, ep); };
         }
         return;
     }

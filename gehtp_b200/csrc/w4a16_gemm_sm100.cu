@@ -34,6 +34,7 @@
 #include "launchers_w4.h"
 #include "sm100_umma.cuh"
 #include "w4_stream.cuh"
+#include "norm_row.cuh"
 
 namespace gehtp {
 
@@ -448,6 +449,40 @@ w4a16_splitk_reduce_kernel(const float* __restrict__ part, uint16_t* __restrict_
     }
 }
 
+// The same reduction for a GEMM that is followed by a residual add and an RMSNorm (W4Epilogue mode 3): one CTA per
+// output row adds the runs (in run order, as above), stores y = f16(sum), then f16(y + res) and its norm - the
+// add + norm kernel with the row taken from the partial sums instead of from y.
+struct NormLoadRuns {
+    const float* part;      // this row's partial sums of run 0
+    size_t plane;           // floats between two runs
+    uint32_t S;
+    uint16_t* y;            // this row of the GEMM's own output
+    __device__ __forceinline__ uint4 operator()(uint32_t i) const {
+        float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < S; r++) {
+            const float4 p = __ldcg((const float4*)(part + r * plane + i)), q = __ldcg((const float4*)(part + r * plane + i + 4));
+            lo.x += p.x; lo.y += p.y; lo.z += p.z; lo.w += p.w;
+            hi.x += q.x; hi.y += q.y; hi.z += q.z; hi.w += q.w;
+        }
+        const uint4 o = make_uint4(pack_out(lo.x, lo.y), pack_out(lo.z, lo.w), pack_out(hi.x, hi.y), pack_out(hi.z, hi.w));
+        *(uint4*)(y + i) = o;
+        return o;
+    }
+};
+
+__global__ void __launch_bounds__(256)
+w4a16_splitk_add_rmsnorm_kernel(const float* __restrict__ part, uint16_t* __restrict__ y, uint32_t M, uint32_t N, uint32_t S, W4Epilogue ep) {
+    extern __shared__ float row[];      // N floats (rows wider than the register form takes)
+    __shared__ double red[256 / 32];
+    __shared__ float s_rms;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t base = (size_t)blockIdx.x * N;
+    const NormLoadRuns load{part + base, (size_t)M * N, S, y + base};
+    rmsnorm_row_t<256>(threadIdx.x, [] { __syncthreads(); }, load, (const uint16_t*)nullptr, ep.res + base, ep.gamma, ep.beta, ep.sum_out + base,
+                       ep.norm_out + base, N, row, red, &s_rms);
+}
+
 // Scratch of the split-K form (fp32 partial sums), per device, made on first use and grown when needed.
 struct SplitScratch { float* part = nullptr; size_t bytes = 0; };
 
@@ -503,7 +538,13 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
         return false;
     }
     g_launches++;
-    if (S > 1) {
+    if (S > 1 && ep.mode == 3) {
+        if (launch_pdl(w4a16_splitk_add_rmsnorm_kernel, dim3(M), dim3(256), (size_t)N * sizeof(float), st, (const float*)part, y, M, N, S, ep) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        g_launches++;
+    } else if (S > 1) {
         const size_t quads = (size_t)M * N / 4;
         uint32_t rg = (uint32_t)((quads + 255) / 256);
         if (rg > (uint32_t)sms * 8) rg = (uint32_t)sms * 8;
@@ -513,6 +554,7 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
         }
         g_launches++;
     }
+    if (S == 1 && ep.mode == 3) k_add_rmsnorm(st, y, ep.res, ep.gamma, ep.beta, ep.sum_out, ep.norm_out, M, N);
     return true;
 }
 
@@ -546,6 +588,9 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
     if (!M || K % BK || N % 128) return false;
     if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)sc & 15) || ((uintptr_t)y & 15)) return false;
     if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
+    if (ep.mode == 3 && (!ep.res || !ep.gamma || !ep.sum_out || !ep.norm_out || N * sizeof(float) > 48u * 1024u ||
+                         (((uintptr_t)ep.res | (uintptr_t)ep.gamma | (uintptr_t)ep.beta | (uintptr_t)ep.sum_out | (uintptr_t)ep.norm_out) & 15)))
+        return false;
     const int sms = sm_count();
     CUtensorMap tmap;
     if (!make_a_map(&tmap, a, M, K)) return false;

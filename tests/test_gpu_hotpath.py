@@ -358,6 +358,35 @@ def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens, F, hd):
         assert a.size and np.array_equal(a, b2), name
 
 
+@pytest.mark.parametrize("tokens,K,N", [(70, 1024, 1024), (133, 256, 2560), (600, 256, 9728)])
+def test_gemm_with_add_and_norm_in_its_epilogue_bit_equal(cuda, tokens, K, N):
+    """W4A16 GEMM -> residual ADD -> RMSNORM2 at GEMM row counts runs as the GEMM plus one kernel that adds
+    the split-K runs, the residual, and normalises (first two shapes: fewer tiles than SMs, K split), or as the
+    GEMM plus the add + norm kernel (third shape: tiles fill the SMs). GEMM output, sum and norm agree bit for bit
+    with the one-kernel-per-op plan."""
+    from gehtp_b200.runlists import Emitter, rand_w4
+    rng = np.random.default_rng(77)
+    e = Emitter("w4")
+    face = e.b.add_ext_in(tokens * (K + N) * 2)
+    x = e.face(S(face), 0, tokens * K, tokens * (K + N))
+    res = e.face(S(face), tokens * K, tokens * N, tokens * (K + N))
+    lin = e.linear(x, *rand_w4(rng, K, N), tokens)
+    summed = e.binary(res, lin, tokens * N, 0)
+    normed = e.rmsnorm(summed, rng.normal(1.0, 0.1, N), tokens * N)
+    buf = e.b.build()
+    inp = np.concatenate([rng.standard_normal(tokens * K), rng.standard_normal(tokens * N)]).astype(np.float16)
+    out = []
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        eng.run_io(inp, normed, None)
+        out.append([eng.temp(t, np.uint16).copy() for t in (lin, summed, normed)])
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    for a, b2, name in zip(out[0], out[1], ("gemm", "sum", "norm")):
+        assert a.size and np.array_equal(a, b2), name
+
+
 def test_gdn_layer_runlist_matches_reference(cuda, ref):
     """Config 5 in small: W4A16 in-projection, causal conv1d, four delta-rule chunks carrying the
     fp32 state, out-projection per chunk; against the reference executor with dequantised weights."""
