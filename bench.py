@@ -410,8 +410,10 @@ def run_micro(which):
                         "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf})
     if which in ("gemm", "swiglu", "all"):   # gate | up of a gated FFN as one tcgen05 launch (product in the epilogue) beside one of its two GEMMs
         for (M, K, N) in ((64, 2560, 9728), (512, 1024, 3072), (2048, 2560, 9728)):
-            us, _, flops = w4(M, K, N, 0, dual=True, n=8)
-            us1, _, _ = w4(M, K, N, 2, n=8)
+            # graphs of 4 launches: in a longer chain of this one kernel the early CTAs of the next launches (released at
+            # kernel entry) hold SMs while they wait for their predecessors and the figure stops describing a launch
+            us, _, flops = w4(M, K, N, 0, dual=True, n=4)
+            us1, _, _ = w4(M, K, N, 2, n=4)
             out.append({"kernel": "w4a16_gemm_tcgen05_swiglu", "M": M, "K": K, "N": N, "us": us, "TFLOPs": flops / us / 1e6,
                         "frac_of_measured_bf16_peak": flops / us / 1e6 / peak_tf, "one_projection_alone_us": us1})
     if which == "swiglu512":   # the gate | up launch of the 0.6B-shape prefill alone: a small case for profiler captures
