@@ -220,7 +220,9 @@ def run_ours(args, rank, world):
 
     rng = np.random.default_rng(4)
     faces = [decode_face(man, rng.integers(0, cfg.vocab, B), p0 + s, hd, cfg.rope_theta) for s in range(total_steps)]
-    out_host = np.zeros(2 * B, np.uint16)
+    # the step's result: B int32 tokens; a tensor-parallel shard adds the B fp16 row maxima its argmax goes with
+    out_units = (3 if shard > 1 else 2) * B
+    out_host = np.zeros(out_units, np.uint16)
     stream = torch.cuda.ExternalStream(lib.gehtp_cuda_stream())
     tok_temp = man["token_temp"]
 
@@ -276,7 +278,7 @@ def run_ours(args, rank, world):
 
     # ---- device-resident: faces already in HBM, tokens stay on the device
     faces_dev = [torch.from_numpy(f.view(np.int16).copy()).cuda() for f in faces]
-    out_dev = torch.zeros(2 * B, dtype=torch.int16, device="cuda")
+    out_dev = torch.zeros(out_units, dtype=torch.int16, device="cuda")
     torch.cuda.synchronize()
 
     def step_dev(s):

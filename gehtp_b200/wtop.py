@@ -284,7 +284,12 @@ class Engine:
             self._in_keep = np.ascontiguousarray(inp)
             ip = self._in_keep.ctypes.data
         op = out.ctypes.data if out is not None else None
+        # wt_exec_run_io copies the temp's last byte count into `out` and takes no size (the reference's contract):
+        # a buffer that was too small is reported right after the call instead of corrupting the heap in silence
         self._check(self.lib.wt_exec_run_io(ctypes.byref(self.blob), ip, op, out_temp, None, None, self._err, 256))
+        if out is not None and self.lib.wt_exec_temp_last_bytes(out_temp) > out.nbytes:
+            raise ValueError("out held %d bytes, temp %d wrote %d: memory behind `out` was overwritten"
+                             % (out.nbytes, out_temp, self.lib.wt_exec_temp_last_bytes(out_temp)))
         return out
 
     def temp(self, tid, dtype=np.float16):
