@@ -358,6 +358,40 @@ def test_prefill_split_rotary_and_swiglu_tail_bit_equal(cuda, tokens, F, hd):
         assert a.size and np.array_equal(a, b2), name
 
 
+@pytest.mark.parametrize("M,K,F", [(64, 64, 128), (65, 128, 256), (257, 64, 128), (128, 2560, 256), (384, 192, 9728)])
+def test_gate_up_gemm_edge_shapes_bit_equal(cuda, M, K, F):
+    """The gate | up GEMM at its smallest shape (64 rows, one k block, one tile), with ragged last row tiles, a long K
+    and enough tiles for the 256-row form: the fused plan's SwiGLU output agrees bit for bit with the op-by-op plan
+    wherever the two separate GEMMs of that plan walk K in one run (fewer than 8 k blocks: nothing to split). With
+    a long K and two tiles they split K into runs and add fp32 partial sums in another order than the one-launch
+    form does: the fp16 gate there."""
+    from gehtp_b200.runlists import Emitter, rand_w4
+    rng = np.random.default_rng(5)
+    e = Emitter("w4")
+    face = e.b.add_ext_in(M * K * 2)
+    d = e.swiglu(S(face), M, rand_w4(rng, K, F), rand_w4(rng, K, F), rand_w4(rng, F, 64))
+    act = d - 1            # the SwiGLU product feeding the down projection (the temp made right before its output)
+    buf = e.b.build()
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    res = []
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        eng.run_io(x, d, None)
+        res.append([eng.temp(t, np.uint16).copy() for t in (act, d)])
+        if fusion:
+            assert cuda.gehtp_cuda_fused_ops() == 5
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    for a, b2, name in zip(res[0], res[1], ("swiglu", "down")):
+        assert a.size == b2.size and a.size
+        if K // 64 < 8:
+            assert np.array_equal(a, b2), name
+        else:
+            assert_fp16_close(a.view(np.float16), b2.view(np.float16), name)
+    assert np.isfinite(res[0][0].view(np.float16).astype(np.float32)).all()
+
+
 @pytest.mark.parametrize("tokens,K,N", [(70, 1024, 1024), (133, 256, 2560), (600, 256, 9728)])
 def test_gemm_with_add_and_norm_in_its_epilogue_bit_equal(cuda, tokens, K, N):
     """W4A16 GEMM -> residual ADD -> RMSNORM2 at GEMM row counts runs as the GEMM plus one kernel that adds
