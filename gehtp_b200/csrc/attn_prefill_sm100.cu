@@ -14,11 +14,12 @@
 // accumulator that an online softmax needs (O stays in TMEM untouched until the end).
 //
 // Operands: Q, K token-major (head_dim contiguous) are K-major for S = Q K^T; for O = P V the
-// contraction runs over key positions, so V is used transposed (V^T[head_dim][positions], written once
-// per call by a small transposition kernel into a scratch buffer) and P is written by the softmax
-// warps into shared memory in the 128-byte-swizzled K-major form tcgen05.mma reads.
+// contraction runs over key positions: V is read as it lies in memory ([position][head_dim]) and declared
+// an MN-major B operand (instruction descriptor bit 16; boxes of 64 positions x 64 head_dim values, see
+// umma_desc_v), and P is written by the softmax warps into shared memory in the 128-byte-swizzled K-major
+// form tcgen05.mma reads.
 //
-//   warp 0     TMA producer: Q once, then K tiles (both passes) and V^T tiles (pass 2), 2-stage rings
+//   warp 0     TMA producer: Q once, then K tiles (both passes) and V tiles (pass 2), 2-stage rings
 //   warp 1     one lane issues tcgen05.mma / tcgen05.commit
 //   warp 2     owns the TMEM allocation (512 columns: two S buffers, O)
 //   warps 4-11 softmax: warp w works on TMEM lanes 32 (w % 4) .. +31 (one query row per thread) and on
@@ -153,9 +154,22 @@ __device__ __forceinline__ bool tile_zero(const uint8_t* zero, uint32_t qt, uint
     return true;
 }
 
+// B-operand descriptor of a V tile as it lies in memory ([position][head_dim], head_dim contiguous = "MN-major"):
+// boxes of 64 positions x 64 head_dim values (128-byte rows, 128-byte swizzle); 8-position groups 1024 bytes
+// apart (stride byte offset), the second head_dim half 8192 bytes further (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_v(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(8192 >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                          const __grid_constant__ CUtensorMap tmap_vt, const SmArgs A) {
+                          const __grid_constant__ CUtensorMap tmap_v, const SmArgs A) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;                          // 2 boxes (head_dim halves)
@@ -228,8 +242,11 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
                         const uint32_t s = iv & 1, ph = (iv >> 1) & 1;
                         if (!mbar_wait(&bars->v_empty[s], ph ^ 1)) { *abort_flag = 1; break; }
                         mbar_expect_tx(&bars->v_full[s], 2 * TILE_BYTES);
-                        tma_load_2d(sV + s * 2 * TILE_BYTES, &tmap_vt, (int)(kt * BKV), (int)(kvhd * HD), &bars->v_full[s]);
-                        tma_load_2d(sV + s * 2 * TILE_BYTES + TILE_BYTES, &tmap_vt, (int)(kt * BKV + 64), (int)(kvhd * HD), &bars->v_full[s]);
+                        // [position half][head_dim half][64 positions x 128 bytes]
+#pragma unroll
+                        for (uint32_t b4 = 0; b4 < 4; b4++)
+                            tma_load_2d(sV + s * 2 * TILE_BYTES + b4 * (TILE_BYTES / 2), &tmap_v, (int)(kvhd * HD + (b4 & 1) * 64),
+                                        (int)(kt * BKV + (b4 >> 1) * 64), &bars->v_full[s]);
                         iv++;
                     }
                 }
@@ -280,8 +297,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
                 for (uint32_t kb = 0; kb < 2; kb++)
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < 4; k4++)
+                        // 16 positions = two 8-position groups = 2048 bytes per step; bit 16: B is MN-major
                         umma_f16(tm_o, umma_desc(p_base + kb * TILE_BYTES) + (uint64_t)(k4 * 2),
-                                 umma_desc(v_base + s * 2 * TILE_BYTES + kb * TILE_BYTES) + (uint64_t)(k4 * 2), idesc_f16(128), (j | kb | k4) ? 1u : 0u);
+                                 umma_desc_v(v_base + s * 2 * TILE_BYTES + kb * TILE_BYTES + k4 * 2048), idesc_f16(128) | (1u << 16), (j | kb | k4) ? 1u : 0u);
                 umma_commit(&bars->v_empty[s]);
                 umma_commit(&bars->p_empty);
             }
@@ -428,29 +446,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     }
 }
 
-// vt[c][r] = v[r][c], v [rows][cols] -> vt [cols][ld]
-__global__ void transpose_f16_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt, uint32_t rows, uint32_t cols, uint32_t ld) {
-    __shared__ uint16_t tile[32][33];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-    for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
-        const uint32_t r = r0 + i, c = c0 + threadIdx.x;
-        tile[i][threadIdx.x] = (r < rows && c < cols) ? v[(size_t)r * cols + c] : (uint16_t)0;
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
-        const uint32_t c = c0 + i, r = r0 + threadIdx.x;
-        if (c < cols && r < ld) vt[(size_t)c * ld + r] = tile[threadIdx.x][i];
-    }
-}
-
-bool make_map(CUtensorMap* tm, const uint16_t* base, uint64_t inner, uint64_t rows, uint64_t row_stride_elems) {
+bool make_map(CUtensorMap* tm, const uint16_t* base, uint64_t inner, uint64_t rows, uint64_t row_stride_elems, uint32_t box_rows = 128) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
     cuuint64_t dims[2] = {inner, rows};
     cuuint64_t strides[1] = {row_stride_elems * 2};
-    cuuint32_t box[2] = {64, 128};
+    cuuint32_t box[2] = {64, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -458,37 +459,27 @@ bool make_map(CUtensorMap* tm, const uint16_t* base, uint64_t inner, uint64_t ro
 
 }  // namespace
 
-size_t attn_prefill_sm100_scratch_bytes(uint32_t seq_k, uint32_t kvh, uint32_t hd) {
-    return (size_t)kvh * hd * ((seq_k + 7) / 8 * 8) * 2;
-}
-
-// `vt_scratch`: attn_prefill_sm100_scratch_bytes(seq_k, kvh, hd) bytes of device memory (V transposed lives there for
-// the duration of the call). false: shape not taken (head_dim other than 128, unaligned operands); nothing launched.
+// false: shape not taken (head_dim other than 128, more than 8192 key positions, unaligned operands, scale <= 0);
+// nothing launched.
 bool k_attn_prefill_sm100(cudaStream_t st, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* mask,
                           size_t mask_head_stride, const uint8_t* skip, const uint8_t* zero, float scale, int scale_div, uint32_t seq_q,
-                          uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out, uint16_t* vt_scratch,
-                          unsigned int* status) {
-    if (hd != 128 || !seq_q || !seq_k || seq_k > 64 * BKV || !kvh || nh % kvh || !vt_scratch) return false;
-    if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out) | ((uintptr_t)vt_scratch)) & 15u) return false;
-    const uint32_t ld = (seq_k + 7) / 8 * 8;
+                          uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out, unsigned int* status) {
+    if (hd != 128 || !seq_q || !seq_k || seq_k > 64 * BKV || !kvh || nh % kvh) return false;
+    if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)out)) & 15u) return false;
+    if (scale <= 0.0f) return false;      // the row maximum is taken before the scale: the scale must keep the order
     CUtensorMap tq, tk, tv;
     if (!make_map(&tq, q, (uint64_t)nh * hd, seq_q, (uint64_t)nh * hd) || !make_map(&tk, k, (uint64_t)kvh * hd, seq_k, (uint64_t)kvh * hd) ||
-        !make_map(&tv, vt_scratch, seq_k, (uint64_t)kvh * hd, ld))
+        !make_map(&tv, v, (uint64_t)kvh * hd, seq_k, (uint64_t)kvh * hd, 64))
         return false;
     const size_t smem = 1024 + 12 * (size_t)TILE_BYTES + sizeof(ABars) + 16;
     static int have[64] = {};
     if (!ensure_dyn_smem(attn_prefill_sm100_kernel, smem, have)) return false;
-    if (launch_pdl(transpose_f16_kernel, dim3((kvh * hd + 31) / 32, (ld + 31) / 32), dim3(32, 8), 0, st, v, vt_scratch, seq_k, kvh * hd, ld) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    if (scale <= 0.0f) return false;      // the row maximum is taken before the scale: the scale must keep the order
     SmArgs a{mask, mask_head_stride, skip, zero, out, seq_q, seq_k, nh, kvh, scale, scale_div, status};
     if (launch_pdl(attn_prefill_sm100_kernel, dim3((seq_q + BQ - 1) / BQ, nh), dim3(NTHREADS), smem, st, tq, tk, tv, a) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    g_launches += 2;
+    g_launches++;
     return true;
 }
 

@@ -429,7 +429,6 @@ bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
 
 std::vector<Span> g_spans;
 float* g_attn_scratch = nullptr;
-uint16_t* g_vt_scratch = nullptr;     // V transposed, for the tcgen05 prefill attention (largest span of the plan)
 std::map<std::pair<uint32_t, uint64_t>, uint8_t*> g_skip_maps;   // (mask slot, S<<32|Sk) -> device tile-skip bitmap
 
 const uint8_t* resolve(const wt_blob* b, uint32_t arg) {
@@ -551,10 +550,6 @@ void fuse_materialize(const wt_blob* b) {
     if (scratch_floats) {
         if (cudaMalloc(&g_attn_scratch, scratch_floats * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return; }
     }
-    size_t vt_bytes = 0;
-    for (const Span& sp : g_spans)
-        if (sp.kind == 4 && sp.hd == 128) vt_bytes = std::max(vt_bytes, attn_prefill_sm100_scratch_bytes(sp.N, sp.kvh, sp.hd));
-    if (vt_bytes && cudaMalloc(&g_vt_scratch, vt_bytes) != cudaSuccess) { cudaGetLastError(); g_vt_scratch = nullptr; }
     g.fused_ops = 0;
     for (const Span& sp : g_spans) {
         PlanOp& head = g.plan[sp.first];
@@ -704,12 +699,11 @@ void fuse_materialize(const wt_blob* b) {
             }
             float scale = sp.scale; int sdiv = sp.scale_div;
             if ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v)) & 15u) continue;
-            uint16_t* vt = g_vt_scratch;
             unsigned int* status = g.d_status;
             static const int sm100_on = [] { const char* e = std::getenv("GEHTP_CUDA_PREFILL_SM100"); return e ? std::atoi(e) : 1; }();
             head.fused = [=](cudaStream_t st) {
                 // head_dim 128: tcgen05 / TMEM form; anything it does not take goes to the mma.sync form
-                if (sm100_on && vt && k_attn_prefill_sm100(st, q, k, v, mask, mstride, skip, zero, scale, sdiv, sq, sk, nh, kvh, hd, out, vt, status)) return;
+                if (sm100_on && k_attn_prefill_sm100(st, q, k, v, mask, mstride, skip, zero, scale, sdiv, sq, sk, nh, kvh, hd, out, status)) return;
                 k_attn_prefill(st, q, k, v, mask, mstride, skip, scale, sdiv, sq, sk, nh, kvh, hd, out);
             };
         } else {
@@ -783,7 +777,6 @@ bool fuse_all_materialized() {
 
 void fuse_release() {
     if (g_attn_scratch) { cudaFree(g_attn_scratch); g_attn_scratch = nullptr; }
-    if (g_vt_scratch) { cudaFree(g_vt_scratch); g_vt_scratch = nullptr; }
     for (auto& kv : g_skip_maps) cudaFree(kv.second);
     g_skip_maps.clear();
     g_spans.clear();

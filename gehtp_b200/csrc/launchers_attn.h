@@ -52,13 +52,12 @@ bool k_attn_prefill(cudaStream_t st, const uint16_t* q, const uint16_t* k, const
                     uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out);
 uint32_t attn_prefill_tile();
 // The same on tcgen05 / TMEM for head_dim 128 (attn_prefill_sm100.cu): 128 x 128 tiles, two passes (row statistics,
-// then P V). `skip` has the 64 x 64 granularity of k_attn_prefill; `zero` (same shape, may be NULL) marks tiles whose mask is +0 everywhere. `vt_scratch`: attn_prefill_sm100_scratch_bytes(...)
-// bytes of device memory that hold V transposed during the call. false: shape not taken, nothing launched.
-size_t attn_prefill_sm100_scratch_bytes(uint32_t seq_k, uint32_t kvh, uint32_t hd);
+// then P V). `skip` has the 64 x 64 granularity of k_attn_prefill; `zero` (same shape, may be NULL) marks tiles whose
+// mask is +0 everywhere. false: shape not taken, nothing launched.
 bool k_attn_prefill_sm100(cudaStream_t st, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* mask,
                           size_t mask_head_stride, const uint8_t* skip, const uint8_t* zero, float scale, int scale_div,
                           uint32_t seq_q, uint32_t seq_k, uint32_t nh, uint32_t kvh, uint32_t hd, uint16_t* out,
-                          uint16_t* vt_scratch, unsigned int* status);
+                          unsigned int* status);
 // rotary embedding, split-half form, with the op chain's roundings: out = f16(f16(x*cos) + f16(rot(x)*sin))
 void k_rope(cudaStream_t st, const uint16_t* x, const uint16_t* cos_t, const uint16_t* sin_t, uint16_t* out,
             uint32_t rows, uint32_t hd);
