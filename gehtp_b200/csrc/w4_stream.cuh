@@ -91,16 +91,23 @@ __device__ __forceinline__ uint16_t swiglu_chain(float gate_acc, float up_acc) {
 }
 
 // Two SwiGLU chains at once, packed: the same roundings through half2 conversions and fp16 multiplies (the fp32
-// product of two fp16 values is exact, so one rounding to fp16 either way). A NaN anywhere in a chain reaches the
-// result as a NaN; those pairs are redone by swiglu_chain, whose conversions turn a NaN into a signed infinity.
-__device__ __forceinline__ uint32_t swiglu_chain2(float g0, float g1, float u0, float u1) {
+// product of two fp16 values is exact, so one rounding to fp16 either way; 1 / x as the correctly rounded reciprocal
+// is the IEEE quotient 1.0f / x). No branch, so that a caller's independent pairs overlap their latencies. A NaN
+// anywhere in a chain reaches the result as a NaN: `nan` is set then, and the caller redoes such pairs with
+// swiglu_chain, whose conversions turn a NaN into a signed infinity.
+__device__ __forceinline__ uint32_t swiglu_pair_fast(float g0, float g1, float u0, float u1, bool& nan) {
     const __half2 gh = __floats2half2_rn(g0, g1);
     const float2 gf = __half22float2(gh);
-    const __half2 sh = __floats2half2_rn(1.0f / (1.0f + expf(-gf.x)), 1.0f / (1.0f + expf(-gf.y)));
+    const __half2 sh = __floats2half2_rn(__frcp_rn(1.0f + expf(-gf.x)), __frcp_rn(1.0f + expf(-gf.y)));
     const __half2 out = __hmul2(__hmul2(gh, sh), __floats2half2_rn(u0, u1));
-    if (__hisnan(__low2half(out)) || __hisnan(__high2half(out)))
-        return (uint32_t)swiglu_chain(g0, u0) | ((uint32_t)swiglu_chain(g1, u1) << 16);
+    nan |= __hisnan(__low2half(out)) || __hisnan(__high2half(out));
     return *(const uint32_t*)&out;
+}
+
+__device__ __forceinline__ uint32_t swiglu_chain2(float g0, float g1, float u0, float u1) {
+    bool nan = false;
+    const uint32_t r = swiglu_pair_fast(g0, g1, u0, u1, nan);
+    return nan ? ((uint32_t)swiglu_chain(g0, u0) | ((uint32_t)swiglu_chain(g1, u1) << 16)) : r;
 }
 
 }  // namespace gehtp

@@ -308,11 +308,20 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                         tmem_ld16(taddr + BN_OUT, vu);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (m < M) {
+                            // the 8 pairs without a branch between them (their latencies overlap); a NaN in any of them
+                            // sends all 8 through the form that redoes the conversions one by one
                             uint32_t o[8];
+                            bool nan = false;
 #pragma unroll
                             for (int q = 0; q < 8; q++)
-                                o[q] = swiglu_chain2(__uint_as_float(vg[2 * q]), __uint_as_float(vg[2 * q + 1]), __uint_as_float(vu[2 * q]),
-                                                     __uint_as_float(vu[2 * q + 1]));
+                                o[q] = swiglu_pair_fast(__uint_as_float(vg[2 * q]), __uint_as_float(vg[2 * q + 1]), __uint_as_float(vu[2 * q]),
+                                                        __uint_as_float(vu[2 * q + 1]), nan);
+                            if (nan) {
+#pragma unroll
+                                for (int q = 0; q < 8; q++)
+                                    o[q] = swiglu_chain2(__uint_as_float(vg[2 * q]), __uint_as_float(vg[2 * q + 1]), __uint_as_float(vu[2 * q]),
+                                                         __uint_as_float(vu[2 * q + 1]));
+                            }
                             uint4* dst = (uint4*)(y + (size_t)m * N + n0 + c * 16);     // 32-byte aligned: N and n0 are multiples of 128
                             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
                             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);

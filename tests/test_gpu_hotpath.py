@@ -392,6 +392,45 @@ def test_gate_up_gemm_edge_shapes_bit_equal(cuda, M, K, F):
     assert np.isfinite(res[0][0].view(np.float16).astype(np.float32)).all()
 
 
+def test_gate_up_gemm_epilogue_on_every_fp16_gate_value(cuda):
+    """The SwiGLU epilogue of the gate | up GEMM forms its roundings on packed pairs (half2 conversions and
+    multiplies, a correctly rounded reciprocal, NaNs redone apart) where the ops it replaces work value by value. Row m of the activations carries the fp16 value with bit pattern m in its
+    first column and the weights pick it out (one weight 1.0 per column, the rest 0), so the 65536 rows put every fp16
+    value - subnormals, infinities and NaNs included - through the epilogue as the gate, with an up value that is the
+    gate itself in half of the columns and 60000 times the gate (mostly infinite) in the others: bit for bit the
+    op-by-op plan's result."""
+    from gehtp_b200.runlists import Emitter
+    M, K, F = 65536, 64, 128
+    nib = np.full((K, F // 2), 0x88, np.uint8)
+    nib[0, :] = 0x99                                   # (9 - 8) * scale in row 0 of every column
+    ones = np.ones((K // 64, F), np.float16)
+    up_scale = ones.copy()
+    up_scale[0, F // 2:] = np.float16(60000.0)         # second half of the columns: up = 60000 gate, infinite beyond |gate| = 1.09
+    e = Emitter("w4")
+    face = e.b.add_ext_in(M * K * 2)
+    rng = np.random.default_rng(9)
+    from gehtp_b200.runlists import rand_w4
+    d = e.swiglu(S(face), M, (nib, ones), (nib, up_scale), rand_w4(rng, F, 64))
+    act = d - 1
+    buf = e.b.build()
+    x = np.zeros((M, K), np.uint16)
+    x[:, 0] = np.arange(M, dtype=np.uint32).astype(np.uint16)
+    res = []
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        eng.run_io(x, d, None)
+        res.append(eng.temp(act, np.uint16).copy())
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    assert res[0].size == M * F and np.array_equal(res[0], res[1])
+    got = res[0].reshape(M, F)
+    g = x[:, 0].view(np.float16).astype(np.float64)
+    ok = np.isfinite(g) & (np.abs(g) < 100)
+    want = g[ok] / (1.0 + np.exp(-g[ok])) * g[ok]
+    assert_fp16_close(got[ok, 0].view(np.float16), want.astype(np.float16), "silu(g) * g")
+
+
 @pytest.mark.parametrize("tokens,K,N", [(70, 1024, 1024), (133, 256, 2560), (600, 256, 9728)])
 def test_gemm_with_add_and_norm_in_its_epilogue_bit_equal(cuda, tokens, K, N):
     """W4A16 GEMM -> residual ADD -> RMSNORM2 at GEMM row counts runs as the GEMM plus one kernel that adds
