@@ -43,6 +43,9 @@ struct PlanOp {
     uint32_t stat = 0;          // index into the stats struct, 0 = none
     bool uses_internal = false; // touches a temp that has no memory in a fused plan
     bool dead_when_fused = false;   // its result is read only by ops that fused chains replace: skipped in whole fused runs
+    // a data-movement op whose inputs are weight slots (or results of such ops) and whose output nobody else writes:
+    // its result is a constant of the blob, made by the first run that reaches it and kept
+    bool const_fold = false, const_done = false;
 };
 
 struct W4Packed {
@@ -97,6 +100,7 @@ struct Engine {
 
     std::vector<PlanOp> plan;
     uint32_t fused_ops = 0;
+    uint32_t const_ops = 0;       // ops of the current plan whose result is made once (const_fold)
     uint32_t demoted_temps = 0;
 
     // I/O staging
@@ -166,6 +170,9 @@ bool tp_p2p_add_rmsnorm(cudaStream_t st, const uint16_t* a, uint16_t* r, const u
 // fuse.cu
 void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector<uint8_t>& internal, std::vector<uint8_t>& dead);
 void fuse_materialize(const wt_blob* b);
+// Marks the ops whose result is a constant of the blob (PlanOp::const_fold). addr / maxb: device address and capacity
+// of every temp id of the plan.
+void fold_constants(const wt_blob* b, uint8_t* const* addr, const uint64_t* maxb);
 bool fuse_all_materialized();
 void fuse_release();
 

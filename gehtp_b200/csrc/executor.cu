@@ -197,6 +197,8 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
     const int64_t t_run0 = now_us();
     const bool hooks = hooks_active();
     std::vector<PlanOp*> pending;
+    cudaStreamCaptureStatus cap_state = cudaStreamCaptureStatusNone;
+    const bool capturing = cudaStreamIsCapturing(g.stream, &cap_state) != cudaSuccess || cap_state != cudaStreamCaptureStatusNone;
     if (hooks) fuse = false;   // dumps need every intermediate temp
     g.exact_ops = hooks;
     for (uint32_t ii = 0; ii < count;) {
@@ -229,7 +231,12 @@ static int queue_range(uint32_t first, uint32_t count, bool fuse, bool per_op_sy
             }
             if (!rc) {
                 if (use_fused) p.fused(g.stream);
-                else for (PlanOp* q : pending) if (q->launch && !(g.skip_dead && q->dead_when_fused)) q->launch(g.stream);
+                else for (PlanOp* q : pending) {
+                    if (!q->launch || (g.skip_dead && q->dead_when_fused)) continue;
+                    if (q->const_fold && q->const_done) continue;        // a constant of the blob, made by an earlier run
+                    q->launch(g.stream);
+                    if (q->const_fold && !capturing) q->const_done = true;   // inside a capture the launch has not run yet
+                }
             }
             if (ev1) cudaEventRecord(ev1, g.stream);
             pending.clear();
@@ -613,6 +620,7 @@ void gehtp_cuda_set_graph(int on) {
 }
 uint64_t gehtp_cuda_launch_count(void) { return g_launches; }
 uint32_t gehtp_cuda_fused_ops(void) { return g.fused_ops; }
+uint32_t gehtp_cuda_const_ops(void) { return g.const_ops; }
 uint32_t gehtp_cuda_demoted_temps(void) { return g.demoted_temps; }
 void* gehtp_cuda_stream(void) { return ensure_device(nullptr, 0) ? (void*)g.stream : nullptr; }
 void* gehtp_cuda_temp_dev(uint32_t id) { return (id < kMaxTemps && g.temp_cap[id]) ? g.temp_dev[id] : nullptr; }

@@ -769,6 +769,73 @@ void fuse_materialize(const wt_blob* b) {
     }
 }
 
+// Constant results. Compiled runlists slice, transpose and broadcast tables that live in weight slots (rotary tables,
+// masks, per-chunk windows of a constant tensor) with one op per ONNX node; such an op gives the same bytes on every
+// run. It is marked when: it only moves data; every tensor it reads is a weight slot with data in the blob or the
+// result of a marked op; it is the only writer of its output temp; that temp's memory overlaps no other temp's; and the
+// runlist has none of the memory-planner ops (SPILL, FILL, DMA: they write slots and parts of temps) and no static
+// temp table (aliased temps). The first eager run that reaches a marked op executes it, later runs - and the
+// captured graph - skip it.
+void fold_constants(const wt_blob* b, uint8_t* const* addr, const uint64_t* maxb) {
+    g.const_ops = 0;
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        const uint32_t oc = b->ops[i].opcode;
+        if (oc == OP_SPILL || oc == OP_FILL || oc == OP_DMA) return;
+    }
+    for (uint32_t s = 0; s < b->n_slots; s++)
+        if (b->slots[s].addr == WT_SLOT_TEMPOFF) return;
+    std::vector<int> writers(kMaxTemps, 0);
+    std::vector<uint8_t> in_span(b->n_ops, 0), const_temp(kMaxTemps, 0);
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        const PlanOp& p = g.plan[i];
+        for (int k = 0; k < 2; k++)
+            if (p.out_id[k] != kNoOff && p.out_id[k] < kMaxTemps) writers[p.out_id[k]]++;
+        if (p.fused && p.span)
+            for (uint32_t k = 0; k < p.span && i + k < b->n_ops; k++) in_span[i + k] = 1;
+    }
+    auto plain_slot = [&](uint32_t s) {
+        if (s >= b->n_slots || !b->slots[s].len) return false;
+        const uint64_t a = b->slots[s].addr;
+        return a != WT_SLOT_EXT_IN && a != WT_SLOT_EXT_OUT && a != WT_SLOT_TEMPOFF && a != WT_SLOT_EXT_WGT && a != WT_SLOT_STATE;
+    };
+    for (uint32_t i = 0; i < b->n_ops; i++) {
+        PlanOp& p = g.plan[i];
+        const wt_op& op = b->ops[i];
+        if (p.rc || !p.launch || in_span[i] || p.uses_internal) continue;
+        switch (op.opcode) {
+        case OP_STRIDED_SLICE_F16: case OP_TRANSPOSE_GEN_F16: case OP_TRANSPOSE_F16: case OP_BROADCAST_F16: case OP_CONCAT_F16:
+        case OP_SPLIT_F16: case OP_PAD_F16:
+            break;
+        default:
+            continue;
+        }
+        int ia[8];
+        const int n = input_args(op, ia);
+        bool ok = n > 0;
+        for (int k = 0; k < n && ok; k++) {
+            const uint32_t a = op.args[ia[k]];
+            if ((a & 0xC000u) == 0x8000u) ok = plain_slot(a & 0x7FFFu);
+            else ok = is_temp_ref(a) && const_temp[a];
+        }
+        int outs = 0;
+        for (int k = 0; k < 2 && ok; k++) {
+            const uint32_t id = p.out_id[k];
+            if (id == kNoOff) continue;
+            outs++;
+            if (id >= kMaxTemps || writers[id] != 1 || !addr[id] || !maxb[id]) { ok = false; break; }
+            const uint8_t *lo = addr[id], *hi = lo + maxb[id];
+            for (uint32_t t = 0; t < kMaxTemps && ok; t++)
+                if (t != id && addr[t] && maxb[t] && addr[t] < hi && lo < addr[t] + maxb[t]) ok = false;
+        }
+        if (!ok || !outs) continue;
+        p.const_fold = true;
+        p.const_done = false;
+        for (int k = 0; k < 2; k++)
+            if (p.out_id[k] != kNoOff) const_temp[p.out_id[k]] = 1;
+        g.const_ops++;
+    }
+}
+
 bool fuse_all_materialized() {
     for (const Span& sp : g_spans)
         if (!g.plan[sp.first].fused || g.plan[sp.first].span != sp.count) return false;

@@ -20,8 +20,8 @@
 // product through registers and a rounding); the chain is latency bound, and mma.sync keeps every
 // intermediate in registers on its way to the next operand.
 //
-// Grid (H, 4): the value dimension m is split over four CTAs per head (b, u, y and the rows of S
-// are independent across m); L, T and the q.k matrix are recomputed by each of them.
+// Grid (H, D / 16): the value dimension m is split into slices of 16 rows, one CTA each (b, u, y and the rows
+// of S are independent across m); L, T and the q.k matrix are recomputed by each of them.
 #include "common.cuh"
 #include "launchers.h"
 #include "w4_stream.cuh"
@@ -56,14 +56,15 @@ __device__ __forceinline__ void split_store(uint16_t* hi, uint16_t* lo, float x)
     *lo = f2h(x - h2f(h));
 }
 
-template <int D>
+template <int D, int NQ>
 __global__ void __launch_bounds__(256)
 delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, const uint16_t* __restrict__ q,
                        const uint16_t* __restrict__ beta, const uint16_t* __restrict__ gl, uint16_t* __restrict__ y,
                        float* __restrict__ Sg, int c, int ntok, int q_raw) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    constexpr int DM = D / 4, DP = D + 8;
+    constexpr int DM = D / NQ, DP = D + 8;
+    static_assert(DM % 16 == 0, "a CTA owns whole 16-row tiles of the state");
     extern __shared__ __align__(16) unsigned char smem[];
     uint16_t* Kh = (uint16_t*)smem;                 // [C][DP]   k
     uint16_t* Qh = Kh + C * DP;                     // [C][DP]   q (unscaled)
@@ -279,14 +280,14 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     }
 }
 
-template <int D>
+template <int D, int NQ>
 bool launch(cudaStream_t st, const uint16_t* k, const uint16_t* v, const uint16_t* q, const uint16_t* beta, const uint16_t* g,
             uint16_t* y, float* S, uint32_t c, uint32_t ntok, uint32_t H, uint32_t q_raw) {
     static int have[64];
-    constexpr int DM = D / 4, DP = D + 8;
+    constexpr int DM = D / NQ, DP = D + 8;
     const size_t smem = (size_t)(2 * C * DP + D * CP + 2 * DM * DP + 6 * DM * CP + 5 * C * CP + 3 * 768) * 2 + 4 * C * sizeof(float);
-    if (!ensure_dyn_smem(delta_chunk_mma_kernel<D>, smem, have)) return false;
-    launch_pdl(delta_chunk_mma_kernel<D>, dim3(dim3(H, 4)), dim3(256), smem, st, k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)q_raw);
+    if (!ensure_dyn_smem(delta_chunk_mma_kernel<D, NQ>, smem, have)) return false;
+    launch_pdl(delta_chunk_mma_kernel<D, NQ>, dim3(dim3(H, NQ)), dim3(256), smem, st, k, v, q, beta, g, y, S, (int)c, (int)ntok, (int)q_raw);
     g_launches++;
     return true;
 }
@@ -298,8 +299,9 @@ bool k_delta_chunk_mma(cudaStream_t st, const uint16_t* k, const uint16_t* v, co
                        const uint16_t* g, uint16_t* y, float* S, uint32_t c, uint32_t ntok, uint32_t H, uint32_t D, uint32_t q_raw) {
     if (!c || c > 64 || c > ntok || !H) return false;
     if ((((uintptr_t)k) | ((uintptr_t)q) | ((uintptr_t)S)) & 15u) return false;
-    if (D == 128) return launch<128>(st, k, v, q, beta, g, y, S, c, ntok, H, q_raw);
-    if (D == 64) return launch<64>(st, k, v, q, beta, g, y, S, c, ntok, H, q_raw);
+    // the value dimension in slices of 16 rows per CTA: 8 CTAs per head at 128, 4 at 64
+    if (D == 128) return launch<128, 8>(st, k, v, q, beta, g, y, S, c, ntok, H, q_raw);
+    if (D == 64) return launch<64, 4>(st, k, v, q, beta, g, y, S, c, ntok, H, q_raw);
     return false;
 }
 

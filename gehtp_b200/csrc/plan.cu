@@ -894,11 +894,13 @@ int build_plan(const wt_blob* b, char* err, size_t errn) {
     for (uint32_t i = 0; i < kMaxTemps; i++) g.temp_dev[i] = P.addr[i];
 
     g.fused_ops = 0;
+    g.const_ops = 0;
     if (fusing) {
         fuse_materialize(b);
         // only when every chain really got its kernel: a chain left op-by-op still reads those results
         if (fuse_all_materialized())
             for (uint32_t i = 0; i < b->n_ops && i < dead_ops.size(); i++) g.plan[i].dead_when_fused = dead_ops[i] != 0;
+        fold_constants(b, P.addr, P.maxb);
     }
     cudaError_t ce = cudaStreamSynchronize(g.stream);
     if (ce != cudaSuccess) { std::snprintf(err, errn, "plan upload: %s", cudaGetErrorString(ce)); return -1; }

@@ -196,6 +196,7 @@ def bind(lib):
     if hasattr(lib, "gehtp_cuda_launch_count"):
         lib.gehtp_cuda_launch_count.restype = c.c_uint64
         lib.gehtp_cuda_fused_ops.restype = c.c_uint32
+        lib.gehtp_cuda_const_ops.restype = c.c_uint32
         lib.gehtp_cuda_demoted_temps.restype = c.c_uint32
         lib.gehtp_cuda_stream.restype = c.c_void_p
         lib.gehtp_cuda_temp_dev.argtypes = [c.c_uint32]

@@ -159,6 +159,9 @@ int gehtp_cuda_tp_p2p_loopback(int world);
 uint64_t gehtp_cuda_launch_count(void);
 /* Number of ops of the current plan replaced by fused launches. */
 uint32_t gehtp_cuda_fused_ops(void);
+/* Number of ops of the current plan whose result is a constant of the blob (data movement over weight slots:
+ * slices, transposes, broadcasts of tables): executed by the first run that reaches them, skipped afterwards. */
+uint32_t gehtp_cuda_const_ops(void);
 /* Number of TEMPOFF entries of the current plan that were moved out of the
  * static pool because their byte ranges overlap another entry's while both
  * tensors are live (the emitter binds plan offsets to recycled temp ids,

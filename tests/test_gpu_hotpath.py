@@ -392,6 +392,45 @@ def test_gate_up_gemm_edge_shapes_bit_equal(cuda, M, K, F):
     assert np.isfinite(res[0][0].view(np.float16).astype(np.float32)).all()
 
 
+def test_constant_ops_run_once(cuda):
+    """A slice of a table that lives in a weight slot and a transposition of that slice give the same bytes on every
+    run: the fused engine executes them on the first run and skips them afterwards (also in the captured graph); a
+    slice of the input face next to them is not a constant. Results equal the one-kernel-per-op engine's on every run."""
+    from gehtp_b200.runlists import Emitter
+    rng = np.random.default_rng(12)
+    e = Emitter("w4")
+    n = 8 * 16
+    face = e.b.add_ext_in(2 * n * 2)
+    table = e.b.add_slot(rng.standard_normal((8, 32)).astype(np.float16))
+    win = e.slice2(S(table), 8, 32, 8, 24)                  # constant: [8][16]
+    win_t = e.transpose3(win, (1, 8, 16), (0, 2, 1))        # constant through its input: [16][8]
+    x = e.face(S(face), n, n, 2 * n)                        # second half of the input: not a constant
+    y = e.binary(win_t, x, n, 0)
+    buf = e.b.build()
+    inputs = [rng.standard_normal(2 * n).astype(np.float16) for _ in range(4)]
+    outs = {}
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        res, launches = [], []
+        for inp in inputs:
+            before = cuda.gehtp_cuda_launch_count()
+            eng.run_io(inp, y, None)
+            launches.append(cuda.gehtp_cuda_launch_count() - before)
+            res.append(eng.temp(y, np.uint16).copy())
+        if fusion:
+            assert cuda.gehtp_cuda_const_ops() == 2
+            assert launches[0] == 4 and launches[1] == 2 and launches[3] == 2, launches
+        else:
+            assert cuda.gehtp_cuda_const_ops() == 0 and launches == [4, 4, 4, 4], launches
+        outs[fusion] = res
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    for a, b2 in zip(outs[1], outs[0]):
+        assert a.size == n and np.array_equal(a, b2)
+    assert not np.array_equal(outs[1][0], outs[1][1])
+
+
 def test_gate_up_gemm_epilogue_on_every_fp16_gate_value(cuda):
     """The SwiGLU epilogue of the gate | up GEMM forms its roundings on packed pairs (half2 conversions and
     multiplies, a correctly rounded reciprocal, NaNs redone apart) where the ops it replaces work value by value. Row m of the activations carries the fp16 value with bit pattern m in its
