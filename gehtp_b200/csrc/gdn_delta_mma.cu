@@ -14,8 +14,8 @@
 //     into hi = f16(x) and lo = f16(x - hi) and multiplied as hi + lo (two or three MMAs), which
 //     carries about 22 bits of mantissa: fp32-class, the state does not degrade over the chunks;
 //   * T = (I + L)^-1: the reference's row-by-row forward substitution inside 16 x 16 diagonal blocks (column j
-//     depends on column j only: four lanes own a column, shuffles, no block-wide barrier), block forward
-//     substitution on the tensor cores below the diagonal.
+//     depends on column j only: one lane owns a column, its entries in registers, no block-wide barrier), block
+//     forward substitution on the tensor cores below the diagonal.
 // The products are far too small for tcgen05 tiles (M = 64 or 32 rows, each result feeds the next
 // product through registers and a rounding); the chain is latency bound, and mma.sync keeps every
 // intermediate in registers on its way to the next operand.
@@ -100,51 +100,85 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
     const float scale = q_raw ? 1.0f : 1.0f / sqrtf((float)D);
 
     // ---- stage 0: operands into shared memory
-    if (warp == 0) {
-        // running sum of g over the chunk, in token order (a warp scan would add in another order)
-        for (int i = lane; i < C; i += 32) G[i] = i < c ? h2f(gh[i]) : 0.0f;
-        __syncwarp();
-        if (lane == 0) {
-            float acc = 0.0f;
-            for (int i = 0; i < C; i++) { acc += G[i]; G[i] = acc; }
-        }
-        __syncwarp();
-        for (int i = lane; i < C; i += 32) {
-            bj[i] = i < c ? h2f(bh[i]) : 0.0f;
-            eG[i] = expf(G[i]);
-            wd[i] = expf(G[c - 1] - G[i]);
-        }
-    }
-    for (int e = tid; e < C * (D / 8); e += 256) {
-        const int r = e / (D / 8), n8 = (e % (D / 8)) * 8;
-        uint4 kv = make_uint4(0, 0, 0, 0), qv = make_uint4(0, 0, 0, 0);
-        if (r < c) { kv = *(const uint4*)(kh + (size_t)r * D + n8); qv = *(const uint4*)(qh + (size_t)r * D + n8); }
-        *(uint4*)(Kh + r * DP + n8) = kv;
-        *(uint4*)(Qh + r * DP + n8) = qv;
-        const uint16_t* ke = (const uint16_t*)&kv;
+    {
+        // every global load of the thread is requested before the first one is used (one round trip, not one per step);
+        // a warp takes 32 consecutive rows of one 8-column group: the 16-bit stores of the transposed copy then fall on
+        // consecutive addresses (taken along a row they hit one bank 16 times over)
+        constexpr int KQ_STEPS = C * (D / 8) / 256, S_STEPS = DM * (D / 4) / 256;
+        static_assert(C * (D / 8) % 256 == 0 && DM * (D / 4) % 256 == 0, "whole steps of the 256 threads");
+        uint4 kv[KQ_STEPS], qv[KQ_STEPS];
+        float4 sv[S_STEPS];
 #pragma unroll
-        for (int i = 0; i < 8; i++) Kt[(n8 + i) * CP + r] = ke[i];
-    }
-    for (int e = tid; e < DM * (D / 4); e += 256) {
-        const int r = e / (D / 4), n4 = (e % (D / 4)) * 4;
-        const float4 s = *(const float4*)(Sglob + (size_t)(m0 + r) * D + n4);
-        split_store(Shi + r * DP + n4, Slo + r * DP + n4, s.x);
-        split_store(Shi + r * DP + n4 + 1, Slo + r * DP + n4 + 1, s.y);
-        split_store(Shi + r * DP + n4 + 2, Slo + r * DP + n4 + 2, s.z);
-        split_store(Shi + r * DP + n4 + 3, Slo + r * DP + n4 + 3, s.w);
+        for (int u = 0; u < KQ_STEPS; u++) {
+            const int e = tid + u * 256, r = e % C, n8 = (e / C) * 8;
+            kv[u] = make_uint4(0, 0, 0, 0); qv[u] = make_uint4(0, 0, 0, 0);
+            if (r < c) { kv[u] = *(const uint4*)(kh + (size_t)r * D + n8); qv[u] = *(const uint4*)(qh + (size_t)r * D + n8); }
+        }
+#pragma unroll
+        for (int u = 0; u < S_STEPS; u++) {
+            const int e = tid + u * 256, r = e / (D / 4), n4 = (e % (D / 4)) * 4;
+            sv[u] = *(const float4*)(Sglob + (size_t)(m0 + r) * D + n4);
+        }
+        // (between the requests and their use: the scan of warp 0 runs while the loads are under way)
+        if (warp == 0) {
+            // running sum of g over the chunk, in token order (a warp scan would add in another order): every lane
+            // adds the 64 values up itself, from registers, and keeps the two sums that are its own
+            for (int i = lane; i < C; i += 32) wd[i] = i < c ? h2f(gh[i]) : 0.0f;      // wd as scratch for the raw values
+            __syncwarp();
+            float acc = 0.0f, mine0 = 0.0f, mine1 = 0.0f, last = 0.0f;
+#pragma unroll
+            for (int i = 0; i < C; i++) {
+                acc += wd[i];
+                if (i == lane) mine0 = acc;
+                if (i == lane + 32) mine1 = acc;
+                if (i == c - 1) last = acc;
+            }
+            __syncwarp();
+            G[lane] = mine0; G[lane + 32] = mine1;
+            eG[lane] = expf(mine0); eG[lane + 32] = expf(mine1);
+            wd[lane] = expf(last - mine0); wd[lane + 32] = expf(last - mine1);
+            for (int i = lane; i < C; i += 32) bj[i] = i < c ? h2f(bh[i]) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < KQ_STEPS; u++) {
+            const int e = tid + u * 256, r = e % C, n8 = (e / C) * 8;
+            *(uint4*)(Kh + r * DP + n8) = kv[u];
+            *(uint4*)(Qh + r * DP + n8) = qv[u];
+            const uint16_t* ke = (const uint16_t*)&kv[u];
+#pragma unroll
+            for (int i = 0; i < 8; i++) Kt[(n8 + i) * CP + r] = ke[i];
+        }
+#pragma unroll
+        for (int u = 0; u < S_STEPS; u++) {
+            const int e = tid + u * 256, r = e / (D / 4), n4 = (e % (D / 4)) * 4;
+            split_store(Shi + r * DP + n4, Slo + r * DP + n4, sv[u].x);
+            split_store(Shi + r * DP + n4 + 1, Slo + r * DP + n4 + 1, sv[u].y);
+            split_store(Shi + r * DP + n4 + 2, Slo + r * DP + n4 + 2, sv[u].z);
+            split_store(Shi + r * DP + n4 + 3, Slo + r * DP + n4 + 3, sv[u].w);
+        }
     }
     __syncthreads();
 
     // ---- stage 1 (with 3 and 5 below): L[j][i] = f16(exp(G_j - G_i) (k_j . k_i) beta_j) for i < j, else 0
-    for (int tile = warp; tile < (C / 16) * (C / 8); tile += 8) {
-        const int mi = tile / (C / 8), ni = tile % (C / 8);
+    // Only the 20 tiles of 16 x 8 that touch the lower triangle carry values (row block mi has 2 mi + 2 of them);
+    // they are numbered 0..19 and dealt out to the warps in turn, the other 12 are zero and filled apart.
+    auto lower_tile = [](int idx, int& mi, int& ni) { mi = idx < 2 ? 0 : idx < 6 ? 1 : idx < 12 ? 2 : 3; ni = idx - (mi * mi + mi); };
+    constexpr int LOWER = 20;
+    static_assert(C == 64, "the tile numbering above is that of a 64-row chunk");
+    for (int idx = warp; idx < LOWER; idx += 8) {
+        int mi, ni;
+        lower_tile(idx, mi, ni);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (ni * 8 < mi * 16 + 16) mma_rows(acc, Kh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
+        mma_rows(acc, Kh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int j = mi * 16 + g + (e >> 1) * 8, i = ni * 8 + 2 * t + (e & 1);
             Lh[j * CP + i] = i < j ? f2h(expf(G[j] - G[i]) * acc[e] * bj[j]) : (uint16_t)0;
         }
+    }
+    for (int e = tid; e < C * C; e += 256) {          // the tiles above: L = 0, QK = 0
+        const int r = e / C, i = e % C;
+        if (i >= ((r >> 4) + 1) * 16) { Lh[r * CP + i] = 0; QKhi[r * CP + i] = 0; QKlo[r * CP + i] = 0; }
     }
     // stages 3 and 5 need the operands only, not L or T: same phase, one barrier for the three
     // ---- stage 3: b[j][m] = beta_j (v[j][m] - e^{G_j} (S0 k_j)[m]), stored transposed as hi + lo
@@ -161,10 +195,11 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
         }
     }
     // ---- stage 5: QK[t][i] = exp(G_t - G_i) (q_t . k_i) for i <= t, as hi + lo
-    for (int tile = warp; tile < (C / 16) * (C / 8); tile += 8) {
-        const int mi = tile / (C / 8), ni = tile % (C / 8);
+    for (int idx = 7 - warp; idx < LOWER; idx += 8) {     // dealt out from the other end: a warp with 3 tiles of L gets 2 here
+        int mi, ni;
+        lower_tile(idx, mi, ni);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (ni * 8 < mi * 16 + 16) mma_rows(acc, Qh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
+        mma_rows(acc, Qh + mi * 16 * DP, DP, Kh + ni * 8 * DP, DP, D, g, t);
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int tt = mi * 16 + g + (e >> 1) * 8, i = ni * 8 + 2 * t + (e & 1);
@@ -175,25 +210,30 @@ delta_chunk_mma_kernel(const uint16_t* __restrict__ k, const uint16_t* __restric
 
     // ---- stage 2: T = (I + L)^-1 in fp16. Within a 16 x 16 diagonal block it is the forward substitution of the
     // reference, row by row with every entry rounded to fp16 before the next row uses it; column j depends on column j
-    // only, so four lanes own a column and run down the 16 rows with shuffles (all four diagonal blocks at once, no
-    // block-wide barrier). The blocks below the diagonal follow from (I + L) T = I block row by block row:
+    // only, so one lane owns a column and runs down the 16 rows (all four diagonal blocks at once, no block-wide
+    // barrier). The blocks below the diagonal follow from (I + L) T = I block row by block row:
     //     T_ik = -T_ii (sum_{k <= m < i} L_im T_mk)
     // two small products per block on the tensor cores (the inner sum as hi + lo), rounded to fp16 once.
     {
-        const int j = tid >> 2, part = tid & 3, r0 = (j >> 4) << 4;
-        for (int rr = 0; rr < 16; rr++) {
-            const int r = r0 + rr;
-            float s = 0.0f;
-            if (j < r)
-                for (int i = j + part; i < r; i += 4) s -= h2f(Lh[r * CP + i]) * h2f(Th[i * CP + j]);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (part == 0) {
-                const uint16_t tv = j <= r ? f2h((r == j ? 1.0f : 0.0f) + s) : (uint16_t)0;
-                Th[r * CP + j] = tv;
-                Tt[j * CP + r] = tv;
+        // One lane per column (64 lanes, two warps): the sum over i < r runs in i order, as the reference's
+        // solve_tri_f16 forms it, with the column's earlier entries in registers; the entries of L of a row are the
+        // same for all 16 columns of a block (broadcast reads that depend on nothing before them).
+        if (tid < C) {
+            const int j = tid, r0 = j & ~15, jl = j & 15;
+            float tc[16];
+#pragma unroll
+            for (int rr = 0; rr < 16; rr++) {
+                float s = 0.0f;
+#pragma unroll
+                for (int il = 0; il < rr; il++) {
+                    const float l = h2f(Lh[(r0 + rr) * CP + r0 + il]);
+                    if (il >= jl) s -= l * tc[il];
+                }
+                const uint16_t tv = jl <= rr ? f2h((rr == jl ? 1.0f : 0.0f) + s) : (uint16_t)0;
+                Th[(r0 + rr) * CP + j] = tv;
+                Tt[j * CP + r0 + rr] = tv;
+                tc[rr] = h2f(tv);
             }
-            __syncwarp();
         }
         for (int e = tid; e < C * C; e += 256) {     // blocks above the block diagonal
             const int r = e / C, jj = e % C;
