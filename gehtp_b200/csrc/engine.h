@@ -36,7 +36,8 @@ struct PlanOp {
     int kv_gather_state = -1;   // AUTO gather: host counter check
     uint32_t w4_m = 0;          // M of a W4A16 matmul (reported through engine_m)
     // a W4A16 matmul at GEMM row counts: the tcgen05 GEMM with an epilogue of the caller's (false: shape not taken)
-    std::function<bool(cudaStream_t, const W4Epilogue&)> launch_w4_gemm;
+    // `a_src` / `a_d` != 0: read the activations from a_src, stored [K / a_d][M][a_d], instead of the op's own operand
+    std::function<bool(cudaStream_t, const W4Epilogue&, const uint16_t* a_src, uint32_t a_d)> launch_w4_gemm;
     // fusion: when `fused` is set on op i, it replaces ops [i, i + span)
     std::function<void(cudaStream_t)> fused;
     uint32_t span = 0;

@@ -125,7 +125,8 @@ Rope match_rope(const Graph& G, int add_op) {
 
 struct Span {
     int kind;                // 0 decode attention, 1 swiglu, 2 add+norm, 3 rotary, 4 prefill attention,
-                             // 5 prefill split + rotary of q|k|v, 6 swiglu tail behind two GEMMs
+                             // 5 prefill split + rotary of q|k|v, 6 swiglu tail behind two GEMMs,
+                             // 7 [head][row][d] -> [row][head * d] transposition in front of a W4A16 GEMM
     uint32_t first, count;
     std::vector<uint32_t> ops;
     // attention
@@ -415,6 +416,25 @@ bool match_swiglu_tail(const Graph& G, uint32_t ip, Span& sp) {
     return true;
 }
 
+// TRANSPOSE_GEN of a [heads][rows][d] tensor to [rows][heads * d] whose only reader is the W4A16 GEMM right behind it
+// (the output of a per-head kernel on its way into a projection): the GEMM reads the untransposed tensor through a
+// three-dimensional tensor map. `i` is the transposition.
+bool match_transpose_gemm(const Graph& G, uint32_t i, Span& sp) {
+    const wt_blob* b = G.b;
+    if (i + 1 >= b->n_ops) return false;
+    const wt_op &tr = b->ops[i], &mm = b->ops[i + 1];
+    if (tr.opcode != OP_TRANSPOSE_GEN_F16 || mm.opcode != OP_MATMUL_W4A16) return false;
+    if (tr.args[2] != 3 || (tr.args[7] & 0xFFFFFFu) != (1u | 0u << 8 | 2u << 16)) return false;
+    const uint32_t heads = tr.args[3], rows = tr.args[4], d = tr.args[5];
+    if (!heads || !rows || !d || d % 64u || rows < w4_gemm_min_rows()) return false;
+    if (!is_temp_ref(tr.args[1]) || mm.args[0] != tr.args[1] || mm.args[3] != rows || mm.args[4] != heads * d || mm.args[5] % 128u) return false;
+    std::vector<uint32_t> ops = {i, i + 1};
+    if (!closed(G, ops, {i + 1})) return false;
+    sp.kind = 7; sp.first = i; sp.count = 2; sp.ops = ops; sp.keep = {i};
+    sp.a_ref = tr.args[0]; sp.M = rows; sp.K = heads * d; sp.N = mm.args[5]; sp.hd = d;
+    return true;
+}
+
 bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
     const wt_blob* b = G.b;
     if (i + 1 >= b->n_ops) return false;
@@ -485,6 +505,10 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
     }
     for (uint32_t i = 0; i + 1 < b->n_ops; i++) {
         Span sp{};
+        if (!taken[i] && !taken[i + 1] && match_transpose_gemm(G, i, sp)) claim(sp);
+    }
+    for (uint32_t i = 0; i + 1 < b->n_ops; i++) {
+        Span sp{};
         if (!taken[i] && !taken[i + 1] && match_add_norm(G, i, sp)) claim(sp);
     }
     // temps written only by interior ops of chains
@@ -522,6 +546,7 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
         case 4: return t == sp.pq || t == sp.pk || t == sp.pv || (!sp.mask_is_slot && t == sp.mask);
         case 5: return t == sp.qkv || t == sp.cos_q || t == sp.sin_q || t == sp.cos_k || t == sp.sin_k;
         case 6: return t == sp.a_ref;
+        case 7: return t == sp.a_ref;
         }
         return true;
     };
@@ -636,6 +661,21 @@ void fuse_materialize(const wt_blob* b) {
                  ((uintptr_t)ko) | ((uintptr_t)vo)) & 3u) continue;
             uint32_t tokens = sp.B, nh = sp.nh, kvh = sp.kvh, hd = sp.hd;
             head.fused = [=](cudaStream_t st) { k_qkv_split_rope(st, qkv, cq, sq, ck, sk, qo, ko, vo, tokens, nh, kvh, hd); };
+        } else if (sp.kind == 7) {
+            const PlanOp &tr = g.plan[sp.first], &mm = g.plan[sp.first + 1];
+            const uint16_t* src = (const uint16_t*)resolve(b, sp.a_ref);
+            if (!tr.launch || !mm.launch || !mm.launch_w4_gemm || tr.rc || mm.rc || !src || (((uintptr_t)src) & 15u) || g.exact_ops) continue;
+            auto transpose = tr.launch, plain = mm.launch;
+            auto gemm = mm.launch_w4_gemm;
+            const uint32_t d = sp.hd;
+            unsigned int* status = g.d_status;
+            head.fused = [=](cudaStream_t st) {
+                W4Epilogue ep;
+                ep.status = status;
+                if (gemm(st, ep, src, d)) return;
+                transpose(st);
+                plain(st);
+            };
         } else if (sp.kind == 6) {
             const PlanOp &pg = g.plan[sp.gate_op], &pu = g.plan[sp.up_op];
             const uint16_t *gt = (const uint16_t*)resolve(b, sp.gate_t), *up = (const uint16_t*)resolve(b, sp.up_t);
@@ -731,7 +771,7 @@ void fuse_materialize(const wt_blob* b) {
                     lin.fused = [=](cudaStream_t st) {
                         W4Epilogue ep;
                         ep.mode = 3; ep.status = status; ep.res = res; ep.gamma = gam; ep.beta = bet; ep.sum_out = sum; ep.norm_out = y;
-                        if (gemm(st, ep)) return;
+                        if (gemm(st, ep, nullptr, 0)) return;
                         plain(st);
                         k_add_rmsnorm(st, aa, ab, gam, bet, sum, y, rows, rw);
                     };

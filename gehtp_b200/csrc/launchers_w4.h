@@ -67,9 +67,11 @@ void k_w4a16_skinny_swiglu(cudaStream_t st, const uint16_t* a, const uint32_t* p
 // tcgen05 / TMEM form for M >= 128 (w4a16_gemm_sm100.cu). Returns false when
 // the shape is outside what it handles (the caller then uses the skinny form).
 // `tile`: 0 = chosen from the shape, 1 = 128x128, 2 = 256x128, 3 = 256x256 (N % 256 == 0).
+// `a_d` != 0: the activations are stored [K / a_d][M][a_d] (a_d a multiple of 64 that divides K) - the output of a
+// per-head kernel, read through a three-dimensional tensor map without the transposition to [M][K].
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed,
                         const uint16_t* sc, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
-                        const W4Epilogue& ep, int tile = 0);
+                        const W4Epilogue& ep, int tile = 0, uint32_t a_d = 0);
 // Gate and up projections of a gated FFN plus its three elementwise ops on the same kernel: y[M, N] =
 // fp16(fp16(g * fp16(sigmoid(g))) * u), g = a . Wg, u = a . Wu (both [K, N]), neither g nor u written to memory.
 // `takes`: the shape test alone (N a multiple of 128, K of 64); the launcher also wants

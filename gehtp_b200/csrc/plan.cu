@@ -198,7 +198,9 @@ void plan_op(Planner& P, const wt_op& op, PlanOp& p) {
                 k_w4a16_skinny(st, act, pk, sc, y, M, K, N, ep);
             };
             if (M >= w4_gemm_min_rows())
-                p.launch_w4_gemm = [=](cudaStream_t st, const W4Epilogue& ep) { return k_w4a16_gemm_sm100(st, act, pk, sc, y, M, K, N, ep); };
+                p.launch_w4_gemm = [=](cudaStream_t st, const W4Epilogue& ep, const uint16_t* a_src, uint32_t a_d) {
+                    return k_w4a16_gemm_sm100(st, a_d ? a_src : act, pk, sc, y, M, K, N, ep, 0, a_d);
+                };
         }
         return;
     }

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4* __restrict__ wp,
                         const uint16_t* __restrict__ sc, const uint4* __restrict__ wp2, const uint16_t* __restrict__ sc2,
                         uint16_t* __restrict__ y, uint32_t M, uint32_t K,
-                        uint32_t N, W4Epilogue ep, uint32_t S, float* __restrict__ part) {
+                        uint32_t N, W4Epilogue ep, uint32_t S, float* __restrict__ part, uint32_t a_d) {
     using C = Cfg<MH, BN>;
     static_assert(!DUAL || BN == 256, "the gate | up form pairs two 128-column halves");
     static_assert(!DUAL || C::GROUPS == 3, "warps 20-23 help the epilogue of the gate | up form: they must own no operand stage");
@@ -186,7 +186,11 @@ w4a16_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint4*
                     mbar_expect_tx(&bars->full[s], A_BYTES);
 #pragma unroll
                     for (int h = 0; h < MH; h++)
-                        tma_load_2d(sA + s * A_BYTES + h * HALF_A_BYTES, &tmap_a, (int)(kb * BK), (int)(m0 + h * 128), &bars->full[s]);
+                        if (a_d)     // A stored [head][row][a_d]: column kb * 64 of A is column (kb * 64) % a_d of head (kb * 64) / a_d
+                            tma_load_3d(sA + s * A_BYTES + h * HALF_A_BYTES, &tmap_a, (int)((kb * BK) % a_d), (int)(m0 + h * 128), (int)((kb * BK) / a_d),
+                                        &bars->full[s]);
+                        else
+                            tma_load_2d(sA + s * A_BYTES + h * HALF_A_BYTES, &tmap_a, (int)(kb * BK), (int)(m0 + h * 128), &bars->full[s]);
                 }
             }
             if (*abort_flag)   // copies already requested must land before the CTA may go away
@@ -514,7 +518,7 @@ SplitScratch* split_scratch(cudaStream_t st, size_t need) {
 template <int MH, int BN, bool DUAL = false>
 bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, const uint16_t* sc, uint16_t* y,
             uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int sms, const uint32_t* packed2 = nullptr,
-            const uint16_t* sc2 = nullptr) {
+            const uint16_t* sc2 = nullptr, uint32_t a_d = 0) {
     using C = Cfg<MH, BN>;
     const size_t smem = 1024 + (size_t)C::STAGES * (C::A_BYTES + C::B_BYTES) + (size_t)C::RSTAGES * C::RAW_SLOT + sizeof(Barriers) + 16;
     static int have[64] = {};
@@ -542,7 +546,7 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     const uint32_t items = tiles * S;
     const uint32_t grid = items < (uint32_t)sms ? items : (uint32_t)sms;
     if (launch_pdl(w4a16_gemm_sm100_kernel<MH, BN, DUAL>, dim3(grid), dim3(NTHREADS), smem, st, tmap, (const uint4*)packed, sc,
-                   (const uint4*)packed2, sc2, y, M, K, N, ep, S, part) != cudaSuccess) {
+                   (const uint4*)packed2, sc2, y, M, K, N, ep, S, part, a_d) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
@@ -567,9 +571,19 @@ bool launch(cudaStream_t st, const CUtensorMap& tmap, const uint32_t* packed, co
     return true;
 }
 
-bool make_a_map(CUtensorMap* tmap, const uint16_t* a, uint32_t M, uint32_t K) {
+// a_d != 0: A is stored [K / a_d][M][a_d] (heads outermost, as a per-head kernel leaves its output); the map is
+// three-dimensional and a k block of 64 columns is a box of one head.
+bool make_a_map(CUtensorMap* tmap, const uint16_t* a, uint32_t M, uint32_t K, uint32_t a_d = 0) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return false;
+    if (a_d) {
+        cuuint64_t dims[3] = {a_d, M, K / a_d};
+        cuuint64_t strides[2] = {(cuuint64_t)a_d * 2, (cuuint64_t)M * a_d * 2};
+        cuuint32_t box[3] = {BK, 128, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        return enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void*)a, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     cuuint64_t dims[2] = {K, M};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     cuuint32_t box[2] = {BK, 128};
@@ -593,8 +607,9 @@ int sm_count() {
 }  // namespace
 
 bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* packed, const uint16_t* sc,
-                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile) {
+                        uint16_t* y, uint32_t M, uint32_t K, uint32_t N, const W4Epilogue& ep, int tile, uint32_t a_d) {
     if (!M || K % BK || N % 128) return false;
+    if (a_d && (a_d % BK || K % a_d)) return false;
     if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)sc & 15) || ((uintptr_t)y & 15)) return false;
     if (ep.mode == 1 && ((uintptr_t)ep.res & 15)) return false;
     if (ep.mode == 3 && (!ep.res || !ep.gamma || !ep.sum_out || !ep.norm_out || N * sizeof(float) > 48u * 1024u ||
@@ -602,15 +617,15 @@ bool k_w4a16_gemm_sm100(cudaStream_t st, const uint16_t* a, const uint32_t* pack
         return false;
     const int sms = sm_count();
     CUtensorMap tmap;
-    if (!make_a_map(&tmap, a, M, K)) return false;
+    if (!make_a_map(&tmap, a, M, K, a_d)) return false;
     // Largest tile that still gives every SM a tile.
     const uint32_t t256 = ((M + 255) / 256) * (N / 256);
     const uint32_t t128 = ((M + 255) / 256) * (N / 128);
     const int force = tile;   // 0: by shape, 1: 128x128, 2: 256x128, 3: 256x256
     if (force == 3 ? N % 256 == 0 : (force == 0 && N % 256 == 0 && M > 128 && t256 >= (uint32_t)sms))
-        return launch<2, 256>(st, tmap, packed, sc, y, M, K, N, ep, sms);
-    if (force == 2 || (force == 0 && M > 128 && t128 >= (uint32_t)sms)) return launch<2, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
-    return launch<1, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms);
+        return launch<2, 256>(st, tmap, packed, sc, y, M, K, N, ep, sms, nullptr, nullptr, a_d);
+    if (force == 2 || (force == 0 && M > 128 && t128 >= (uint32_t)sms)) return launch<2, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms, nullptr, nullptr, a_d);
+    return launch<1, 128>(st, tmap, packed, sc, y, M, K, N, ep, sms, nullptr, nullptr, a_d);
 }
 
 bool w4a16_gemm_sm100_swiglu_takes(uint32_t M, uint32_t K, uint32_t N) {

@@ -392,6 +392,33 @@ def test_gate_up_gemm_edge_shapes_bit_equal(cuda, M, K, F):
     assert np.isfinite(res[0][0].view(np.float16).astype(np.float32)).all()
 
 
+@pytest.mark.parametrize("H,rows,D,N", [(4, 64, 64, 128), (16, 64, 128, 1024), (3, 200, 128, 256)])
+def test_gemm_reads_per_head_tensor_without_transposition(cuda, H, rows, D, N):
+    """[heads][rows][d] -> TRANSPOSE_GEN -> W4A16 GEMM at GEMM row counts: the fused plan gives the GEMM the
+    untransposed tensor through a three-dimensional tensor map (one box of 64 columns lies in one head). Bit for bit
+    the op-by-op plan's result; the second shape is the out-projection of the delta-rule layer."""
+    from gehtp_b200.runlists import Emitter, rand_w4
+    rng = np.random.default_rng(21)
+    e = Emitter("w4")
+    face = e.b.add_ext_in(H * rows * D * 2)
+    x = e.face(S(face), 0, H * rows * D, H * rows * D)
+    xt = e.transpose3(x, (H, rows, D), (1, 0, 2))
+    y = e.linear(xt, *rand_w4(rng, H * D, N), rows)
+    buf = e.b.build()
+    inp = rng.standard_normal(H * rows * D).astype(np.float16)
+    res = []
+    for fusion in (1, 0):
+        cuda.gehtp_cuda_set_fusion(fusion)
+        eng = Engine(cuda, buf)
+        eng.run_io(inp, y, None)
+        res.append(eng.temp(y, np.uint16).copy())
+        if fusion:
+            assert cuda.gehtp_cuda_fused_ops() == 2
+        eng.shutdown()
+    cuda.gehtp_cuda_set_fusion(1)
+    assert res[0].size == rows * N and np.array_equal(res[0], res[1])
+
+
 def test_constant_ops_run_once(cuda):
     """A slice of a table that lives in a weight slot and a transposition of that slice give the same bytes on every
     run: the fused engine executes them on the first run and skips them afterwards (also in the captured graph); a
