@@ -20,12 +20,14 @@
 //   warps 4-7 : epilogue (tcgen05.ld -> fp16 -> 64-byte row segments)
 // All mbarrier waits are bounded; on a timeout the CTA raises the engine's status word, every role
 // stops, in-flight copies are waited for (bounded) and the TMEM is freed.
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_umma.cuh"
+#include "w4_stream.cuh"
 
 namespace gehtp {
 
@@ -345,6 +347,68 @@ f16_gemv_nk_kernel(const uint16_t* a, const uint16_t* __restrict__ w, uint16_t* 
     }
 }
 
+// ---- the same on the tensor cores (mma.sync m16n8k16) for up to 8 rows per CTA row tile: a warp owns 8 output
+// columns and walks K in chunks of 32. Lane (g, t) loads 16 bytes of weight row n0 + g (8 consecutive k values)
+// and the 16 bytes at the same k of activation row g from shared memory; the first and the second half of those
+// 8 values feed two MMAs. Which of the 16 k slots of an MMA a value takes does not matter as long as A and B
+// agree, so no shuffling into the fragment order is needed: one 16-byte load per operand and chunk, 2 MMAs,
+// where the scalar form above spends some 140 instructions on the same 8 weights at 8 rows.
+// The first batch of weights (constants) is requested before the dependency wait.
+template <int UNR>
+__global__ void __launch_bounds__(256)
+f16_gemv_mma_kernel(const uint16_t* a, const uint16_t* __restrict__ w, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy) {
+    extern __shared__ __align__(16) unsigned char smem_a[];      // [8][K * 2 + 64] bytes: rows 64 bytes apart in the banks
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t m0 = blockIdx.y * 8, n0 = (blockIdx.x * 8 + warp) * 8, KC = K / 32, RS = K * 2 + 64;
+    const bool active = n0 < N;
+    const uint4* wr = (const uint4*)(w + (size_t)min(n0 + g, N - 1) * K) + t;      // chunk kc lies 4 * kc further
+    uint4 wq[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; u++) wq[u] = (active && (uint32_t)u < KC) ? __ldcs(wr + 4 * u) : make_uint4(0, 0, 0, 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t i = threadIdx.x; i < 8 * (K / 8); i += blockDim.x) {
+        const uint32_t r = i / (K / 8), c = i % (K / 8), m = min(m0 + r, M - 1);       // rows past M repeat row M-1; never stored
+        *(uint4*)(smem_a + r * RS + c * 16) = __ldcg((const uint4*)(a + (size_t)m * K) + c);
+    }
+    __syncthreads();
+    if (!active) return;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const unsigned char* arow = smem_a + g * RS + t * 16;
+    for (uint32_t kc0 = 0; kc0 < KC; kc0 += UNR) {
+        uint4 nx[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; u++) nx[u] = kc0 + UNR + u < KC ? __ldcs(wr + 4 * (kc0 + UNR + u)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < UNR; u++) {
+            if (kc0 + u >= KC) break;
+            const uint4 av = *(const uint4*)(arow + (kc0 + u) * 64);
+            const uint32_t a1[4] = {av.x, 0u, av.y, 0u}, a2[4] = {av.z, 0u, av.w, 0u};    // rows g + 8 of the tile: none
+            mma16816(acc, a1, wq[u].x, wq[u].y);
+            mma16816(acc, a2, wq[u].z, wq[u].w);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; u++) wq[u] = nx[u];
+    }
+    const uint32_t m = m0 + g, n = n0 + 2 * t;
+    if (m < M) {
+        if (n < N) y[(size_t)m * ldy + n] = f2h(acc[0]);
+        if (n + 1 < N) y[(size_t)m * ldy + n + 1] = f2h(acc[1]);
+    }
+}
+
+bool launch_gemv_mma(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy) {
+    const size_t smem = (size_t)8 * (K * 2 + 64);
+    static int have[64] = {};
+    if (K % 32 || smem > 200 * 1024 || (smem > 48 * 1024 && !ensure_dyn_smem(f16_gemv_mma_kernel<8>, smem, have))) return false;
+    if (launch_pdl(f16_gemv_mma_kernel<8>, dim3((N + 63) / 64, (M + 7) / 8), dim3(256), smem, st, a, w, y, M, K, N, ldy) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    g_launches++;
+    return true;
+}
+
 template <int MR>
 bool launch_gemv(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, uint32_t M, uint32_t K, uint32_t N, uint32_t ldy) {
     const size_t smem = (size_t)MR * K * 2;
@@ -367,7 +431,11 @@ bool launch_gemv(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t
 bool k_matmul_f16_nk(cudaStream_t st, const uint16_t* a, const uint16_t* w, uint16_t* y, uint32_t M, uint32_t K, uint32_t N,
                      uint32_t ldy, unsigned int* status) {
     if (!M || !K || !N || (K & 7u) || ((((uintptr_t)a) | ((uintptr_t)w)) & 15u)) return false;
-    if (M < 32) return M <= 4 ? launch_gemv<4>(st, a, w, y, M, K, N, ldy) : launch_gemv<8>(st, a, w, y, M, K, N, ldy);
+    if (M < 32) {
+        static const int mma_on = [] { const char* e = std::getenv("GEHTP_CUDA_F16_GEMV_MMA"); return e ? std::atoi(e) : 1; }();
+        if (mma_on && launch_gemv_mma(st, a, w, y, M, K, N, ldy)) return true;
+        return M <= 4 ? launch_gemv<4>(st, a, w, y, M, K, N, ldy) : launch_gemv<8>(st, a, w, y, M, K, N, ldy);
+    }
     if (M < 128 || K % BK || N % 128 || (ldy & 7u) || ((uintptr_t)y & 15u)) return false;
     static int sms_of[64] = {};
     int dev = 0;
