@@ -1,28 +1,29 @@
-// W4A16 group-64 GEMM for prefill (M >= 128) on the 5th-generation tensor cores:
+// W4A16 group-64 GEMM from 64 rows up (prefill, wide decode batches) on the 5th-generation tensor cores:
 // Y[M,N] = A[M,K] . W, W = fp16((q-8)*scale), fp32 accumulation in TMEM.
 //
-// Persistent kernel, one CTA per SM. A CTA walks output tiles of (128*MH) x 128
-// (MH = 1 or 2 row halves sharing one dequantised B tile); K is walked in steps
-// of 64 (one scale group, one 128-byte swizzled row per operand row).
-//   warp 0     : one lane issues the TMA loads of the A tile (MH boxes of 128
-//                rows x 64 k, SWIZZLE_128B) into a STAGES-deep ring.
-//   warp 1     : one lane issues tcgen05.mma (4 x k16 x MH per stage, M128 N128)
-//                and tcgen05.commit, which frees the stage when the MMAs have
-//                read it; the accumulators are double-buffered in TMEM so the
-//                epilogue of a tile overlaps the main loop of the next one.
-//   warp 2     : one lane streams the int4 tile of each k block (8 strip units,
-//                4 KB contiguous in the strip-major layout) and its 128 group
-//                scales with bulk copies into an RSTAGES-deep ring.
+// Persistent kernel, one CTA per SM. A CTA walks output tiles of (128*MH) x BN (MH = 1 or 2 row halves sharing
+// one dequantised B tile, BN = 128 or 256 columns); K is walked in steps of 64 (one scale group, one 128-byte
+// swizzled row per operand row).
+//   warp 0     : one lane issues the TMA loads of the A tile (MH boxes of 128 rows x 64 k, SWIZZLE_128B) into a
+//                STAGES-deep ring. A is [M][K], or [K / d][M][d] read through a three-dimensional map (the
+//                output of a per-head kernel, without a transposed copy).
+//   warp 1     : walks the k loop as a whole warp (uniform counters and descriptors); one lane issues
+//                tcgen05.mma (4 x k16 x MH per stage, M128 x BN) and tcgen05.commit, which frees the stage
+//                when the MMAs have read it. The accumulators are double-buffered in TMEM (except 256 x 256)
+//                so that the epilogue of a tile overlaps the main loop of the next one.
+//   warp 2     : one lane streams the int4 tile of each k block (BN / 16 strip units, contiguous in the
+//                strip-major layout) and its BN group scales with bulk copies into an RSTAGES-deep ring.
 //   warp 3     : owns the TMEM allocation.
-//   warps 4-7  : epilogue (tcgen05.ld -> fp16 -> 64-byte row segments).
-//   warps 8-23 : dequant, one group of four warps per operand stage (the 3-stage
-//                configurations have no stage for warps 20-23: idle, or epilogue helpers in the gate | up form). A warp turns its strip units into fp16 with
-//                the magic-number trick, multiplies by the group scale and stores
-//                16-byte chunks into the stage's B tile in the 128B-swizzled
-//                K-major form tcgen05.mma reads.
+//   warps 4-7  : epilogue (tcgen05.ld -> fp16 -> row segments).
+//   warps 8-23 : dequant, one group of four warps per operand stage (the 3-stage configurations have no stage
+//                for warps 20-23: idle, or epilogue helpers in the gate | up form). A warp turns its strip units
+//                into fp16 with the magic-number trick, multiplies by the group scale and stores 16-byte chunks
+//                into the stage's B tile in the 128B-swizzled K-major form tcgen05.mma reads.
+// Gate | up form (DUAL): the B tile holds 128 columns of two matrices, the epilogue writes their SwiGLU product.
 // Few-tile shapes (prefill projections with N = 1024, decode at 64 rows): K is cut into S runs, one work item per
 // (tile, run); a run writes its fp32 partial sums and w4a16_splitk_reduce_kernel adds the runs in order (same bits
-// on every call) and applies the epilogue. 512 x 3072 x 1024: 22.9 -> 12.7 us.
+// on every call) and applies the epilogue - or, where a residual ADD and an RMSNORM2 follow the matmul,
+// w4a16_splitk_add_rmsnorm_kernel adds the runs, the residual, and normalises. 512 x 3072 x 1024: 22.9 -> 12.4 us.
 // All mbarrier waits are bounded; on a timeout the CTA raises a flag, every role
 // stops, in-flight copies are waited for (bounded), and the TMEM is freed.
 #include <cstdlib>
