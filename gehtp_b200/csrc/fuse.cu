@@ -1,16 +1,23 @@
-// Plan-time fusion: recognises op chains of the runlist and replaces each by
-// one or two launches. Three chains are handled, all in the shape the
-// reference's emitter decomposes ONNX graphs into (one op per node):
+// Plan-time fusion: recognises op chains of the runlist and replaces each by one to three launches. The chains
+// are the shapes the reference's emitter decomposes ONNX graphs into (one op per node):
 //
-//   attention step   SPLIT x3, rotary on q and k (mul / slice / slice / neg /
-//                    concat / mul / add, twice), KV_APPEND (AUTO position),
-//                    KV_GATHER K^T and V, batched MATMUL_F16 scores, BINARY
-//                    scale by a broadcast constant, ADD mask, SOFTMAX, batched
-//                    MATMUL_F16 with V           -> rope+append kernel, split-KV
-//                                                   attention kernel, merge kernel
-//   SwiGLU           W4A16 gate, UNARY sigmoid, BINARY mul, W4A16 up, BINARY mul
-//                                                -> one pass over both matrices
-//   residual + norm  ADD followed by RMSNORM2 of its result -> one kernel
+//   decode attention    SPLIT x3, rotary on q and k (mul / slice / slice / neg / concat / mul / add, twice),
+//                       KV_APPEND (AUTO position), KV_GATHER K^T and V, batched MATMUL_F16 scores, BINARY scale by a
+//                       broadcast constant, ADD mask, SOFTMAX, batched MATMUL_F16 with V
+//                                               -> rotary + append (in the q|k|v projection's epilogue where it can),
+//                                                  split-KV attention kernel, merge kernel
+//   SwiGLU              W4A16 gate, UNARY sigmoid, BINARY mul, W4A16 up, BINARY mul
+//                                               -> one GEMV over both matrices (few rows), one tcgen05 GEMM with both
+//                                                  accumulators in TMEM (64 rows and up), or two GEMMs + one
+//                                                  elementwise kernel (widths the GEMM does not take)
+//   residual + norm     ADD followed by RMSNORM2 of its result -> one kernel; behind a W4A16 GEMM: in the kernel that
+//                       adds the GEMM's split-K runs
+//   rotary              the 7-op rotary chain on its own -> one kernel
+//   prefill attention   TRANSPOSE_GEN x3, scores, scale, mask, SOFTMAX, P V, TRANSPOSE_GEN -> tcgen05 attention
+//   prefill q|k|v head  SPLIT x3 + two rotary chains (17 ops) -> one kernel
+//   transposition + GEMM  [heads][rows][d] -> [rows][heads d] in front of a W4A16 GEMM -> the GEMM reads the
+//                       untransposed tensor through a three-dimensional tensor map
+// and marks the data-movement ops whose result is a constant of the blob (fold_constants).
 //
 // A chain is fused only when every intermediate temp is consumed inside the
 // chain and the chain's ops are contiguous in the list. Temps that exist only
