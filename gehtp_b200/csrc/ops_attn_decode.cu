@@ -699,8 +699,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, AttnDecodeArgs 
 // flight together) into a running (max, sum, vector) of its own; the 16 warp results are then combined in warp
 // order. Every slice of the scratch buffers is written by the split-KV kernel (an empty one as max = -inf,
 // sum = 0), so nothing here depends on the position counter and the first loads leave right after the wait.
-constexpr int MERGE_WARPS = 16;
-
+// MERGE_WARPS warps share the slices of one query head (8 slices in flight per warp and pass); their partial
+// results meet in shared memory. Few slices want few warps: the closing combination walks all of them.
+template <int MERGE_WARPS>
 __global__ void __launch_bounds__(MERGE_WARPS * 32)
 attn_decode_merge_kernel(const float* part_o, const float* part_ml, uint16_t* out, uint32_t rep, uint32_t hd,
                          uint32_t nsplit, uint32_t* bump_counter) {
@@ -911,8 +912,17 @@ bool k_attn_decode(cudaStream_t st, const AttnDecodeArgs& a, uint32_t hd, uint16
         }
     }
     if (!ok) { cudaGetLastError(); return false; }
-    ok = launch_pdl(attn_decode_merge_kernel, dim3(kv_heads_total * a.rep), dim3(MERGE_WARPS * 32), 0, st,
-                    (const float*)a.part_o, (const float*)a.part_ml, out, a.rep, hd, a.nsplit, a.bump_counter) == cudaSuccess;
+    {
+        static const int forced = [] { const char* e = std::getenv("GEHTP_CUDA_MERGE_WARPS"); return e ? std::atoi(e) : 0; }();
+        const int mw = forced ? forced : (a.nsplit <= 32 ? 4 : a.nsplit <= 64 ? 8 : 16);
+        const dim3 grid(kv_heads_total * a.rep);
+        const float *po = (const float*)a.part_o, *pml = (const float*)a.part_ml;
+        cudaError_t ce;
+        if (mw <= 4) ce = launch_pdl(attn_decode_merge_kernel<4>, grid, dim3(128), 0, st, po, pml, out, a.rep, hd, a.nsplit, a.bump_counter);
+        else if (mw <= 8) ce = launch_pdl(attn_decode_merge_kernel<8>, grid, dim3(256), 0, st, po, pml, out, a.rep, hd, a.nsplit, a.bump_counter);
+        else ce = launch_pdl(attn_decode_merge_kernel<16>, grid, dim3(512), 0, st, po, pml, out, a.rep, hd, a.nsplit, a.bump_counter);
+        ok = ce == cudaSuccess;
+    }
     if (!ok) { cudaGetLastError(); return false; }
     g_launches += 2;
     return true;
