@@ -133,7 +133,8 @@ Rope match_rope(const Graph& G, int add_op) {
 struct Span {
     int kind;                // 0 decode attention, 1 swiglu, 2 add+norm, 3 rotary, 4 prefill attention,
                              // 5 prefill split + rotary of q|k|v, 6 swiglu tail behind two GEMMs,
-                             // 7 [head][row][d] -> [row][head * d] transposition in front of a W4A16 GEMM
+                             // 7 [head][row][d] -> [row][head * d] transposition in front of a W4A16 GEMM,
+                             // 8 per-row SLICE + ARGMAX of a matrix joined by a CONCAT tree (greedy sampling of a batch)
     uint32_t first, count;
     std::vector<uint32_t> ops;
     // attention
@@ -442,6 +443,68 @@ bool match_transpose_gemm(const Graph& G, uint32_t i, Span& sp) {
     return true;
 }
 
+// Greedy sampling of a batch as the op list spells it: for every row r of the logits [rows][n] a SLICE of that row and
+// an ARGMAX of the slice, the int32 results joined in row order by a tree of CONCAT ops (up to four inputs each).
+// `root` is the CONCAT at the top of such a tree. One launch finds all the maxima and writes them where the root's
+// output lies.
+bool match_argmax_rows(const Graph& G, uint32_t root, Span& sp) {
+    const wt_blob* b = G.b;
+    std::vector<uint32_t> ops, leaves;
+    // depth-first, inputs in order: the leaves come out in the order their values lie in the root's output
+    std::vector<std::pair<uint32_t, uint32_t>> stack;     // (concat op, next input)
+    if (b->ops[root].opcode != OP_CONCAT_F16) return false;
+    stack.push_back({root, 0});
+    std::vector<uint32_t> width(b->n_ops, 0);              // fp16 units an op contributes
+    while (!stack.empty()) {
+        const uint32_t c = stack.back().first, k = stack.back().second;
+        const wt_op& co = b->ops[c];
+        const uint32_t n_seg = co.args[10];
+        if (n_seg < 1 || n_seg > 4 || ops.size() > 4096) return false;
+        if (k == n_seg) {
+            uint32_t total = 0;
+            for (uint32_t s = 0; s < n_seg; s++) total += co.args[12 + s];
+            if (co.args[11] != total || total != width[c]) return false;      // one outer row, sizes add up to what came in
+            ops.push_back(c);
+            stack.pop_back();
+            if (!stack.empty()) width[stack.back().first] += total;
+            continue;
+        }
+        stack.back().second++;
+        const int p = G.producer_of_arg[k][c];
+        if (p < 0) return false;
+        if (b->ops[p].opcode == OP_CONCAT_F16) {
+            if (co.args[12 + k] == 0) return false;
+            stack.push_back({(uint32_t)p, 0});
+        } else if (b->ops[p].opcode == OP_ARGMAX_F16) {
+            if (co.args[12 + k] != 2) return false;                            // an int32 = two fp16-sized units
+            leaves.push_back((uint32_t)p);
+            ops.push_back((uint32_t)p);
+            width[c] += 2;
+        } else {
+            return false;
+        }
+    }
+    if (leaves.size() < 2 || leaves.size() > kArgmaxMaxRows) return false;
+    uint32_t src = 0, n = 0;
+    for (size_t r = 0; r < leaves.size(); r++) {
+        const wt_op& am = b->ops[leaves[r]];
+        const int sl = G.producer_of_arg[0][leaves[r]];
+        if (sl < 0 || b->ops[sl].opcode != OP_STRIDED_SLICE_F16) return false;
+        const wt_op& s = b->ops[sl];
+        if (r == 0) { src = s.args[0]; n = am.args[2]; }
+        // rank 2, rows [r, r+1) x columns [0, n) of a [rows][n] tensor, unit strides
+        if (s.args[0] != src || am.args[2] != n || s.args[2] != n || s.args[3] != 2 || s.args[4] != r || s.args[5] != 0 ||
+            s.args[7] != r + 1 || s.args[8] != n || s.args[10] > 1 || s.args[11] > 1 || s.args[13] < leaves.size() || s.args[14] != n)
+            return false;
+        ops.push_back((uint32_t)sl);
+    }
+    uint32_t first;
+    if (!contiguous(ops, first) || !closed(G, ops, {root})) return false;
+    sp.kind = 8; sp.first = first; sp.count = (uint32_t)ops.size(); sp.ops = ops;
+    sp.a_ref = src; sp.y = b->ops[root].args[8]; sp.M = (uint32_t)leaves.size(); sp.N = n;
+    return true;
+}
+
 bool match_add_norm(const Graph& G, uint32_t i, Span& sp) {
     const wt_blob* b = G.b;
     if (i + 1 >= b->n_ops) return false;
@@ -514,6 +577,10 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
         Span sp{};
         if (!taken[i] && !taken[i + 1] && match_transpose_gemm(G, i, sp)) claim(sp);
     }
+    for (uint32_t i = b->n_ops; i-- > 0;) {      // from the back: the root of a CONCAT tree comes after its branches
+        Span sp{};
+        if (!taken[i] && b->ops[i].opcode == OP_CONCAT_F16 && match_argmax_rows(G, i, sp)) claim(sp);
+    }
     for (uint32_t i = 0; i + 1 < b->n_ops; i++) {
         Span sp{};
         if (!taken[i] && !taken[i + 1] && match_add_norm(G, i, sp)) claim(sp);
@@ -554,6 +621,7 @@ void fuse_analyze(const wt_blob* b, const std::vector<PlanOp>& meas, std::vector
         case 5: return t == sp.qkv || t == sp.cos_q || t == sp.sin_q || t == sp.cos_k || t == sp.sin_k;
         case 6: return t == sp.a_ref;
         case 7: return t == sp.a_ref;
+        case 8: return t == sp.a_ref;
         }
         return true;
     };
@@ -668,6 +736,22 @@ void fuse_materialize(const wt_blob* b) {
                  ((uintptr_t)ko) | ((uintptr_t)vo)) & 3u) continue;
             uint32_t tokens = sp.B, nh = sp.nh, kvh = sp.kvh, hd = sp.hd;
             head.fused = [=](cudaStream_t st) { k_qkv_split_rope(st, qkv, cq, sq, ck, sk, qo, ko, vo, tokens, nh, kvh, hd); };
+        } else if (sp.kind == 8) {
+            const uint16_t* x = (const uint16_t*)resolve(b, sp.a_ref);
+            int32_t* y = (int32_t*)resolve(b, sp.y);
+            if (!x || !y || (((uintptr_t)y) & 3u)) continue;
+            const uint32_t rows = sp.M, n = sp.N;
+            // the ops of the tree, in list order, for the case that the one launch is refused
+            std::vector<std::function<void(cudaStream_t)>> each;
+            bool whole = true;
+            for (uint32_t o : sp.ops) {
+                if (g.plan[o].rc || !g.plan[o].launch || g.plan[o].uses_internal) { whole = false; break; }
+                each.push_back(g.plan[o].launch);
+            }
+            head.fused = [=](cudaStream_t st) {
+                if (k_argmax_rows(st, x, y, rows, n)) return;
+                if (whole) for (const auto& f : each) f(st);
+            };
         } else if (sp.kind == 7) {
             const PlanOp &tr = g.plan[sp.first], &mm = g.plan[sp.first + 1];
             const uint16_t* src = (const uint16_t*)resolve(b, sp.a_ref);

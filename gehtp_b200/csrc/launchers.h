@@ -38,6 +38,9 @@ void k_gather(cudaStream_t st, const uint16_t* tbl, const int32_t* idx, uint16_t
 void k_scatter_nd(cudaStream_t st, const int32_t* idx, const uint16_t* upd, uint16_t* y,
                   uint32_t n, uint32_t K, uint32_t n_idx, uint32_t block, const uint32_t* od5);
 void k_argmax(cudaStream_t st, const uint16_t* x, int32_t* y, uint32_t n);
+// y[r] = argmax of row r of x [rows][n] (rows <= kArgmaxMaxRows): one launch for a batch of rows. false: too many rows.
+constexpr uint32_t kArgmaxMaxRows = 256;
+bool k_argmax_rows(cudaStream_t st, const uint16_t* x, int32_t* y, uint32_t rows, uint32_t n);
 void k_im2col(cudaStream_t st, const uint16_t* a, uint16_t* cols, const uint32_t* args15);
 void k_conv2d(cudaStream_t st, const uint16_t* A, const uint16_t* W, const uint16_t* Bv,
               uint16_t* out, uint32_t M, uint32_t K, uint32_t N, uint32_t oy0, uint32_t ox0,

@@ -538,6 +538,79 @@ void k_argmax(cudaStream_t st, const uint16_t* x, int32_t* y, uint32_t n) {
     g_launches++;
 }
 
+// The same for a batch of rows in one launch (grid.y = row): greedy sampling of a decode step over B sequences is
+// B argmax ops on the rows of the logits matrix; per-row winners and counters, the last CTA of a row merges it.
+__device__ float g_argmax_rows_val[kArgmaxMaxRows][128];
+__device__ int g_argmax_rows_idx[kArgmaxMaxRows][128];
+__device__ unsigned int g_argmax_rows_done[kArgmaxMaxRows];
+
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const uint16_t* x, int32_t* __restrict__ y, uint32_t n) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ bool s_last;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t row = blockIdx.y;
+    const uint16_t* xr = x + (size_t)row * n;
+    const uint32_t per = ((n + gridDim.x - 1) / gridDim.x + 7u) & ~7u;
+    const uint32_t lo = blockIdx.x * per, hi = (lo + per < n) ? lo + per : n;
+    float bv = -1e30f;
+    int bi = 0x7fffffff;
+    if (lo < hi) {
+        if ((((uintptr_t)xr) & 15u) == 0) {
+            for (uint32_t i = lo + threadIdx.x * 8; i < hi; i += blockDim.x * 8) {
+                if (i + 8 <= hi) {
+                    const uint4 q = __ldcg((const uint4*)(xr + i));
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float a = h2f((uint16_t)(w[k] & 0xffffu)), b = h2f((uint16_t)(w[k] >> 16));
+                        if (a > bv) { bv = a; bi = (int)(i + 2 * k); }
+                        if (b > bv) { bv = b; bi = (int)(i + 2 * k + 1); }
+                    }
+                } else {
+                    for (uint32_t k = i; k < hi; k++) { const float a = h2f(__ldcg(xr + k)); if (a > bv) { bv = a; bi = (int)k; } }
+                }
+            }
+        } else {
+            for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) { const float a = h2f(__ldcg(xr + i)); if (a > bv) { bv = a; bi = (int)i; } }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_take(ov, oi, bv, bi);
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) argmax_take(sv[w], si[w], bv, bi);
+        g_argmax_rows_val[row][blockIdx.x] = bv;
+        g_argmax_rows_idx[row][blockIdx.x] = bi;
+        __threadfence();
+        s_last = atomicAdd(&g_argmax_rows_done[row], 1u) + 1 == gridDim.x;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence();
+        float fv = -1e30f;
+        int fi = 0x7fffffff;
+        for (uint32_t b = 0; b < gridDim.x; b++)
+            argmax_take(__ldcg(&g_argmax_rows_val[row][b]), __ldcg(&g_argmax_rows_idx[row][b]), fv, fi);
+        y[row] = (fi == 0x7fffffff) ? 0 : fi;
+        g_argmax_rows_done[row] = 0;
+    }
+}
+bool k_argmax_rows(cudaStream_t st, const uint16_t* x, int32_t* y, uint32_t rows, uint32_t n) {
+    if (!rows || rows > kArgmaxMaxRows || !n) return false;
+    unsigned gx = (n + 4095) / 4096;
+    if (gx < 1) gx = 1;
+    if (gx > 128) gx = 128;
+    if (launch_pdl(argmax_rows_kernel, dim3(gx, rows), dim3(256), 0, st, x, y, n) != cudaSuccess) { cudaGetLastError(); return false; }
+    g_launches++;
+    return true;
+}
+
 // im2col for the conv pipeline (oplist_exec.c:615-645).
 struct U15 { uint32_t v[15]; };
 __global__ void im2col_kernel(const uint16_t* __restrict__ a, uint16_t* __restrict__ cols, U15 g) {
